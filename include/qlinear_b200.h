@@ -1,0 +1,126 @@
+/*
+ * qlinear_b200 -- C ABI of the B200 (sm_100a) quantized-linear kernels.
+ *
+ * Every entry point takes plain pointers and sizes, is stream-ordered on the caller's stream
+ * (a cudaStream_t / CUstream passed as void*), never synchronises the device and returns a
+ * ql_status; ql_last_error() gives the message of the calling thread's last failure.  All
+ * tensors are dense, row-major and live in device memory unless stated otherwise.
+ *
+ * Reference interfaces each group replaces (paths inside NVIDIA/TensorRT-Incubator):
+ *   tensorrt.quantize      mlir-tensorrt/tensorrt/include/mlir-tensorrt-dialect/TensorRT/IR/TensorRTOps.td:3091-3273
+ *   tensorrt.dequantize    .../TensorRTOps.td:3364-3506
+ *   argument rules         mlir-tensorrt/tensorrt/lib/TensorRT/IR/Verification.cpp:1182-1380
+ *   tp.quantize/dequantize tripy/nvtripy/frontend/ops/quantize.py:39-119, dequantize.py:39-114
+ *   tp.Linear / matmul     tripy/nvtripy/frontend/module/linear.py:112-151, frontend/ops/matmul.py:29-108
+ */
+#ifndef QLINEAR_B200_H
+#define QLINEAR_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QL_API __attribute__((visibility("default")))
+#define QL_MAX_RANK 8
+
+typedef enum {
+  QL_F32 = 0,
+  QL_F16 = 1,
+  QL_BF16 = 2,
+  QL_I8 = 3,
+  QL_I4 = 4,     /* two values per byte, first element in the low nibble */
+  QL_F8E4M3 = 5  /* e4m3fn: no infinities, 0x7F/0xFF are NaN, largest finite 448 */
+} ql_dtype;
+
+typedef enum {
+  QL_OK = 0,
+  QL_ERR_INVALID_ARGUMENT = 1, /* violates the operator's argument rules; message says which */
+  QL_ERR_UNSUPPORTED = 2,      /* legal for the reference operator but not built here */
+  QL_ERR_CUDA = 3,             /* a CUDA call failed; message carries cudaGetErrorString */
+  QL_ERR_NO_DEVICE = 4,        /* no usable sm_100 device / driver */
+  QL_ERR_DEVICE_TIMEOUT = 5    /* a bounded on-device wait ran out (kernel returned early) */
+} ql_status;
+
+/* fp8 quantize semantics found in the reference tree; QL_FP8_DIRECT is the operator's
+ * specification (one rounding from the f32 quotient, saturate to +-448). */
+typedef enum {
+  QL_FP8_DIRECT = 0,
+  QL_FP8_VIA_F16 = 1,   /* f32 -> f16 -> e4m3, as kernel/lib/Kernel/Transforms/NormalizeQuantizedConversions.cpp:43-80 lowers it */
+  QL_FP8_STABLEHLO = 2  /* divide, round to integer, clamp, convert in the input type
+                           (compiler/lib/Dialect/StablehloExt/Transforms/StablehloRaiseQDQ.cpp:233-265) */
+} ql_fp8_mode;
+
+typedef struct {
+  void *data;                 /* device pointer (scales may also be device pointers only) */
+  int32_t dtype;              /* ql_dtype */
+  int32_t rank;               /* 0 = scalar */
+  int64_t shape[QL_MAX_RANK]; /* logical element counts; QL_I4 tensors hold ceil(numel/2) bytes */
+} ql_tensor;
+
+/* Attributes of tensorrt.quantize / tensorrt.dequantize.  The mode follows the scale's rank as in
+ * the reference verifier: rank 0 = per-tensor (axis must be absent), rank 1 = per-channel (axis
+ * required, scale length == input.shape[axis]), rank == input rank = block quantization (axis
+ * absent; exactly one differing dimension, the last or second last; block size =
+ * input.shape[d] / scale.shape[d]). */
+typedef struct {
+  int32_t has_axis;
+  int32_t axis;
+  int32_t fp8_mode; /* ql_fp8_mode; ignored unless the quantized type is QL_F8E4M3 */
+} ql_qdq_attrs;
+
+QL_API int ql_version(void);
+QL_API const char *ql_last_error(void);
+/* Number of kernels this library has launched in this process since it was loaded. */
+QL_API uint64_t ql_launch_count(void);
+/* Device properties the host side needs: SM count, compute capability (major*10+minor). */
+QL_API int ql_device_info(int32_t *sm_count, int32_t *compute_capability);
+
+/* output = clamp(round_half_even(input / (f32)scale), qmin, qmax) as i8 / i4, or the saturating
+ * e4m3 conversion of the quotient.  input: f32 | f16 | bf16.  scale: f32 | f16 | bf16. */
+QL_API int ql_quantize(const ql_tensor *input, const ql_tensor *scale, ql_tensor *output,
+                       const ql_qdq_attrs *attrs, void *stream);
+
+/* output = (out type)((f32)input * (f32)scale).  input: i8 | i4 | e4m3.  output: f32 | f16 | bf16. */
+QL_API int ql_dequantize(const ql_tensor *input, const ql_tensor *scale, ql_tensor *output,
+                         const ql_qdq_attrs *attrs, void *stream);
+
+/* One pass that writes both quantize(input) and dequantize(quantize(input)); `dequantized` has the
+ * input's type.  Bit-identical to ql_quantize followed by ql_dequantize. */
+QL_API int ql_quantize_dequantize(const ql_tensor *input, const ql_tensor *scale,
+                                  ql_tensor *quantized, ql_tensor *dequantized,
+                                  const ql_qdq_attrs *attrs, void *stream);
+
+/* Dynamic scales (the reference only accepts constant scales; its user guide defines
+ * scale = amax / maxbound, tripy/docs/pre0_user_guides/02-quantization.md:104-112):
+ * scale[j] = max|input| over group j, divided by `maxbound` in f32, rounded to scale->dtype.
+ * Groups follow scale->rank exactly as in ql_qdq_attrs. */
+QL_API int ql_amax_scale(const ql_tensor *input, ql_tensor *scale, const ql_qdq_attrs *attrs,
+                         float maxbound, void *stream);
+
+/* Weight-only linear layers, Y[M,N] = X[M,K] . dequantize(W)[N,K]^T with f32 accumulation
+ * (linear.py:140-151 with quant_dtype set and no input scale).
+ *   w8: W int8 [N,K], scale [N] per output channel (weight_quant_dim = 0)
+ *   w4: W int4 packed [N,K/2], scale [N, K/block] (block quantization along K)
+ * X and Y are f16 or bf16 (same type); scales f32, f16 or bf16. */
+QL_API int ql_linear_w8a16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *scale,
+                           ql_tensor *y, void *stream);
+QL_API int ql_linear_w4a16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *scale,
+                           ql_tensor *y, void *stream);
+
+/* Quantized GEMMs on the tensor cores, Y[M,N] = (Xq[M,K] . Wq[N,K]^T) * sx * sw, f32 (fp8) or
+ * s32 (int8) accumulation, scales applied in the epilogue, Y bf16 or f16.
+ * sx: f32 scalar or [M] (per token); sw: f32 scalar or [N] (per output channel). */
+QL_API int ql_gemm_fp8(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx,
+                       const ql_tensor *sw, ql_tensor *y, void *stream);
+QL_API int ql_gemm_i8(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx,
+                      const ql_tensor *sw, ql_tensor *y, void *stream);
+/* 16-bit GEMM Y = (X . W^T) * sw, X and W both bf16 or both f16 ([M,K], [N,K]); sw may be null. */
+QL_API int ql_gemm_16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *sw, ql_tensor *y,
+                      void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QLINEAR_B200_H */

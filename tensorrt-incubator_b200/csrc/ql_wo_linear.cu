@@ -1,0 +1,225 @@
+// Weight-only linear layers for small batches: Y[M,N] = X[M,K] . dequantize(W)[N,K]^T.
+//
+// The work is bounded by reading W once from HBM, so the kernel streams W with 16-byte loads
+// straight into registers, dequantizes there (integer -> f16/bf16 is exact, so the scale can be
+// applied to f32 partial sums instead of to every weight) and feeds the warp-level tensor-core
+// MMA m16n8k16 with the weight tile as the 16-row operand and X as the 8-column operand.  A dot
+// product does not care in which order k is visited, which is used twice: each lane's 16 bytes of
+// one weight row are consumed as they lie in memory, and for int4 the value pairs that one mask
+// extracts (elements e and e+4 of a word) are matched by permuting the X registers.
+//
+// One block owns 16 output channels; its 8 warps split K and reduce through shared memory.
+// Reference composition this implements: tripy/nvtripy/frontend/module/linear.py:140-151
+// (quantize -> dequantize -> x @ transpose(w)) with the dequantize folded into the product.
+#include <cuda/std/type_traits>
+
+#include "ql_common.cuh"
+
+namespace ql {
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kThreadsWo = kWarps * 32;
+constexpr int kRowsPerBlock = 16;
+
+template <typename XT>
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  if constexpr (cuda::std::is_same<XT, __half>::value) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  } else {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+}
+
+// bytes i and i+1 of `u` (int8 values with their sign bit already flipped, i.e. value + 128)
+// -> packed pair of XT holding the exact integers
+template <typename XT, int I>
+__device__ __forceinline__ uint32_t int8_pair(uint32_t u) {
+  if constexpr (cuda::std::is_same<XT, __half>::value) {
+    // f16 0x6400 | b is 1024 + b; subtract 1024 + 128
+    uint32_t v = __byte_perm(u, 0x64646464u, 0x4040 | I | ((I + 1) << 8));
+    __half2 h = __hsub2(*reinterpret_cast<__half2 *>(&v), __half2half2(__ushort_as_half(0x6480)));
+    return *reinterpret_cast<uint32_t *>(&h);
+  } else {
+    // f32 0x4B000000 | b is 2^23 + b; subtract 2^23 + 128, then round (exactly) to bf16
+    float lo = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540 | I)) - 8388736.f;
+    float hi = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540 | (I + 1))) - 8388736.f;
+    __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&b);
+  }
+}
+
+// nibbles E and E+4 of `w` (signed int4) -> packed pair of XT holding the exact integers
+template <typename XT, int E>
+__device__ __forceinline__ uint32_t int4_pair(uint32_t w) {
+  uint32_t t = (w >> (4 * E)) & 0x000F000Fu;
+  if constexpr (cuda::std::is_same<XT, __half>::value) {
+    uint32_t v = t ^ 0x64086408u; // 1024 + (n ^ 8) = 1032 + value
+    __half2 h = __hsub2(*reinterpret_cast<__half2 *>(&v), __half2half2(__ushort_as_half(0x6408)));
+    return *reinterpret_cast<uint32_t *>(&h);
+  } else {
+    uint32_t v = t ^ 0x43084308u; // 128 + (n ^ 8) = 136 + value
+    __nv_bfloat162 h = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&v), __bfloat162bfloat162(__ushort_as_bfloat16(0x4308)));
+    return *reinterpret_cast<uint32_t *>(&h);
+  }
+}
+
+template <int WBITS> struct WoTraits {
+  static constexpr int kElemsPerLane = 128 / WBITS;       // elements in one 16-byte load
+  static constexpr int kStep = 4 * kElemsPerLane;         // k covered by one warp iteration
+  static constexpr int kXWords = kElemsPerLane / 2;       // 32-bit X words per lane and row
+};
+
+// NT = number of 8-row tiles of X handled at once (M <= 8 * NT).
+template <typename XT, int WBITS, int NT>
+__global__ void __launch_bounds__(kThreadsWo)
+wo_linear_kernel(const XT *__restrict__ X, const uint8_t *__restrict__ W, const void *__restrict__ scale, int sdt,
+                 XT *__restrict__ Y, int M, int N, int K, int block) {
+  using T = WoTraits<WBITS>;
+  __shared__ float red[kWarps][kRowsPerBlock][NT * 8 + 1];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * kRowsPerBlock;
+  const int row_a = min(n0 + g, N - 1), row_b = min(n0 + g + 8, N - 1);
+  const int64_t row_bytes = (int64_t)K * WBITS / 8;
+  const uint8_t *wa_ptr = W + (int64_t)row_a * row_bytes + t * 16;
+  const uint8_t *wb_ptr = W + (int64_t)row_b * row_bytes + t * 16;
+  const int n_iters = K / T::kStep;
+  const int nb = (WBITS == 4) ? K / block : 0;
+
+  float acc[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+
+#pragma unroll 2
+  for (int it = warp; it < n_iters; it += kWarps) {
+    const int kb = it * T::kStep;
+    const uint4 wa = __ldcs(reinterpret_cast<const uint4 *>(wa_ptr + (int64_t)it * 64));
+    const uint4 wb = __ldcs(reinterpret_cast<const uint4 *>(wb_ptr + (int64_t)it * 64));
+    const uint32_t wav[4] = {wa.x, wa.y, wa.z, wa.w};
+    const uint32_t wbv[4] = {wb.x, wb.y, wb.z, wb.w};
+
+    if constexpr (WBITS == 8) {
+      // A fragments of the four MMAs this lane's 16 bytes feed
+      uint32_t a[4][4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        uint32_t ua = wav[j] ^ 0x80808080u, ub = wbv[j] ^ 0x80808080u;
+        a[j][0] = int8_pair<XT, 0>(ua);
+        a[j][1] = int8_pair<XT, 0>(ub);
+        a[j][2] = int8_pair<XT, 2>(ua);
+        a[j][3] = int8_pair<XT, 2>(ub);
+      }
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++) {
+        const int m = nt * 8 + g;
+        uint32_t xw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (m < M) {
+          const uint4 *xp = reinterpret_cast<const uint4 *>(X + (int64_t)m * K + kb + t * 16);
+          uint4 x0 = __ldg(xp), x1 = __ldg(xp + 1);
+          xw[0] = x0.x; xw[1] = x0.y; xw[2] = x0.z; xw[3] = x0.w;
+          xw[4] = x1.x; xw[5] = x1.y; xw[6] = x1.z; xw[7] = x1.w;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) mma16816<XT>(acc[nt], a[j][0], a[j][1], a[j][2], a[j][3], xw[2 * j], xw[2 * j + 1]);
+      }
+    } else {
+      // int4: this iteration lies inside one scale block (block % 128 == 0)
+      const float sa = load_scale(scale, sdt, (int64_t)row_a * nb + kb / block);
+      const float sb = load_scale(scale, sdt, (int64_t)row_b * nb + kb / block);
+      float part[NT][4];
+#pragma unroll
+      for (int i = 0; i < NT; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) part[i][j] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; j++) { // word j = elements 8j .. 8j+7 of this lane's 32
+        uint32_t a_lo[4], a_hi[4];
+        a_lo[0] = int4_pair<XT, 0>(wav[j]); a_lo[1] = int4_pair<XT, 0>(wbv[j]);
+        a_lo[2] = int4_pair<XT, 1>(wav[j]); a_lo[3] = int4_pair<XT, 1>(wbv[j]);
+        a_hi[0] = int4_pair<XT, 2>(wav[j]); a_hi[1] = int4_pair<XT, 2>(wbv[j]);
+        a_hi[2] = int4_pair<XT, 3>(wav[j]); a_hi[3] = int4_pair<XT, 3>(wbv[j]);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          const int m = nt * 8 + g;
+          uint4 xv = make_uint4(0, 0, 0, 0);
+          if (m < M) xv = __ldg(reinterpret_cast<const uint4 *>(X + (int64_t)m * K + kb + t * 32 + j * 8));
+          // x pairs (0,4) (1,5) (2,6) (3,7) to line up with the weight pairs
+          uint32_t p04 = __byte_perm(xv.x, xv.z, 0x5410), p15 = __byte_perm(xv.x, xv.z, 0x7632);
+          uint32_t p26 = __byte_perm(xv.y, xv.w, 0x5410), p37 = __byte_perm(xv.y, xv.w, 0x7632);
+          mma16816<XT>(part[nt], a_lo[0], a_lo[1], a_lo[2], a_lo[3], p04, p15);
+          mma16816<XT>(part[nt], a_hi[0], a_hi[1], a_hi[2], a_hi[3], p26, p37);
+        }
+      }
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++) {
+        acc[nt][0] = fmaf(part[nt][0], sa, acc[nt][0]);
+        acc[nt][1] = fmaf(part[nt][1], sa, acc[nt][1]);
+        acc[nt][2] = fmaf(part[nt][2], sb, acc[nt][2]);
+        acc[nt][3] = fmaf(part[nt][3], sb, acc[nt][3]);
+      }
+    }
+  }
+
+  // cross-warp reduction: red[warp][row][m]
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++) {
+    red[warp][g][nt * 8 + 2 * t] = acc[nt][0];
+    red[warp][g][nt * 8 + 2 * t + 1] = acc[nt][1];
+    red[warp][g + 8][nt * 8 + 2 * t] = acc[nt][2];
+    red[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < kRowsPerBlock * NT * 8; idx += kThreadsWo) {
+    const int r = idx % kRowsPerBlock, m = idx / kRowsPerBlock;
+    const int n = n0 + r;
+    if (m >= M || n >= N) continue;
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; w++) s += red[w][r][m];
+    if constexpr (WBITS == 8) s *= load_scale(scale, sdt, n);
+    Y[(int64_t)m * N + n] = FloatIO<XT>::from_f32(s);
+  }
+}
+
+template <typename XT, int WBITS>
+int launch_wo_t(const void *X, const void *W, const void *scale, int sdt, void *Y, int M, int N, int K, int block,
+                cudaStream_t st) {
+  const unsigned grid = (unsigned)((N + kRowsPerBlock - 1) / kRowsPerBlock);
+  // batches larger than 32 rows are walked in slices; the weights of the later slices come from L2
+  for (int m0 = 0; m0 < M; m0 += 32) {
+    const int mc = min(32, M - m0);
+    const XT *xp = static_cast<const XT *>(X) + (int64_t)m0 * K;
+    XT *yp = static_cast<XT *>(Y) + (int64_t)m0 * N;
+    const uint8_t *wp = static_cast<const uint8_t *>(W);
+    if (mc <= 8) wo_linear_kernel<XT, WBITS, 1><<<grid, kThreadsWo, 0, st>>>(xp, wp, scale, sdt, yp, mc, N, K, block);
+    else if (mc <= 16) wo_linear_kernel<XT, WBITS, 2><<<grid, kThreadsWo, 0, st>>>(xp, wp, scale, sdt, yp, mc, N, K, block);
+    else wo_linear_kernel<XT, WBITS, 4><<<grid, kThreadsWo, 0, st>>>(xp, wp, scale, sdt, yp, mc, N, K, block);
+    count_launches(1);
+  }
+  QL_CUDA_TRY(cudaGetLastError());
+  return QL_OK;
+}
+
+} // namespace
+
+int launch_wo_linear(int wbits, int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M,
+                     int N, int K, int block, cudaStream_t st) {
+  if (M == 0 || N == 0) return QL_OK;
+  if (wbits == 8) {
+    if (xdt == QL_F16) return launch_wo_t<__half, 8>(X, W, scale, sdt, Y, M, N, K, block, st);
+    return launch_wo_t<__nv_bfloat16, 8>(X, W, scale, sdt, Y, M, N, K, block, st);
+  }
+  if (xdt == QL_F16) return launch_wo_t<__half, 4>(X, W, scale, sdt, Y, M, N, K, block, st);
+  return launch_wo_t<__nv_bfloat16, 4>(X, W, scale, sdt, Y, M, N, K, block, st);
+}
+
+} // namespace ql

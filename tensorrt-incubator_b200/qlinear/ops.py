@@ -1,0 +1,145 @@
+"""Operator layer: quantize / dequantize with the signatures and argument contract of Tripy's
+tp.quantize / tp.dequantize (tripy/nvtripy/frontend/ops/quantize.py:39-119,
+dequantize.py:39-114, argument checks frontend/ops/utils.py:187-251), running the sm_100a
+kernels through the C ABI.  Tensors are torch tensors in GPU memory; int4 results are
+Int4Tensor.  Scales are constants, as in the reference: a Python number, a numpy array or a
+torch tensor (host or device); they are rounded to the floating-point type of the data."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from . import dtypes as dt
+from .tensor import Int4Tensor, current_stream, dtype_of, empty_quantized, ql_view, require_cuda
+
+
+class QuantizeError(ValueError):
+    """Argument-contract violation, worded as Tripy words it."""
+
+
+def _as_scale(scale, float_dtype: dt.dtype) -> torch.Tensor:
+    """The scale as a tensor of the data's floating-point type (still wherever it was)."""
+    if isinstance(scale, torch.Tensor):
+        if scale.dtype != float_dtype.torch:
+            raise QuantizeError(
+                f"Scale dtype does not match expected dtype. scale should have dtype={float_dtype}, got {scale.dtype}")
+        return scale
+    return torch.as_tensor(scale, dtype=torch.float64).to(float_dtype.torch)
+
+
+def _float_dtype_or_none(t):
+    try:
+        return dtype_of(t)
+    except TypeError:
+        return None
+
+
+def check_qdq_args(input, scale, dtype, dim, is_quantize: bool) -> None:
+    """The checks of Tripy's check_qdq_args, same order, same wording."""
+    valid_in = dt.QUANTIZABLE_DTYPES if is_quantize else dt.QUANTIZED_DTYPES
+    valid_out = dt.QUANTIZED_DTYPES if is_quantize else dt.QUANTIZABLE_DTYPES
+    op = "quantize op" if is_quantize else "dequantize op"
+    try:
+        in_dtype = dtype_of(input)
+    except TypeError:
+        in_dtype = None
+    if in_dtype not in valid_in:
+        raise QuantizeError(f"Input does not have a valid dtype in {op}. input.dtype must be one of {valid_in}, got {in_dtype}")
+    if dtype not in valid_out:
+        raise QuantizeError(f"Unsupported data type in {op}. Supported data types are: {valid_out}. Got dtype={dtype}")
+    quantized = dtype if is_quantize else in_dtype
+    rank_in = len(input.shape)
+    rank_s = scale.dim()
+    if dim is not None:
+        if rank_s != 1:
+            raise QuantizeError(f"If dim is given, scale must be a 1-D tensor in per-channel {op}. scale has rank={rank_s}.")
+    elif rank_s == 2:
+        if rank_in != 2:
+            raise QuantizeError(f"Input must be a 2-D tensor in block-wise {op}. input has rank={rank_in}.")
+        if quantized is not dt.int4:
+            raise QuantizeError(f"Unsupported data type in block-wise {op}. Only `int4` is supported, got {quantized}")
+    elif rank_s != 0:
+        raise QuantizeError(f"Scale must be a scalar tensor in per-tensor {op}. scale has rank={rank_s}.")
+
+
+def quantize(input: torch.Tensor, scale, dtype: dt.dtype, dim=None, *, fp8_mode: str = "direct", out=None):
+    """output = clamp(round_half_even(input / scale)) as `dtype` (int8, int4 or float8).
+
+    `dim` given: per-channel, scale is 1-D of input.shape[dim].  2-D scale: block-wise (int4).
+    Otherwise scale is a scalar: per-tensor."""
+    float_dtype = _float_dtype_or_none(input)
+    if float_dtype not in dt.QUANTIZABLE_DTYPES:
+        check_qdq_args(input, torch.zeros(()), dtype, dim, True)
+    s = _as_scale(scale, float_dtype)
+    check_qdq_args(input, s, dtype, dim, True)
+    require_cuda(input, "input")
+    s = s.to(input.device).contiguous()
+    x = input.contiguous()
+    q = out if out is not None else empty_quantized(x.shape, dtype, x.device)
+    attrs = _lib.make_attrs(dim, fp8_mode)
+    tx, ts, tq = ql_view(x), ql_view(s), ql_view(q)
+    _lib.check(_lib.lib().ql_quantize(tx, ts, tq, attrs, current_stream(x.device)))
+    return q
+
+
+def dequantize(input, scale, dtype: dt.dtype, dim=None, *, out=None) -> torch.Tensor:
+    """output = input * scale as `dtype` (float32, float16 or bfloat16)."""
+    if dtype not in dt.QUANTIZABLE_DTYPES:
+        check_qdq_args(input, torch.zeros(()), dtype, dim, False)
+    s = _as_scale(scale, dtype)
+    check_qdq_args(input, s, dtype, dim, False)
+    require_cuda(input, "input")
+    s = s.to(input.device).contiguous()
+    q = input if isinstance(input, Int4Tensor) else input.contiguous()
+    y = out if out is not None else torch.empty(tuple(q.shape), dtype=dtype.torch, device=q.device)
+    attrs = _lib.make_attrs(dim)
+    tq, ts, ty = ql_view(q), ql_view(s), ql_view(y)
+    _lib.check(_lib.lib().ql_dequantize(tq, ts, ty, attrs, current_stream(q.device)))
+    return y
+
+
+def quantize_dequantize(input: torch.Tensor, scale, dtype: dt.dtype, dim=None, *, fp8_mode: str = "direct"):
+    """(quantize(input), dequantize(quantize(input))) in one pass over the input."""
+    float_dtype = _float_dtype_or_none(input)
+    if float_dtype not in dt.QUANTIZABLE_DTYPES:
+        check_qdq_args(input, torch.zeros(()), dtype, dim, True)
+    s = _as_scale(scale, float_dtype)
+    check_qdq_args(input, s, dtype, dim, True)
+    require_cuda(input, "input")
+    s = s.to(input.device).contiguous()
+    x = input.contiguous()
+    q = empty_quantized(x.shape, dtype, x.device)
+    y = torch.empty_like(x)
+    attrs = _lib.make_attrs(dim, fp8_mode)
+    tx, ts, tq, ty = ql_view(x), ql_view(s), ql_view(q), ql_view(y)
+    _lib.check(_lib.lib().ql_quantize_dequantize(tx, ts, tq, ty, attrs, current_stream(x.device)))
+    return q, y
+
+
+def amax_scale(input: torch.Tensor, dtype: dt.dtype, dim=None, block=None, *, scale_dtype: dt.dtype | None = None,
+               out=None) -> torch.Tensor:
+    """scale = max|input| / maxbound(dtype) per tensor, per channel along `dim`, or per block.
+
+    `block` = (block_dim, block_size) for 2-D inputs.  The reference has no such operator (its
+    scales are constants); the formula is the one its user guide gives for calibration."""
+    require_cuda(input, "input")
+    x = input.contiguous()
+    sd = scale_dtype or dtype_of(x)
+    if block is not None:
+        bdim, bsize = block
+        if x.dim() != 2:
+            raise QuantizeError("Input must be a 2-D tensor in block-wise quantize op.")
+        shape = list(x.shape)
+        if shape[bdim] % bsize:
+            raise QuantizeError(f"block size {bsize} does not divide dimension {bdim} of {tuple(x.shape)}")
+        shape[bdim] //= bsize
+        dim = None
+    elif dim is not None:
+        shape = [x.shape[dim]]
+    else:
+        shape = []
+    s = out if out is not None else torch.empty(shape, dtype=sd.torch, device=x.device)
+    attrs = _lib.make_attrs(dim)
+    tx, ts = ql_view(x), ql_view(s)
+    _lib.check(_lib.lib().ql_amax_scale(tx, ts, attrs, dt.MAXBOUND[dtype], current_stream(x.device)))
+    return s

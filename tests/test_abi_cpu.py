@@ -1,0 +1,109 @@
+"""The C-ABI shared library on a machine without a GPU: it loads, exports every symbol the
+headers declare, validates arguments with the reference verifier's wording, and refuses to
+compute without a device (there is no CPU path in the product)."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from conftest import ROOT
+
+import qlinear
+from qlinear import _lib
+
+
+def _declared_symbols():
+    names = []
+    for fn in sorted(os.listdir(os.path.join(ROOT, "include"))):
+        text = open(os.path.join(ROOT, "include", fn)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        text = "\n".join(l for l in text.splitlines() if not l.lstrip().startswith("#"))
+        names += re.findall(r"(?:QL_API|MTRT_CAPI_EXPORTED)\s+[\w\s\*]*?\b(\w+)\s*\(", text)
+    return sorted(set(names))
+
+
+def test_library_exports_every_declared_symbol():
+    L = ctypes.CDLL(_lib.LIB_PATH)
+    names = _declared_symbols()
+    assert len(names) >= 12
+    for n in names:
+        assert hasattr(L, n), n
+    assert set(_lib.SIGNATURES) <= set(names)
+    assert _lib.lib().ql_version() >= 100
+
+
+def _t(dtype, shape, ptr=0x1000):
+    return _lib.make_tensor(ptr, dtype, shape)
+
+
+def _err(rc):
+    assert rc != 0
+    return _lib.lib().ql_last_error().decode()
+
+
+@pytest.mark.parametrize("fn", ["ql_quantize", "ql_dequantize"])
+def test_verifier_messages(fn):
+    """Wording of tensorrt/lib/TensorRT/IR/Verification.cpp:1182-1265 / 1296-1380."""
+    L = _lib.lib()
+    f = getattr(L, fn)
+    is_q = fn == "ql_quantize"
+
+    def call(data_shape, scale_shape, qdtype=_lib.I8, axis=None):
+        fl, q, s = _t(_lib.F32, data_shape), _t(qdtype, data_shape), _t(_lib.F32, scale_shape)
+        a = _lib.make_attrs(axis)
+        return f(fl, s, q, a, None) if is_q else f(q, s, fl, a, None)
+
+    assert "axis value must be provided" in _err(call([4, 4], [4]))
+    assert "expected axis to be non-negative and less than 2" in _err(call([4, 4], [4], axis=2))
+    assert "expected the scales tensor dimension to match" in _err(call([4, 4], [3], axis=0))
+    assert "axis value shouldn't be provided" in _err(call([4, 4], [], axis=0))
+    assert "Scale value must be scalar for per-tensor" in _err(call([2, 4, 4], [2, 2]))
+    assert "Block quantization is supported only for int4, fp4 or fp8" in _err(call([4, 4], [2, 4]))
+    assert "Axis is not valid in this case" in _err(call([4, 4], [2, 4], _lib.I4, axis=0))
+    assert "blocking dimension should be either last or second last" in _err(call([4, 4, 4], [2, 4, 4], _lib.I4))
+    assert "all input and scale dimensions match except a single blocking dimension" in _err(call([4, 4], [2, 2], _lib.I4))
+
+
+def test_type_rules():
+    L = _lib.lib()
+    a = _lib.make_attrs()
+    rc = L.ql_quantize(_t(_lib.I8, [4]), _t(_lib.F32, []), _t(_lib.I8, [4]), a, None)
+    assert "valid conversions are" in _err(rc)
+    rc = L.ql_dequantize(_t(_lib.F32, [4]), _t(_lib.F32, []), _t(_lib.F32, [4]), a, None)
+    assert "valid conversions are" in _err(rc)
+    rc = L.ql_quantize(_t(_lib.F32, [4]), _t(_lib.F32, []), _t(_lib.I8, [5]), a, None)
+    assert "shapes differ" in _err(rc)
+    rc = L.ql_quantize(_t(_lib.F32, [4]), _t(_lib.I8, []), _t(_lib.I8, [4]), a, None)
+    assert "scale must be f32, f16 or bf16" in _err(rc)
+    rc = L.ql_quantize(None, _t(_lib.F32, []), _t(_lib.I8, [4]), a, None)
+    assert "is null" in _err(rc)
+
+
+def test_linear_argument_rules():
+    L = _lib.lib()
+    x, w, y = _t(_lib.BF16, [4, 128]), _t(_lib.I8, [32, 128]), _t(_lib.BF16, [4, 32])
+    assert "expected the scales tensor dimension to match" in _err(L.ql_linear_w8a16(x, w, _t(_lib.F32, [31]), y, None))
+    assert "x and y must both be f16 or both be bf16" in _err(L.ql_linear_w8a16(_t(_lib.F32, [4, 128]), w, _t(_lib.F32, [32]), y, None))
+    assert "y must be [M,N]" in _err(L.ql_linear_w8a16(x, w, _t(_lib.F32, [32]), _t(_lib.BF16, [4, 33]), None))
+    w4 = _t(_lib.I4, [32, 128])
+    assert "single blocking dimension" in _err(L.ql_linear_w4a16(x, w4, _t(_lib.F32, [32, 3]), y, None))
+    assert "multiples of 128" in _err(L.ql_linear_w4a16(x, w4, _t(_lib.F32, [32, 2]), y, None))
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-device behaviour")
+def test_no_cpu_fallback():
+    """Without a GPU the product refuses to compute instead of falling back."""
+    x = torch.ones(4)
+    with pytest.raises(_lib.QlError) as e:
+        qlinear.quantize(x, 1.0, qlinear.int8)
+    assert e.value.status == _lib.ERR_NO_DEVICE
+    # and the raw entry point reports a CUDA failure rather than computing on the host
+    buf = (ctypes.c_float * 64)()
+    out = (ctypes.c_int8 * 64)()
+    sc = (ctypes.c_float * 1)(1.0)
+    p = lambda b: ctypes.cast(b, ctypes.c_void_p).value
+    rc = _lib.lib().ql_quantize(_t(_lib.F32, [64], p(buf)), _t(_lib.F32, [], p(sc)), _t(_lib.I8, [64], p(out)), _lib.make_attrs(), None)
+    assert rc in (_lib.ERR_NO_DEVICE, _lib.ERR_CUDA)
+    assert bytes(out) == bytes(64)
