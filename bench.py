@@ -43,51 +43,60 @@ def measured_peaks():
 # clocks sampled during the timed region
 # ----------------------------------------------------------------------------------------------
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons of one GPU, polled through NVML every few milliseconds from a
+    thread while the timed region runs (reading settings only; nothing is changed)."""
 
-    def __init__(self, index: int):
-        self.index = index
-        self.samples = []
-        self.proc = None
+    def __init__(self, index: int, period_s: float = 0.004):
+        self.index, self.period = index, period_s
+        self.mhz, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self.thread = None
+        self.error = None
+
+    def _run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            uuid = None
+            try:
+                import torch
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(self.index).uuid)
+            except Exception:
+                pass
+            h = None
+            if uuid:
+                try:
+                    h = nv.nvmlDeviceGetHandleByUUID(uuid.encode() if isinstance(uuid, str) else uuid)
+                except Exception:
+                    h = None
+            if h is None:
+                h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            names = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown, "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                     "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown, "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+            while not self._stop.is_set():
+                self.mhz.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                for n, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(n)
+                time.sleep(self.period)
+        except Exception as e:  # NVML missing: report it, never fail the bench
+            self.error = repr(e)
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) >= 6:
-                self.samples.append(parts)
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        mhz, mx, reasons = [], None, set()
-        for s in self.samples:
-            try:
-                mhz.append(float(s[0]))
-                mx = float(s[1])
-            except ValueError:
-                continue
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        mhz.sort()
-        med = mhz[len(mhz) // 2] if mhz else None
-        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(mhz)}
+        self._stop.set()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        m = sorted(self.mhz)
+        out = {"sm_mhz": m[len(m) // 2] if m else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(m)}
+        if self.error:
+            out["error"] = self.error
+        return out
 
 
 # ----------------------------------------------------------------------------------------------
@@ -248,8 +257,11 @@ def cpu_reference(workload: str, budget_s: float = 12.0):
         t0 = time.perf_counter()
         orc.linear_w8(x, orc.BF16, wq, s, orc.F16, orc.BF16, acc64=False)
         t1 = time.perf_counter() - t0
-        # grow the slice of output channels so that the timed sample takes about `budget_s`
-        n_big = int(min(N, max(n_s, n_s * budget_s / max(t1, 1e-4))))
+        # grow the slice of output channels, then the rows, so that the sample takes about `budget_s`
+        grow = budget_s / max(t1, 1e-4)
+        n_big = int(min(N, max(n_s, n_s * grow)))
+        m_s = int(min(2048, max(m_s, m_s * grow * n_s / n_big)))
+        x = orc.from_f32(rng.standard_normal((m_s, K)).astype(np.float32), orc.BF16)
         wq = rng.integers(-127, 128, size=(n_big, K), dtype=np.int8)
         s = (rng.random(n_big).astype(np.float32) * 1e-3 + 1e-4).astype(np.float16)
         t0 = time.perf_counter()
@@ -303,7 +315,7 @@ def run_reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])

@@ -120,6 +120,12 @@ QL_API int ql_gemm_i8(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor 
 QL_API int ql_gemm_16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *sw, ql_tensor *y,
                       void *stream);
 
+/* The tensor-core kernels bound every on-device wait (mbarrier, tensor-memory hand-over) by a
+ * cycle limit; a kernel that runs out records a code and returns early instead of hanging.  This
+ * call synchronises the device, returns QL_ERR_DEVICE_TIMEOUT if a code was recorded since the
+ * last call (and clears it), and stores the code in *code when code is not null. */
+QL_API int ql_gemm_status(int32_t *code);
+
 #ifdef __cplusplus
 }
 #endif

@@ -42,6 +42,18 @@ int sm_count() {
   return cached[dev];
 }
 
+int *device_status_word() {
+  // one word per device, allocated on first use and kept for the life of the process
+  static int *words[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!words[dev]) {
+    if (cudaMalloc(&words[dev], sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(words[dev], 0, sizeof(int));
+  }
+  return words[dev];
+}
+
 // kernels (ql_qdq.cu)
 int launch_quantize(const ql_tensor *in, const ql_tensor *scale, ql_tensor *q, ql_tensor *y, const QdqPlan &p,
                     int fp8_mode, cudaStream_t st);

@@ -8,7 +8,8 @@
 // one weight row are consumed as they lie in memory, and for int4 the value pairs that one mask
 // extracts (elements e and e+4 of a word) are matched by permuting the X registers.
 //
-// One block owns 16 output channels; its 8 warps split K and reduce through shared memory.
+// One block owns 16 output channels.  A producer warp streams their weights into a shared-memory
+// ring with bulk asynchronous copies; 8 consumer warps split K and reduce through shared memory.
 // Reference composition this implements: tripy/nvtripy/frontend/module/linear.py:140-151
 // (quantize -> dequantize -> x @ transpose(w)) with the dequantize folded into the product.
 #include <cuda/std/type_traits>
@@ -70,115 +71,198 @@ __device__ __forceinline__ uint32_t int4_pair(uint32_t w) {
 }
 
 template <int WBITS> struct WoTraits {
-  static constexpr int kElemsPerLane = 128 / WBITS;       // elements in one 16-byte load
-  static constexpr int kStep = 4 * kElemsPerLane;         // k covered by one warp iteration
-  static constexpr int kXWords = kElemsPerLane / 2;       // 32-bit X words per lane and row
+  static constexpr int kElemsPerLane = 128 / WBITS;       // elements in one 16-byte word
+  static constexpr int kStep = 4 * kElemsPerLane;         // k covered by one warp iteration (64 bytes of a row)
 };
 
+// Shared-memory ring of weight slabs.  A stage holds kChunkBytes of each of the 16 rows; rows are
+// padded by 64 bytes so that the two rows one quarter-warp reads fall into different banks.
+constexpr int kStagesWo = 4;
+constexpr int kChunkBytes = 1024;
+constexpr int kRowPitch = kChunkBytes + 64;
+constexpr int kStageBytesWo = kRowsPerBlock * kRowPitch;
+constexpr int kItersPerStage = kChunkBytes / 64;
+constexpr long long kWoWaitLimit = 1ll << 31;
+
+__device__ __forceinline__ uint32_t wo_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool wo_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+               : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
+// bounded wait: false once the limit has run out (the caller records it and stops consuming)
+__device__ __forceinline__ bool wo_wait(uint32_t bar, uint32_t parity) {
+  if (wo_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!wo_try_wait(bar, parity))
+    if (clock64() - t0 > kWoWaitLimit) return false;
+  return true;
+}
+
 // NT = number of 8-row tiles of X handled at once (M <= 8 * NT).
+// Warps 0..7 consume; warp 8 streams the block's 16 weight rows from HBM into the ring with bulk
+// asynchronous copies (one per row and stage), so HBM latency is hidden by the copy engine's
+// queue instead of by registers.
 template <typename XT, int WBITS, int NT>
-__global__ void __launch_bounds__(kThreadsWo)
+__global__ void __launch_bounds__(kThreadsWo + 32)
 wo_linear_kernel(const XT *__restrict__ X, const uint8_t *__restrict__ W, const void *__restrict__ scale, int sdt,
-                 XT *__restrict__ Y, int M, int N, int K, int block) {
+                 XT *__restrict__ Y, int M, int N, int K, int block, int *status) {
   using T = WoTraits<WBITS>;
-  __shared__ float red[kWarps][kRowsPerBlock][NT * 8 + 1];
+  extern __shared__ __align__(128) uint8_t wo_smem[];
+  uint8_t *ring = wo_smem;
+  float(*red)[kRowsPerBlock][NT * 8 + 1] = reinterpret_cast<float(*)[kRowsPerBlock][NT * 8 + 1]>(wo_smem + kStagesWo * kStageBytesWo);
+  __shared__ __align__(8) uint64_t bars[2 * kStagesWo];
+  __shared__ int gave_up;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * kRowsPerBlock;
-  const int row_a = min(n0 + g, N - 1), row_b = min(n0 + g + 8, N - 1);
   const int64_t row_bytes = (int64_t)K * WBITS / 8;
-  const uint8_t *wa_ptr = W + (int64_t)row_a * row_bytes + t * 16;
-  const uint8_t *wb_ptr = W + (int64_t)row_b * row_bytes + t * 16;
-  const int n_iters = K / T::kStep;
-  const int nb = (WBITS == 4) ? K / block : 0;
+  const int n_iters = K / T::kStep;                                   // warp iterations over the whole K
+  const int n_stages = (int)((row_bytes + kChunkBytes - 1) / kChunkBytes);
+  const uint32_t bar0 = wo_smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kStagesWo + s); };
 
-  float acc[NT][4];
-#pragma unroll
-  for (int i = 0; i < NT; i++)
-#pragma unroll
-    for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
-
-#pragma unroll 2
-  for (int it = warp; it < n_iters; it += kWarps) {
-    const int kb = it * T::kStep;
-    const uint4 wa = __ldcs(reinterpret_cast<const uint4 *>(wa_ptr + (int64_t)it * 64));
-    const uint4 wb = __ldcs(reinterpret_cast<const uint4 *>(wb_ptr + (int64_t)it * 64));
-    const uint32_t wav[4] = {wa.x, wa.y, wa.z, wa.w};
-    const uint32_t wbv[4] = {wb.x, wb.y, wb.z, wb.w};
-
-    if constexpr (WBITS == 8) {
-      // A fragments of the four MMAs this lane's 16 bytes feed
-      uint32_t a[4][4];
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        uint32_t ua = wav[j] ^ 0x80808080u, ub = wbv[j] ^ 0x80808080u;
-        a[j][0] = int8_pair<XT, 0>(ua);
-        a[j][1] = int8_pair<XT, 0>(ub);
-        a[j][2] = int8_pair<XT, 2>(ua);
-        a[j][3] = int8_pair<XT, 2>(ub);
-      }
-#pragma unroll
-      for (int nt = 0; nt < NT; nt++) {
-        const int m = nt * 8 + g;
-        uint32_t xw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (m < M) {
-          const uint4 *xp = reinterpret_cast<const uint4 *>(X + (int64_t)m * K + kb + t * 16);
-          uint4 x0 = __ldg(xp), x1 = __ldg(xp + 1);
-          xw[0] = x0.x; xw[1] = x0.y; xw[2] = x0.z; xw[3] = x0.w;
-          xw[4] = x1.x; xw[5] = x1.y; xw[6] = x1.z; xw[7] = x1.w;
-        }
-#pragma unroll
-        for (int j = 0; j < 4; j++) mma16816<XT>(acc[nt], a[j][0], a[j][1], a[j][2], a[j][3], xw[2 * j], xw[2 * j + 1]);
-      }
-    } else {
-      // int4: this iteration lies inside one scale block (block % 128 == 0)
-      const float sa = load_scale(scale, sdt, (int64_t)row_a * nb + kb / block);
-      const float sb = load_scale(scale, sdt, (int64_t)row_b * nb + kb / block);
-      float part[NT][4];
-#pragma unroll
-      for (int i = 0; i < NT; i++)
-#pragma unroll
-        for (int j = 0; j < 4; j++) part[i][j] = 0.f;
-#pragma unroll
-      for (int j = 0; j < 4; j++) { // word j = elements 8j .. 8j+7 of this lane's 32
-        uint32_t a_lo[4], a_hi[4];
-        a_lo[0] = int4_pair<XT, 0>(wav[j]); a_lo[1] = int4_pair<XT, 0>(wbv[j]);
-        a_lo[2] = int4_pair<XT, 1>(wav[j]); a_lo[3] = int4_pair<XT, 1>(wbv[j]);
-        a_hi[0] = int4_pair<XT, 2>(wav[j]); a_hi[1] = int4_pair<XT, 2>(wbv[j]);
-        a_hi[2] = int4_pair<XT, 3>(wav[j]); a_hi[3] = int4_pair<XT, 3>(wbv[j]);
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-          const int m = nt * 8 + g;
-          uint4 xv = make_uint4(0, 0, 0, 0);
-          if (m < M) xv = __ldg(reinterpret_cast<const uint4 *>(X + (int64_t)m * K + kb + t * 32 + j * 8));
-          // x pairs (0,4) (1,5) (2,6) (3,7) to line up with the weight pairs
-          uint32_t p04 = __byte_perm(xv.x, xv.z, 0x5410), p15 = __byte_perm(xv.x, xv.z, 0x7632);
-          uint32_t p26 = __byte_perm(xv.y, xv.w, 0x5410), p37 = __byte_perm(xv.y, xv.w, 0x7632);
-          mma16816<XT>(part[nt], a_lo[0], a_lo[1], a_lo[2], a_lo[3], p04, p15);
-          mma16816<XT>(part[nt], a_hi[0], a_hi[1], a_hi[2], a_hi[3], p26, p37);
-        }
-      }
-#pragma unroll
-      for (int nt = 0; nt < NT; nt++) {
-        acc[nt][0] = fmaf(part[nt][0], sa, acc[nt][0]);
-        acc[nt][1] = fmaf(part[nt][1], sa, acc[nt][1]);
-        acc[nt][2] = fmaf(part[nt][2], sb, acc[nt][2]);
-        acc[nt][3] = fmaf(part[nt][3], sb, acc[nt][3]);
-      }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStagesWo; s++) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full_bar(s)), "r"(1) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty_bar(s)), "r"(kWarps) : "memory");
     }
-  }
-
-  // cross-warp reduction: red[warp][row][m]
-#pragma unroll
-  for (int nt = 0; nt < NT; nt++) {
-    red[warp][g][nt * 8 + 2 * t] = acc[nt][0];
-    red[warp][g][nt * 8 + 2 * t + 1] = acc[nt][1];
-    red[warp][g + 8][nt * 8 + 2 * t] = acc[nt][2];
-    red[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
+    gave_up = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < kRowsPerBlock * NT * 8; idx += kThreadsWo) {
+
+  if (warp == kWarps) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      for (int st = 0; st < n_stages; st++) {
+        const int slot = st % kStagesWo;
+        if (st >= kStagesWo && !wo_wait(empty_bar(slot), ((st / kStagesWo) - 1) & 1)) {
+          atomicCAS(status, 0, 11);
+          break;
+        }
+        const int64_t off = (int64_t)st * kChunkBytes;
+        const uint32_t bytes = (uint32_t)((row_bytes - off) < kChunkBytes ? (row_bytes - off) : kChunkBytes);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_bar(slot)), "r"(bytes * kRowsPerBlock) : "memory");
+        for (int r = 0; r < kRowsPerBlock; r++) {
+          const int row = min(n0 + r, N - 1);
+          const uint8_t *src = W + (int64_t)row * row_bytes + off;
+          const uint32_t dst = wo_smem_u32(ring + slot * kStageBytesWo + r * kRowPitch);
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                       ::"r"(dst), "l"(src), "r"(bytes), "r"(full_bar(slot)) : "memory");
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- consumers
+    const int g = lane >> 2, t = lane & 3;
+    const int row_a = min(n0 + g, N - 1), row_b = min(n0 + g + 8, N - 1);
+    const int nb = (WBITS == 4) ? K / block : 0;
+    float acc[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+
+    bool ok = true;
+    for (int st = 0; st < n_stages && ok; st++) {
+      const int slot = st % kStagesWo;
+      if (!wo_wait(full_bar(slot), (st / kStagesWo) & 1)) {
+        if (lane == 0) { atomicCAS(status, 0, 12); gave_up = 1; }
+        ok = false;
+        break;
+      }
+      const uint8_t *stage = ring + slot * kStageBytesWo;
+#pragma unroll
+      for (int half = 0; half < kItersPerStage / kWarps; half++) {
+        const int it_in = warp + half * kWarps;            // iteration inside the stage
+        const int it = st * kItersPerStage + it_in;        // iteration over the whole K
+        if (it >= n_iters) break;
+        const int kb = it * T::kStep;
+        const uint4 wa = *reinterpret_cast<const uint4 *>(stage + g * kRowPitch + it_in * 64 + t * 16);
+        const uint4 wb = *reinterpret_cast<const uint4 *>(stage + (g + 8) * kRowPitch + it_in * 64 + t * 16);
+        const uint32_t wav[4] = {wa.x, wa.y, wa.z, wa.w};
+        const uint32_t wbv[4] = {wb.x, wb.y, wb.z, wb.w};
+
+        if constexpr (WBITS == 8) {
+          uint32_t a[4][4];
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            uint32_t ua = wav[j] ^ 0x80808080u, ub = wbv[j] ^ 0x80808080u;
+            a[j][0] = int8_pair<XT, 0>(ua);
+            a[j][1] = int8_pair<XT, 0>(ub);
+            a[j][2] = int8_pair<XT, 2>(ua);
+            a[j][3] = int8_pair<XT, 2>(ub);
+          }
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++) {
+            const int m = nt * 8 + g;
+            uint32_t xw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (m < M) {
+              const uint4 *xp = reinterpret_cast<const uint4 *>(X + (int64_t)m * K + kb + t * 16);
+              uint4 x0 = __ldg(xp), x1 = __ldg(xp + 1);
+              xw[0] = x0.x; xw[1] = x0.y; xw[2] = x0.z; xw[3] = x0.w;
+              xw[4] = x1.x; xw[5] = x1.y; xw[6] = x1.z; xw[7] = x1.w;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) mma16816<XT>(acc[nt], a[j][0], a[j][1], a[j][2], a[j][3], xw[2 * j], xw[2 * j + 1]);
+          }
+        } else {
+          // int4: one iteration (128 k) lies inside one scale block (block % 128 == 0)
+          const float sa = load_scale(scale, sdt, (int64_t)row_a * nb + kb / block);
+          const float sb = load_scale(scale, sdt, (int64_t)row_b * nb + kb / block);
+          float part[NT][4];
+#pragma unroll
+          for (int i = 0; i < NT; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) part[i][j] = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; j++) { // word j = elements 8j .. 8j+7 of this lane's 32
+            uint32_t a_lo[4], a_hi[4];
+            a_lo[0] = int4_pair<XT, 0>(wav[j]); a_lo[1] = int4_pair<XT, 0>(wbv[j]);
+            a_lo[2] = int4_pair<XT, 1>(wav[j]); a_lo[3] = int4_pair<XT, 1>(wbv[j]);
+            a_hi[0] = int4_pair<XT, 2>(wav[j]); a_hi[1] = int4_pair<XT, 2>(wbv[j]);
+            a_hi[2] = int4_pair<XT, 3>(wav[j]); a_hi[3] = int4_pair<XT, 3>(wbv[j]);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+              const int m = nt * 8 + g;
+              uint4 xv = make_uint4(0, 0, 0, 0);
+              if (m < M) xv = __ldg(reinterpret_cast<const uint4 *>(X + (int64_t)m * K + kb + t * 32 + j * 8));
+              // x pairs (0,4) (1,5) (2,6) (3,7) to line up with the weight pairs
+              uint32_t p04 = __byte_perm(xv.x, xv.z, 0x5410), p15 = __byte_perm(xv.x, xv.z, 0x7632);
+              uint32_t p26 = __byte_perm(xv.y, xv.w, 0x5410), p37 = __byte_perm(xv.y, xv.w, 0x7632);
+              mma16816<XT>(part[nt], a_lo[0], a_lo[1], a_lo[2], a_lo[3], p04, p15);
+              mma16816<XT>(part[nt], a_hi[0], a_hi[1], a_hi[2], a_hi[3], p26, p37);
+            }
+          }
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++) {
+            acc[nt][0] = fmaf(part[nt][0], sa, acc[nt][0]);
+            acc[nt][1] = fmaf(part[nt][1], sa, acc[nt][1]);
+            acc[nt][2] = fmaf(part[nt][2], sb, acc[nt][2]);
+            acc[nt][3] = fmaf(part[nt][3], sb, acc[nt][3]);
+          }
+        }
+      }
+      // this warp is done with the slot: let the producer refill it
+      __syncwarp();
+      if (lane == 0 && st + kStagesWo < n_stages) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_bar(slot)) : "memory");
+    }
+
+    // cross-warp reduction: red[warp][row][m]
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+      red[warp][g][nt * 8 + 2 * t] = acc[nt][0];
+      red[warp][g][nt * 8 + 2 * t + 1] = acc[nt][1];
+      red[warp][g + 8][nt * 8 + 2 * t] = acc[nt][2];
+      red[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
+    }
+  }
+  __syncthreads();
+  if (gave_up) return; // a copy never arrived: leave Y untouched, the status word says why
+  for (int idx = threadIdx.x; idx < kRowsPerBlock * NT * 8; idx += kThreadsWo + 32) {
     const int r = idx % kRowsPerBlock, m = idx / kRowsPerBlock;
     const int n = n0 + r;
     if (m >= M || n >= N) continue;
@@ -190,20 +274,42 @@ wo_linear_kernel(const XT *__restrict__ X, const uint8_t *__restrict__ W, const 
   }
 }
 
+template <int NT> constexpr int wo_dynamic_smem() { return kStagesWo * kStageBytesWo + kWarps * kRowsPerBlock * (NT * 8 + 1) * 4; }
+
+template <typename XT, int WBITS, int NT>
+int launch_wo_nt(const XT *xp, const uint8_t *wp, const void *scale, int sdt, XT *yp, int mc, int N, int K, int block,
+                 int *status, unsigned grid, cudaStream_t st) {
+  auto kern = wo_linear_kernel<XT, WBITS, NT>;
+  constexpr int smem = wo_dynamic_smem<NT>();
+  static bool configured[64] = {false};
+  int dev = 0;
+  QL_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    QL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured[dev] = true;
+  }
+  kern<<<grid, kThreadsWo + 32, smem, st>>>(xp, wp, scale, sdt, yp, mc, N, K, block, status);
+  count_launches(1);
+  return QL_OK;
+}
+
 template <typename XT, int WBITS>
 int launch_wo_t(const void *X, const void *W, const void *scale, int sdt, void *Y, int M, int N, int K, int block,
                 cudaStream_t st) {
   const unsigned grid = (unsigned)((N + kRowsPerBlock - 1) / kRowsPerBlock);
+  int *status = device_status_word();
+  if (!status) return set_error(QL_ERR_CUDA, "weight-only linear: could not allocate the device status word");
   // batches larger than 32 rows are walked in slices; the weights of the later slices come from L2
   for (int m0 = 0; m0 < M; m0 += 32) {
     const int mc = min(32, M - m0);
     const XT *xp = static_cast<const XT *>(X) + (int64_t)m0 * K;
     XT *yp = static_cast<XT *>(Y) + (int64_t)m0 * N;
     const uint8_t *wp = static_cast<const uint8_t *>(W);
-    if (mc <= 8) wo_linear_kernel<XT, WBITS, 1><<<grid, kThreadsWo, 0, st>>>(xp, wp, scale, sdt, yp, mc, N, K, block);
-    else if (mc <= 16) wo_linear_kernel<XT, WBITS, 2><<<grid, kThreadsWo, 0, st>>>(xp, wp, scale, sdt, yp, mc, N, K, block);
-    else wo_linear_kernel<XT, WBITS, 4><<<grid, kThreadsWo, 0, st>>>(xp, wp, scale, sdt, yp, mc, N, K, block);
-    count_launches(1);
+    int rc;
+    if (mc <= 8) rc = launch_wo_nt<XT, WBITS, 1>(xp, wp, scale, sdt, yp, mc, N, K, block, status, grid, st);
+    else if (mc <= 16) rc = launch_wo_nt<XT, WBITS, 2>(xp, wp, scale, sdt, yp, mc, N, K, block, status, grid, st);
+    else rc = launch_wo_nt<XT, WBITS, 4>(xp, wp, scale, sdt, yp, mc, N, K, block, status, grid, st);
+    if (rc != QL_OK) return rc;
   }
   QL_CUDA_TRY(cudaGetLastError());
   return QL_OK;

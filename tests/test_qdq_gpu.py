@@ -199,11 +199,11 @@ def test_amax_scales(in_dtype):
             s = ql.amax_scale(x, qd, **kw)
             am = orc.amax(to_np(x), code_of(x), mode, axis, sshape)
             want = orc.scale_from_amax(am, mb, code_of(x))
-            assert np.array_equal(to_np(s).view(np.uint8).reshape(-1), want.view(np.uint8).reshape(-1)), (kw, qd)
+            assert np.array_equal(to_np(s).reshape(-1).view(np.uint8), want.reshape(-1).view(np.uint8)), (kw, qd)
     x3 = randn((4, 6, 50), in_dtype, 18)
     s = ql.amax_scale(x3, ql.int8, dim=1)
     am = orc.amax(to_np(x3), code_of(x3), orc.PER_CHANNEL, 1)
-    assert np.array_equal(to_np(s).view(np.uint8), orc.scale_from_amax(am, 127.0, code_of(x3)).view(np.uint8))
+    assert np.array_equal(to_np(s).reshape(-1).view(np.uint8), orc.scale_from_amax(am, 127.0, code_of(x3)).reshape(-1).view(np.uint8))
 
 
 def test_config1_full_size_per_tensor_int8():
@@ -219,7 +219,7 @@ def test_config1_full_size_per_tensor_int8():
     # size-independent properties: idempotence of Q on its own output, and |x - y| <= scale / 2
     q2 = ql.quantize(y, s, ql.int8)
     assert torch.equal(q2, q)
-    assert float((x - y).abs().max()) <= float(s) * 0.5 * (1 + 1e-6)
+    assert float((x - y).abs().max()) <= float(s) * 0.5 * (1 + 1e-5)
 
 
 def test_config2_and_3_weight_quantization_full_size():
