@@ -28,6 +28,10 @@ sys.path.insert(0, os.path.join(ROOT, "tensorrt-incubator_b200"))
 
 L2_BYTES = 126 * 1024 * 1024
 
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of each workload's dominant
+# kernel, from the ncu captures summarised under profiles/ (None until a capture exists).
+TRAFFIC = {}
+
 
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -46,7 +50,7 @@ class ClockSampler:
     """SM clock and throttle reasons of one GPU, polled through NVML every few milliseconds from a
     thread while the timed region runs (reading settings only; nothing is changed)."""
 
-    def __init__(self, index: int, period_s: float = 0.004):
+    def __init__(self, index: int, period_s: float = 0.001):
         self.index, self.period = index, period_s
         self.mhz, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
@@ -88,6 +92,11 @@ class ClockSampler:
         self.thread = threading.Thread(target=self._run, daemon=True)
         self.thread.start()
 
+    def wait_ready(self, timeout_s: float = 5.0):
+        t0 = time.time()
+        while not self.mhz and self.error is None and time.time() - t0 < timeout_s:
+            time.sleep(0.002)
+
     def stop(self):
         self._stop.set()
         if self.thread is not None:
@@ -105,13 +114,13 @@ class ClockSampler:
 class Workload:
     """A workload owns its device buffers and knows its algorithmic work.
 
-    parts(): list of (name, fn, flops, bytes) -- the kernels of one step, each timed separately
-    so that the dominant one can be reported against its roofline."""
+    parts(): list of (name, fn, flops, bytes, bound) -- the kernels of one step, each timed
+    separately so that the dominant one can be reported against its roofline."""
 
-    name = ""
-    metric = ""
-    unit = ""
-    dtype = ""
+    name = metric = unit = dtype = ""
+    use_graphs = True    # replay captured CUDA graphs: device time without host launch gaps
+    scaling = "weak"
+    parallelism = "replicas only"
 
 
 class W8A16Linear(Workload):
@@ -126,7 +135,7 @@ class W8A16Linear(Workload):
     MS = (1, 16, 128, 2048)
     REPLICAS = 6  # 6 x 45 MB of weights cycled per launch: every launch finds its weights cold in L2
 
-    def __init__(self, torch, ql, device, seed=1002):
+    def __init__(self, torch, ql, device, dist=None, seed=1002):
         self.torch, self.ql, self.device = torch, ql, device
         g = torch.Generator(device="cpu").manual_seed(seed)
         w = (torch.randn((self.N, self.K), generator=g, dtype=torch.float32) * 0.02).to(torch.float16).to(device)
@@ -152,7 +161,7 @@ class W8A16Linear(Workload):
         self.ql.linear_w8a16(self.x[m], w, self.scale, out=self.y[m])
 
     def parts(self):
-        return [(f"M={m}", (lambda m=m: self.run_part(m)), self.flops(m), self.bytes(m)) for m in self.MS]
+        return [(f"M={m}", (lambda m=m: self.run_part(m)), self.flops(m), self.bytes(m), "tensor" if m >= 512 else "hbm") for m in self.MS]
 
     def e2e_step(self):
         for m in self.MS:
@@ -161,18 +170,61 @@ class W8A16Linear(Workload):
             self.y_host[m].copy_(self.y[m], non_blocking=True)
 
     def e2e_bytes(self):
-        h2d = sum(m * self.K * 2 for m in self.MS)
-        d2h = sum(m * self.N * 2 for m in self.MS)
-        return h2d, d2h
+        return sum(m * self.K * 2 for m in self.MS), sum(m * self.N * 2 for m in self.MS)
 
     def config(self):
         return {"workload": self.name, "N": self.N, "K": self.K, "M": list(self.MS), "weights": "int8 per-channel (axis 0), f16 scales",
                 "l2": f"{self.REPLICAS} weight replicas ({self.REPLICAS * self.N * self.K >> 20} MiB > 126 MiB L2) cycled per launch",
                 "seed": 1002}
 
-    def bound_of(self, m):
-        # ridge of the measured peaks: tensor-bound once flops/bytes exceeds peak_flops/peak_bw
-        return "tensor" if m >= 512 else "hbm"
+
+class W4A16Linear(Workload):
+    """Config 3: W f16 [4096,4096] ~ N(0,0.02) -> int4 in blocks of 128 along K (f16 scales, low nibble
+    first); X f16 [M,4096]; Y = X . dequant(W)^T, f16; M in {1, 8, 32}."""
+
+    name = "config3_w4a16_linear"
+    metric = "quantized GEMM TFLOP/s (config 3: block-128 int4 weights, W4A16 linear, M in {1,8,32})"
+    unit = "TFLOP/s"
+    dtype = "f16 x int4 -> f32 accumulate -> f16"
+    N, K, B = 4096, 4096, 128
+    MS = (1, 8, 32)
+    REPLICAS = 24  # 24 x 8.25 MiB of weights + scales cycled per launch (198 MiB > L2)
+
+    def __init__(self, torch, ql, device, dist=None, seed=1003):
+        self.torch, self.ql, self.device = torch, ql, device
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        w = (torch.randn((self.N, self.K), generator=g, dtype=torch.float32) * 0.02).to(torch.float16).to(device)
+        s = ql.amax_scale(w, ql.int4, block=(1, self.B))
+        q = ql.quantize(w, s, ql.int4)
+        self.wq = [q] + [ql.Int4Tensor(q.packed.clone(), q.shape) for _ in range(self.REPLICAS - 1)]
+        self.scale = [s] + [s.clone() for _ in range(self.REPLICAS - 1)]
+        self.x_host = {m: torch.randn((m, self.K), generator=g, dtype=torch.float32).to(torch.float16).pin_memory() for m in self.MS}
+        self.x = {m: self.x_host[m].to(device) for m in self.MS}
+        self.y = {m: torch.empty((m, self.N), dtype=torch.float16, device=device) for m in self.MS}
+        self.y_host = {m: torch.empty((m, self.N), dtype=torch.float16).pin_memory() for m in self.MS}
+        self.turn = 0
+
+    def run_part(self, m):
+        i = self.turn % self.REPLICAS
+        self.turn += 1
+        self.ql.linear_w4a16(self.x[m], self.wq[i], self.scale[i], out=self.y[m])
+
+    def parts(self):
+        return [(f"M={m}", (lambda m=m: self.run_part(m)), 2 * m * self.N * self.K,
+                 self.N * self.K // 2 + self.N * (self.K // self.B) * 2 + m * self.K * 2 + m * self.N * 2, "hbm") for m in self.MS]
+
+    def e2e_step(self):
+        for m in self.MS:
+            self.x[m].copy_(self.x_host[m], non_blocking=True)
+            self.run_part(m)
+            self.y_host[m].copy_(self.y[m], non_blocking=True)
+
+    def e2e_bytes(self):
+        return sum(m * self.K * 2 for m in self.MS), sum(m * self.N * 2 for m in self.MS)
+
+    def config(self):
+        return {"workload": self.name, "N": self.N, "K": self.K, "block": self.B, "M": list(self.MS),
+                "l2": f"{self.REPLICAS} weight replicas (198 MiB > 126 MiB L2) cycled per launch", "seed": 1003}
 
 
 class QdqInt8(Workload):
@@ -186,7 +238,7 @@ class QdqInt8(Workload):
     SHAPE = (4096, 4096)
     REPLICAS = 4  # 4 x (64 + 16 + 64) MiB
 
-    def __init__(self, torch, ql, device, seed=1001):
+    def __init__(self, torch, ql, device, dist=None, seed=1001):
         self.torch, self.ql, self.device = torch, ql, device
         g = torch.Generator(device="cpu").manual_seed(seed)
         self.x_host = torch.randn(self.SHAPE, generator=g, dtype=torch.float32).pin_memory()
@@ -212,7 +264,7 @@ class QdqInt8(Workload):
 
     def parts(self):
         n = self.SHAPE[0] * self.SHAPE[1]
-        return [("fused_qdq", self.run_part, 0, 9 * n)]
+        return [("fused_qdq", self.run_part, 0, 9 * n, "hbm")]
 
     def e2e_step(self):
         i = self.turn % self.REPLICAS
@@ -229,11 +281,92 @@ class QdqInt8(Workload):
         return {"workload": self.name, "shape": list(self.SHAPE), "scale": "max|x|/127 (f32, computed on the GPU)",
                 "l2": f"{self.REPLICAS} input/output replicas (576 MiB > 126 MiB L2) cycled per step", "seed": 1001}
 
-    def bound_of(self, _):
-        return "hbm"
+
+class Fp8Gemm(Workload):
+    """Config 4: X bf16 [8192,8192] ~ N(0,1) quantized per step to e4m3 with scale amax/448; W [28672,8192]
+    (the [8192,28672] matrix of the config held in Linear's [out,in] layout) ~ N(0,0.02) quantized once
+    per tensor; Y = (Xq . Wq^T) * sx * sw, bf16.  With g GPUs each rank owns N/g output columns and the
+    ranks all-gather Y (strong scaling)."""
+
+    name = "config4_fp8_w8a8_gemm"
+    metric = "quantized GEMM TFLOP/s (config 4: fp8 e4m3 W8A8, 8192x8192x28672, dynamic per-tensor activation scale)"
+    unit = "TFLOP/s"
+    dtype = "e4m3 x e4m3 -> f32 accumulate -> bf16"
+    M, K, N = 8192, 8192, 28672
+    use_graphs = False
+    scaling = "strong"
+
+    def __init__(self, torch, ql, device, dist=None, seed=1004):
+        self.torch, self.ql, self.device, self.dist = torch, ql, device, dist
+        self.world = dist.get_world_size() if dist is not None else 1
+        self.rank = dist.get_rank() if dist is not None else 0
+        self.parallelism = f"column-parallel over {self.world} GPUs, NCCL all-gather of Y" if self.world > 1 else "1 GPU"
+        nl = self.N // self.world
+        self.nl = nl
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        self.x_host = torch.randn((self.M, self.K), generator=g, dtype=torch.float32).to(torch.bfloat16).pin_memory()
+        self.x = self.x_host.to(device)
+        # the weight shard of this rank, drawn from the same stream on every rank
+        wq_parts, amax = [], torch.zeros((), device=device)
+        gw = torch.Generator(device="cpu").manual_seed(seed + 1)
+        rows = 1024
+        shard = torch.empty((nl, self.K), dtype=torch.bfloat16, device=device)
+        for r0 in range(0, self.N, rows):
+            blk = (torch.randn((rows, self.K), generator=gw, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+            amax = torch.maximum(amax, blk.float().abs().max().to(device))
+            lo, hi = self.rank * nl, (self.rank + 1) * nl
+            if r0 + rows > lo and r0 < hi:
+                a, b = max(r0, lo), min(r0 + rows, hi)
+                shard[a - lo:b - lo] = blk[a - r0:b - r0].to(device)
+        self.sw = (amax / 448.0).to(torch.bfloat16)            # per-tensor weight scale (rounded to the data type)
+        self.wq = ql.quantize(shard, self.sw, ql.float8)
+        self.sw32 = self.sw.float().reshape(())
+        del shard
+        self.sx32 = torch.empty((), dtype=torch.float32, device=device)
+        self.xq = torch.empty((self.M, self.K), dtype=torch.float8_e4m3fn, device=device)
+        self.y_local = torch.empty((self.M, nl), dtype=torch.bfloat16, device=device)
+        self.y_all = torch.empty((self.world, self.M, nl), dtype=torch.bfloat16, device=device) if self.world > 1 else None
+        self.y_host = torch.empty((self.M, nl), dtype=torch.bfloat16).pin_memory()
+
+    def p_scale(self):
+        self.ql.amax_scale(self.x, self.ql.float8, scale_dtype=self.ql.float32, out=self.sx32)
+
+    def p_quant(self):
+        self.ql.quantize_to(self.x, self.sx32, self.xq)
+
+    def p_gemm(self):
+        self.ql.gemm_fp8(self.xq, self.wq, self.sx32, self.sw32, out=self.y_local)
+
+    def p_gather(self):
+        self.dist.all_gather_into_tensor(self.y_all, self.y_local)
+
+    def parts(self):
+        mk = self.M * self.K
+        ps = [("x_amax_scale", self.p_scale, 0, 2 * mk, "hbm"), ("x_quantize", self.p_quant, 0, 3 * mk, "hbm"),
+              ("fp8_gemm", self.p_gemm, 2 * self.M * self.K * self.nl, mk + self.nl * self.K + 2 * self.M * self.nl, "tensor_fp8")]
+        if self.world > 1:
+            ps.append(("all_gather_y", self.p_gather, 0, 2 * self.M * self.nl * (self.world - 1), "nvlink"))
+        return ps
+
+    def step_flops_global(self):
+        return 2 * self.M * self.K * self.N
+
+    def e2e_step(self):
+        self.x.copy_(self.x_host, non_blocking=True)
+        for _, fn, _, _, _ in self.parts():
+            fn()
+        self.y_host.copy_(self.y_local, non_blocking=True)
+
+    def e2e_bytes(self):
+        return self.M * self.K * 2, self.M * self.nl * 2
+
+    def config(self):
+        return {"workload": self.name, "M": self.M, "K": self.K, "N": self.N, "N_per_gpu": self.nl,
+                "weights": "e4m3 per-tensor, quantized once; stored [N,K]", "activations": "bf16 -> e4m3 every step, scale = amax/448",
+                "l2": "operands and output (>= 600 MiB per GPU) exceed the 126 MiB L2", "seed": 1004}
 
 
-WORKLOADS = {"c2": W8A16Linear, "c1": QdqInt8}
+WORKLOADS = {"c1": QdqInt8, "c2": W8A16Linear, "c3": W4A16Linear, "c4": Fp8Gemm}
 
 
 # ----------------------------------------------------------------------------------------------
@@ -269,6 +402,34 @@ def cpu_reference(workload: str, budget_s: float = 12.0):
         dt = time.perf_counter() - t0
         flops = 2.0 * m_s * n_big * K
         return flops / dt / 1e12, "TFLOP/s", cores, f"M={m_s} rows x {n_big} of {N} output channels x K={K}, f32 accumulation, {dt:.1f} s"
+    if workload == "c3":
+        N, K, B = 4096, 4096, 128
+        m_s, n_s = 8, 128
+        x = rng.standard_normal((m_s, K)).astype(np.float16)
+        def sample(n_rows):
+            wp = rng.integers(0, 256, size=(n_rows, K // 2), dtype=np.uint8)
+            sc = (rng.random((n_rows, K // B)).astype(np.float32) * 1e-3 + 1e-4).astype(np.float16)
+            t0 = time.perf_counter()
+            orc.linear_w4(x, orc.F16, wp, sc, orc.F16, orc.F16, B, acc64=False)
+            return time.perf_counter() - t0
+        t1 = sample(n_s)
+        n_big = int(min(N, max(n_s, n_s * budget_s / max(t1, 1e-4))))
+        dt = sample(n_big)
+        return 2.0 * m_s * n_big * K / dt / 1e12, "TFLOP/s", cores, f"M={m_s} rows x {n_big} of {N} output channels x K={K}, block {B}, f32 accumulation, {dt:.1f} s"
+    if workload == "c4":
+        M, K, N = 8192, 8192, 28672
+        m_s, n_s = 32, 64
+        def sample(mm, nn):
+            xq = rng.integers(0, 0x7F, size=(mm, K), dtype=np.uint8)
+            wq = rng.integers(0, 0x7F, size=(nn, K), dtype=np.uint8)
+            t0 = time.perf_counter()
+            orc.gemm_fp8(xq, wq, np.float32(0.01), np.float32(0.01), orc.BF16, acc64=False)
+            return time.perf_counter() - t0
+        t1 = sample(m_s, n_s)
+        grow = (budget_s / max(t1, 1e-4)) ** 0.5
+        mm, nn = int(min(M, max(m_s, m_s * grow))), int(min(N, max(n_s, n_s * grow)))
+        dt = sample(mm, nn)
+        return 2.0 * mm * nn * K / dt / 1e12, "TFLOP/s", cores, f"{mm} of {M} rows x {nn} of {N} columns x K={K}, f32 accumulation, {dt:.1f} s"
     if workload == "c1":
         n = 1 << 22
         x = rng.standard_normal(n).astype(np.float32)
@@ -349,33 +510,78 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    wl = WORKLOADS[args.workload](torch, ql, device)
+    wl = WORKLOADS[args.workload](torch, ql, device, dist)
     parts = wl.parts()
     stream = torch.cuda.current_stream(device)
     L = ql.lib()
+    K = args.steps
 
-    # -------- device-resident timing: K steps, every part bracketed by events on the launch stream
-    for _ in range(args.warmup):
-        for _, fn, _, _ in parts:
+    def run_step():
+        for _, fn, _, _, _ in parts:
             fn()
+
+    for _ in range(args.warmup):
+        run_step()
     barrier()
+
+    # Optionally replay captured CUDA graphs, so that what is timed is the device work and not the
+    # Python/ctypes launch path.  One graph per buffer rotation keeps every launch on cold data.
+    rot = getattr(wl, "REPLICAS", 1)
+    step_graphs, part_graphs, launches_per_step = None, None, None
+    if wl.use_graphs:
+        step_graphs, part_graphs = [], [[] for _ in parts]
+        for _ in range(rot):
+            g = torch.cuda.CUDAGraph()
+            c0 = L.ql_launch_count()
+            with torch.cuda.graph(g):
+                run_step()
+            launches_per_step = L.ql_launch_count() - c0
+            step_graphs.append(g)
+        for p, (_, fn, _, _, _) in enumerate(parts):
+            for _ in range(rot):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    fn()
+                part_graphs[p].append(g)
+        stream = torch.cuda.current_stream(device)
+        for g in step_graphs:  # one untimed replay each
+            g.replay()
+        barrier()
+
     clocks = ClockSampler(local)
     clocks.start()
-    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in parts] for _ in range(args.steps)]
+    clocks.wait_ready()
+
+    # -------- whole steps, device-resident inputs
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = L.ql_launch_count()
+    barrier()
     t_start.record(stream)
-    for s in range(args.steps):
-        for p, (_, fn, _, _) in enumerate(parts):
-            ev[s][p][0].record(stream)
-            fn()
-            ev[s][p][1].record(stream)
+    for s_ in range(K):
+        if step_graphs:
+            step_graphs[s_ % rot].replay()
+        else:
+            run_step()
     t_end.record(stream)
     barrier()
-    launches = L.ql_launch_count() - launches0
     total_ms = t_start.elapsed_time(t_end)
+    launches = (launches_per_step * K) if step_graphs else (L.ql_launch_count() - launches0)
+
+    # -------- each part on its own (K launches back to back, rotating buffers): the roofline numbers
+    part_ms = []
+    for p, (_, fn, _, _, _) in enumerate(parts):
+        a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a_.record(stream)
+        for s_ in range(K):
+            if part_graphs:
+                part_graphs[p][s_ % rot].replay()
+            else:
+                fn()
+        b_.record(stream)
+        barrier()
+        part_ms.append(a_.elapsed_time(b_) / K)
     clock_info = clocks.stop()
-    part_ms = [sum(ev[s][p][0].elapsed_time(ev[s][p][1]) for s in range(args.steps)) / args.steps for p in range(len(parts))]
 
     # -------- end to end: inputs from pinned host memory, results read back, every step
     for _ in range(3):
@@ -383,40 +589,47 @@ def main():
     barrier()
     e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_start.record(stream)
-    for _ in range(args.steps):
+    for _ in range(K):
         wl.e2e_step()
     e_end.record(stream)
     barrier()
     e2e_ms = e_start.elapsed_time(e_end)
 
     if dist is not None:
-        t = torch.tensor([total_ms, e2e_ms], device=device, dtype=torch.float64)
+        t = torch.tensor([total_ms, e2e_ms] + part_ms, device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, e2e_ms = float(t[0]), float(t[1])
+        total_ms, e2e_ms, part_ms = float(t[0]), float(t[1]), [float(v) for v in t[2:]]
 
-    step_flops = sum(f for _, _, f, _ in parts)
-    step_bytes = sum(b for _, _, _, b in parts)
-    work = step_flops if wl.unit == "TFLOP/s" else step_bytes
+    strong = wl.scaling == "strong"
+    if hasattr(wl, "step_flops_global"):
+        work = wl.step_flops_global()                      # whole job, however many GPUs share it
+    else:
+        work = sum((f if wl.unit == "TFLOP/s" else b) for _, _, f, b, _ in parts) * world   # replicas
     denom = 1e12 if wl.unit == "TFLOP/s" else 1e9
-    value = work * args.steps * world / (total_ms * 1e-3) / denom
-    e2e_value = work * args.steps * world / (e2e_ms * 1e-3) / denom
+    value = work * K / (total_ms * 1e-3) / denom
+    e2e_value = work * K / (e2e_ms * 1e-3) / denom
 
     peaks = measured_peaks()
     dom = max(range(len(parts)), key=lambda p: part_ms[p])
-    name, _, f, b = parts[dom]
-    m_dom = wl.MS[dom] if hasattr(wl, "MS") else None
-    bound = wl.bound_of(m_dom)
+    name, _, f, b, bound = parts[dom]
+    sec = part_ms[dom] * 1e-3
     if bound == "tensor":
-        achieved, peak, unit = f / (part_ms[dom] * 1e-3) / 1e12, peaks["bf16_tflops_sustained"], "TFLOP/s"
+        achieved, peak, unit, note = f / sec / 1e12, peaks["bf16_tflops_sustained"], "TFLOP/s", "measured cuBLAS bf16, sustained"
+    elif bound == "tensor_fp8":
+        achieved, peak, unit, note = f / sec / 1e12, 2 * peaks["bf16_tflops_sustained"], "TFLOP/s", "2 x measured cuBLAS bf16 sustained (no fp8 peak was measured)"
+        bound = "tensor"
+    elif bound == "nvlink":
+        achieved, peak, unit, note = b / sec / 1e9, 770.0, "GB/s", "measured peer copy per direction"
     else:
-        achieved, peak, unit = b / (part_ms[dom] * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
+        achieved, peak, unit, note = b / sec / 1e9, peaks["hbm_gbs"], "GB/s", "measured copy bandwidth"
     roofline = {"kernel": f"{wl.name}:{name}", "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
-                "frac": achieved / peak, "peak_source": peaks["source"], "traffic": None,
+                "frac": achieved / peak, "peak_source": f"{peaks['source']}: {note}", "traffic": TRAFFIC.get(f"{wl.name}:{name}"),
                 "algorithmic_bytes_per_launch": b, "algorithmic_flops_per_launch": f, "avg_launch_ms": part_ms[dom]}
     per_part = {}
-    for p, (nm, _, f, b) in enumerate(parts):
-        per_part[nm] = {"ms": part_ms[p], "GB/s": b / (part_ms[p] * 1e-3) / 1e9, "TFLOP/s": f / (part_ms[p] * 1e-3) / 1e12,
-                        "frac_hbm": b / (part_ms[p] * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    for p, (nm, _, f, b, bd) in enumerate(parts):
+        sec = part_ms[p] * 1e-3
+        per_part[nm] = {"ms": part_ms[p], "GB/s": b / sec / 1e9, "TFLOP/s": f / sec / 1e12, "bound": bd,
+                        "frac_hbm_measured": b / sec / 1e9 / peaks["hbm_gbs"]}
 
     if rank != 0:
         if dist is not None:
@@ -424,11 +637,13 @@ def main():
         return
 
     h2d, d2h = wl.e2e_bytes()
-    line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": wl.dtype, "data": "synthetic (seeded)", "config": dict(wl.config(), parallelism="replicas only" if world > 1 else "1 GPU"),
+    line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": K, "warmup": args.warmup,
+            "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None,
+            "dtype": wl.dtype, "data": "synthetic (seeded)",
+            "config": dict(wl.config(), parallelism=(wl.parallelism if world > 1 else "1 GPU"),
+                           timing="CUDA graph replay" if step_graphs else "direct launches"),
             "clocks": clock_info, "gpu_launches": int(launches),
-            "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
+            "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / K},
             "roofline": roofline, "parts": per_part}
     if not args.no_cpu_baseline and world == 1:
         v, u, cores, sample = cpu_reference(args.workload)

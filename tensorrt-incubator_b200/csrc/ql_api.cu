@@ -30,6 +30,20 @@ int cuda_error(cudaError_t e, const char *what) {
 static std::atomic<uint64_t> g_launches{0};
 void count_launches(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
+// The stream-ordered allocator gives scratch memory back to the driver at every synchronisation
+// unless told otherwise; keep it cached so that scratch users pay for it once.
+void keep_scratch_pool_warm() {
+  static bool done[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || done[dev]) return;
+  cudaMemPool_t pool;
+  if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+    uint64_t keep = UINT64_MAX;
+    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+  }
+  done[dev] = true;
+}
+
 int sm_count() {
   static int cached[64];
   int dev = 0;
@@ -64,6 +78,15 @@ int launch_scale_from_amax(const float *amax, void *scale, int sdt, int64_t n, f
 // ql_wo_linear.cu
 int launch_wo_linear(int wbits, int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M,
                      int N, int K, int block, cudaStream_t st);
+
+int launch_w8a16_large(int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M, int N, int K,
+                       cudaStream_t st);
+// ql_gemm_tc.cu
+int gemm16_device(int dtype, const void *X, const void *W, const float *sb, int sb_n, void *Y, int M, int N, int K,
+                  cudaStream_t st);
+
+// Above this many rows of X the weight-only layers leave the streaming kernel for the tcgen05 GEMM.
+constexpr int kWeightOnlyMaxRows = 64;
 
 static bool same_shape(const ql_tensor *a, const ql_tensor *b) {
   if (a->rank != b->rank) return false;
@@ -266,6 +289,7 @@ int ql_amax_scale(const ql_tensor *input, ql_tensor *scale, const ql_qdq_attrs *
   }
   // 16-bit scales: f32 accumulators in stream-ordered scratch memory
   float *acc = nullptr;
+  keep_scratch_pool_warm();
   QL_CUDA_TRY(cudaMallocAsync(&acc, sizeof(float) * (size_t)plan.n_scales, st));
   rc = launch_amax(input, acc, plan, st);
   if (rc == QL_OK) rc = launch_scale_from_amax(acc, scale->data, scale->dtype, plan.n_scales, maxbound, st);
@@ -309,6 +333,9 @@ int ql_linear_w8a16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *sca
                      "%s: For per-channel quantization, expected the scales tensor dimension to match the "
                      "quantization axis dimension of input tensor", op);
   if (K % 64 != 0) return set_error(QL_ERR_UNSUPPORTED, "%s: K must be a multiple of 64 (got %lld)", op, (long long)K);
+  if (M > kWeightOnlyMaxRows)
+    return launch_w8a16_large(x->dtype, x->data, w->data, scale->data, scale->dtype, y->data, (int)M, (int)N, (int)K,
+                              (cudaStream_t)stream);
   return launch_wo_linear(8, x->dtype, x->data, w->data, scale->data, scale->dtype, y->data, (int)M, (int)N, (int)K, 0,
                           (cudaStream_t)stream);
 }
@@ -326,6 +353,21 @@ int ql_linear_w4a16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *sca
   if (K % 128 != 0 || block % 128 != 0)
     return set_error(QL_ERR_UNSUPPORTED, "%s: K and the block size must be multiples of 128 (K=%lld, block=%lld)", op,
                      (long long)K, (long long)block);
+  if (M > kWeightOnlyMaxRows) {
+    // dequantize to the activation type in scratch memory (the reference's dequantize), then the 16-bit GEMM
+    cudaStream_t st = (cudaStream_t)stream;
+    void *wide = nullptr;
+    keep_scratch_pool_warm();
+    QL_CUDA_TRY(cudaMallocAsync(&wide, (size_t)N * K * 2, st));
+    ql_tensor wd{wide, x->dtype, 2, {N, K}};
+    QdqPlan plan;
+    rc = plan_qdq(w, scale, nullptr, QL_I4, op, &plan);
+    if (rc == QL_OK) rc = launch_dequantize(w, scale, &wd, plan, st);
+    if (rc == QL_OK) rc = gemm16_device(x->dtype, x->data, wide, nullptr, 0, y->data, (int)M, (int)N, (int)K, st);
+    cudaError_t fe = cudaFreeAsync(wide, st);
+    if (rc == QL_OK && fe != cudaSuccess) return cuda_error(fe, "cudaFreeAsync");
+    return rc;
+  }
   return launch_wo_linear(4, x->dtype, x->data, w->data, scale->data, scale->dtype, y->data, (int)M, (int)N, (int)K,
                           (int)block, (cudaStream_t)stream);
 }

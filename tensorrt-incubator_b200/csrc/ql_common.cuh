@@ -26,6 +26,7 @@ int sm_count();
 void count_launches(int n); // bumps the counter ql_launch_count() reports
 // One int per device in global memory where kernels record that a bounded wait ran out (0 = none).
 int *device_status_word();
+void keep_scratch_pool_warm(); // call before cudaMallocAsync
 
 static inline int64_t numel(const ql_tensor *t) {
   int64_t n = 1;

@@ -475,6 +475,16 @@ int run_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_te
 }
 
 } // namespace
+
+// Y[M,N] = (X[M,K] . W[N,K]^T) * sb[n]; X, W and Y of the same 16-bit type (QL_BF16 / QL_F16).
+int gemm16_device(int dtype, const void *X, const void *W, const float *sb, int sb_n, void *Y, int M, int N, int K,
+                  cudaStream_t st) {
+  ql_tensor x{const_cast<void *>(X), dtype, 2, {M, K}}, w{const_cast<void *>(W), dtype, 2, {N, K}}, y{Y, dtype, 2, {M, N}};
+  ql_tensor s{const_cast<float *>(sb), QL_F32, 1, {sb_n}};
+  if (dtype == QL_BF16) return run_gemm<KIND_BF16>("gemm_16", &x, &w, nullptr, sb ? &s : nullptr, &y, st);
+  return run_gemm<KIND_F16>("gemm_16", &x, &w, nullptr, sb ? &s : nullptr, &y, st);
+}
+
 } // namespace ql
 
 using namespace ql;

@@ -315,7 +315,49 @@ int launch_wo_t(const void *X, const void *W, const void *scale, int sdt, void *
   return QL_OK;
 }
 
+// int8 -> f16 / bf16, exact (|v| <= 128 fits both significands); 16 values per thread
+template <typename XT>
+__global__ void __launch_bounds__(256) widen_i8_kernel(const uint8_t *__restrict__ w, XT *__restrict__ out, int64_t n16) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n16) return;
+  const uint4 raw = __ldcs(reinterpret_cast<const uint4 *>(w) + i);
+  const uint32_t v[4] = {raw.x ^ 0x80808080u, raw.y ^ 0x80808080u, raw.z ^ 0x80808080u, raw.w ^ 0x80808080u};
+  uint4 lo = make_uint4(int8_pair<XT, 0>(v[0]), int8_pair<XT, 2>(v[0]), int8_pair<XT, 0>(v[1]), int8_pair<XT, 2>(v[1]));
+  uint4 hi = make_uint4(int8_pair<XT, 0>(v[2]), int8_pair<XT, 2>(v[2]), int8_pair<XT, 0>(v[3]), int8_pair<XT, 2>(v[3]));
+  reinterpret_cast<uint4 *>(out)[2 * i] = lo;
+  reinterpret_cast<uint4 *>(out)[2 * i + 1] = hi;
+}
+
+__global__ void __launch_bounds__(256) scale_to_f32_kernel(const void *__restrict__ s, int sdt, float *__restrict__ out, int n) {
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i < n) out[i] = load_scale(s, sdt, i);
+}
+
 } // namespace
+
+// Large batches: the weights are widened to the activation type in scratch memory (exact) and the
+// product runs on the tcgen05 GEMM with the per-channel scales in its epilogue.
+int gemm16_device(int dtype, const void *X, const void *W, const float *sb, int sb_n, void *Y, int M, int N, int K,
+                  cudaStream_t st);
+
+int launch_w8a16_large(int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M, int N, int K,
+                       cudaStream_t st) {
+  const int64_t n = (int64_t)N * K;
+  const size_t wide_bytes = (size_t)n * 2, scale_off = (wide_bytes + 255) & ~size_t(255);
+  uint8_t *scratch = nullptr;
+  keep_scratch_pool_warm();
+  QL_CUDA_TRY(cudaMallocAsync(&scratch, scale_off + (size_t)N * sizeof(float), st));
+  float *sf = reinterpret_cast<float *>(scratch + scale_off);
+  const int64_t n16 = n / 16; // K % 64 == 0
+  if (xdt == QL_F16) widen_i8_kernel<__half><<<(unsigned)((n16 + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t *>(W), reinterpret_cast<__half *>(scratch), n16);
+  else widen_i8_kernel<__nv_bfloat16><<<(unsigned)((n16 + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t *>(W), reinterpret_cast<__nv_bfloat16 *>(scratch), n16);
+  scale_to_f32_kernel<<<(N + 255) / 256, 256, 0, st>>>(scale, sdt, sf, N);
+  count_launches(2);
+  int rc = gemm16_device(xdt, X, scratch, sf, N, Y, M, N, K, st);
+  cudaError_t fe = cudaFreeAsync(scratch, st);
+  if (rc == QL_OK && fe != cudaSuccess) return cuda_error(fe, "cudaFreeAsync");
+  return rc;
+}
 
 int launch_wo_linear(int wbits, int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M,
                      int N, int K, int block, cudaStream_t st) {

@@ -3,5 +3,5 @@ B200 (sm_100a) kernels in ../csrc, reached through the C ABI in include/qlinear_
 from ._lib import QlError, lib  # noqa: F401
 from .dtypes import bfloat16, float8, float16, float32, int4, int8  # noqa: F401
 from .linear import Linear, gemm_16, gemm_fp8, gemm_i8, linear_w4a16, linear_w8a16  # noqa: F401
-from .ops import QuantizeError, amax_scale, dequantize, quantize, quantize_dequantize  # noqa: F401
+from .ops import QuantizeError, amax_scale, dequantize, quantize, quantize_dequantize, quantize_to  # noqa: F401
 from .tensor import Int4Tensor  # noqa: F401

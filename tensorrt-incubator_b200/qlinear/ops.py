@@ -82,6 +82,16 @@ def quantize(input: torch.Tensor, scale, dtype: dt.dtype, dim=None, *, fp8_mode:
     return q
 
 
+def quantize_to(input: torch.Tensor, scale: torch.Tensor, out, dim=None, *, fp8_mode: str = "direct"):
+    """tensorrt.quantize into a preallocated output with a device-resident scale of any float type
+    (the operator itself allows f32 scales for 16-bit data; only Tripy's layer ties the two)."""
+    require_cuda(input, "input")
+    require_cuda(scale, "scale")
+    tx, ts, tq = ql_view(input), ql_view(scale), ql_view(out)
+    _lib.check(_lib.lib().ql_quantize(tx, ts, tq, _lib.make_attrs(dim, fp8_mode), current_stream(input.device)))
+    return out
+
+
 def dequantize(input, scale, dtype: dt.dtype, dim=None, *, out=None) -> torch.Tensor:
     """output = input * scale as `dtype` (float32, float16 or bfloat16)."""
     if dtype not in dt.QUANTIZABLE_DTYPES:

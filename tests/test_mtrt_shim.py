@@ -1,0 +1,129 @@
+"""The executor runtime's CUDA-module boundary (mtrt_cuda_*), the symbols generated host code
+calls.  Modelled on the reference's launch-ABI tests
+(compiler/test/IntegrationTests/CUDA/cuda-launch-kernel.mlir: a memref plus i32 and f32 scalar
+arguments; EmitC/cuda-launch-argpack.mlir:19-21: the missing-artifact error path)."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ROOT
+
+import oracle as orc
+import qlinear as ql
+from qlinear import _lib
+
+PTX = os.path.join(ROOT, "tests", "golden", "add_scalar.ptx")
+
+
+@pytest.fixture(scope="module")
+def rt():
+    L = ctypes.CDLL(_lib.LIB_PATH)
+    vp = ctypes.c_void_p
+    L.mtrt_cuda_module_load_from_ptx.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
+    L.mtrt_cuda_module_load_from_ptx.restype = vp
+    L.mtrt_cuda_module_load_from_ptx_file.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
+    L.mtrt_cuda_module_load_from_ptx_file.restype = vp
+    L.mtrt_cuda_module_unload.argtypes = [vp]
+    L.mtrt_cuda_module_get_function.argtypes = [vp, ctypes.c_char_p, ctypes.c_int64]
+    L.mtrt_cuda_module_get_function.restype = vp
+    L.mtrt_cuda_launch_kernel.argtypes = [vp] + [ctypes.c_int32] * 7 + [vp, ctypes.POINTER(vp)]
+    L.mtrt_cuda_last_error.restype = ctypes.c_char_p
+    L.ql_mtrt_bind_kernel.argtypes = [ctypes.c_char_p, ctypes.c_char_p]
+    L.mtrt_cuda_stream_create.restype = vp
+    L.mtrt_cuda_stream_sync.argtypes = [vp]
+    L.mtrt_cuda_stream_destroy.argtypes = [vp]
+    L.mtrt_cuda_alloc_async.argtypes = [vp, ctypes.c_int64, ctypes.c_int32, ctypes.c_int8, ctypes.c_int8]
+    L.mtrt_cuda_alloc_async.restype = vp
+    L.mtrt_cuda_memcpy_async.argtypes = [vp, vp, vp, ctypes.c_int64]
+    L.mtrt_cuda_free.argtypes = [vp, vp, ctypes.c_int8, ctypes.c_int8]
+    return L
+
+
+def _args(*values):
+    """void** args: each entry points at one kernel parameter."""
+    holders = list(values)
+    arr = (ctypes.c_void_p * len(holders))(*[ctypes.cast(ctypes.byref(h), ctypes.c_void_p) for h in holders])
+    return arr, holders
+
+
+def test_handles_without_a_gpu(rt):
+    ptx = open(PTX, "rb").read()
+    mod = rt.mtrt_cuda_module_load_from_ptx(ptx, len(ptx))
+    assert mod
+    name = b"ql:quantize;in=f32;out=i8;scale=f32;shape=4x4_trailing_bytes_are_ignored"
+    fn = rt.mtrt_cuda_module_get_function(mod, name, len(b"ql:quantize;in=f32;out=i8;scale=f32;shape=4x4"))
+    assert fn  # the name is length-delimited, not NUL-terminated
+    assert rt.ql_mtrt_bind_kernel(b"main_kernel_0", b"ql:dequantize;in=i8;out=f32;scale=f32;shape=8") == 0
+    assert rt.mtrt_cuda_module_get_function(mod, b"main_kernel_0", 13)
+    assert rt.ql_mtrt_bind_kernel(b"bad", b"not a spec") != 0
+    rt.mtrt_cuda_module_unload(mod)
+    # missing artifact: an error, not an abort
+    missing = b"/nonexistent/kernels.ptx"
+    assert not rt.mtrt_cuda_module_load_from_ptx_file(missing, len(missing))
+    assert b"could not open artifact" in rt.mtrt_cuda_last_error()
+
+
+@pytest.mark.gpu
+def test_jit_kernel_from_caller_ptx_with_memref_and_scalar_args(rt):
+    """A kernel the library does not own goes through the driver JIT exactly as in the reference."""
+    mod = rt.mtrt_cuda_module_load_from_ptx_file(PTX.encode(), len(PTX))
+    assert mod, rt.mtrt_cuda_last_error()
+    fn = rt.mtrt_cuda_module_get_function(mod, b"add_scalar", 10)
+    assert fn, rt.mtrt_cuda_last_error()
+    stream = rt.mtrt_cuda_stream_create()
+    n = 1000
+    host = np.arange(n, dtype=np.float32)
+    dev = rt.mtrt_cuda_alloc_async(stream, n * 4, 16, 0, 0)
+    rt.mtrt_cuda_memcpy_async(stream, host.ctypes.data, dev, n * 4)
+    arr, keep = _args(ctypes.c_void_p(dev), ctypes.c_int32(n), ctypes.c_float(2.5))
+    rt.mtrt_cuda_launch_kernel(fn, (n + 127) // 128, 1, 1, 128, 1, 1, 0, stream, arr)
+    out = np.zeros(n, dtype=np.float32)
+    rt.mtrt_cuda_memcpy_async(stream, dev, out.ctypes.data, n * 4)
+    rt.mtrt_cuda_stream_sync(stream)
+    assert np.array_equal(out, host + np.float32(2.5))
+    rt.mtrt_cuda_free(stream, dev, 0, 0)
+    rt.mtrt_cuda_stream_sync(stream)
+    rt.mtrt_cuda_stream_destroy(stream)
+    assert not rt.mtrt_cuda_module_get_function(mod, b"no_such_kernel", 14)
+    rt.mtrt_cuda_module_unload(mod)
+
+
+@pytest.mark.gpu
+def test_library_kernels_through_the_launch_abi(rt):
+    """Kernel names bound to library kernels: same host-side calls, hand-written sm_100a code."""
+    mod = rt.mtrt_cuda_module_load_from_ptx(b"", 0)
+    g = torch.Generator(device="cpu").manual_seed(9)
+    x = torch.randn((64, 256), generator=g).cuda()
+    s = (x.abs().max() / 127).reshape(())
+    q = torch.empty((64, 256), dtype=torch.int8, device="cuda")
+    assert rt.ql_mtrt_bind_kernel(b"quantize_kernel", b"ql:quantize;in=f32;out=i8;scale=f32;shape=64x256") == 0
+    fn = rt.mtrt_cuda_module_get_function(mod, b"quantize_kernel", 15)
+    stream = torch.cuda.current_stream().cuda_stream
+    arr, keep = _args(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(s.data_ptr()), ctypes.c_void_p(q.data_ptr()))
+    # grid and block describe the generated kernel the name used to denote; they are ignored
+    rt.mtrt_cuda_launch_kernel(fn, 1, 1, 1, 128, 1, 1, 0, stream, arr)
+    torch.cuda.synchronize()
+    assert rt.mtrt_cuda_last_error() == b""
+    want = orc.quantize(x.cpu().numpy(), orc.F32, s.cpu().numpy(), orc.F32, orc.I8)
+    assert np.array_equal(q.cpu().numpy(), want)
+
+    # per-channel int8 weights and the W8A16 linear, by self-describing names
+    w = (torch.randn((32, 128), generator=g) * 0.02).to(torch.float16).cuda()
+    ws = ql.amax_scale(w, ql.int8, dim=0)
+    wq = torch.empty((32, 128), dtype=torch.int8, device="cuda")
+    name = b"ql:quantize;in=f16;out=i8;scale=f16;shape=32x128;axis=0"
+    arr, keep = _args(ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(ws.data_ptr()), ctypes.c_void_p(wq.data_ptr()))
+    rt.mtrt_cuda_launch_kernel(rt.mtrt_cuda_module_get_function(mod, name, len(name)), 1, 1, 1, 1, 1, 1, 0, stream, arr)
+    xa = torch.randn((4, 128), generator=g).to(torch.bfloat16).cuda()
+    y = torch.empty((4, 32), dtype=torch.bfloat16, device="cuda")
+    name = b"ql:linear_w8a16;x=bf16;scale=f16;M=4;N=32;K=128"
+    arr, keep = _args(ctypes.c_void_p(xa.data_ptr()), ctypes.c_void_p(wq.data_ptr()), ctypes.c_void_p(ws.data_ptr()), ctypes.c_void_p(y.data_ptr()))
+    rt.mtrt_cuda_launch_kernel(rt.mtrt_cuda_module_get_function(mod, name, len(name)), 1, 1, 1, 1, 1, 1, 0, stream, arr)
+    torch.cuda.synchronize()
+    assert rt.mtrt_cuda_last_error() == b""
+    assert torch.equal(wq, ql.quantize(w, ws, ql.int8, 0))
+    assert torch.equal(y, ql.linear_w8a16(xa, wq, ws))
+    rt.mtrt_cuda_module_unload(mod)
