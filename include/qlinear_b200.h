@@ -120,6 +120,14 @@ QL_API int ql_gemm_i8(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor 
 QL_API int ql_gemm_16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *sw, ql_tensor *y,
                       void *stream);
 
+/* Row kernels of the quantized MLP block (RMSNorm / SwiGLU are not reference operators; the quantize
+ * step inside them is tensorrt.quantize with one scale per row, scale = max|row| / 448):
+ *   rmsnorm_quant_fp8: r = x * rsqrt(mean(x^2) + eps) (weight 1); q = e4m3(r / s[t]); x [T,H] bf16|f16
+ *   swiglu_quant_fp8:  a = silu(gate) * up with gate_up = [gate | up] [T, 2I]; q = e4m3(a / s[t]), q [T,I]
+ * q is e4m3, scale f32 [T]; row lengths must be multiples of 16. */
+QL_API int ql_rmsnorm_quant_fp8(const ql_tensor *x, float eps, ql_tensor *q, ql_tensor *scale, void *stream);
+QL_API int ql_swiglu_quant_fp8(const ql_tensor *gate_up, ql_tensor *q, ql_tensor *scale, void *stream);
+
 /* The tensor-core kernels bound every on-device wait (mbarrier, tensor-memory hand-over) by a
  * cycle limit; a kernel that runs out records a code and returns early instead of hanging.  This
  * call synchronises the device, returns QL_ERR_DEVICE_TIMEOUT if a code was recorded since the

@@ -54,6 +54,7 @@ def lib():
         L.orc_gemm_fp8.argtypes = [vp, vp, vp, i64, vp, i64, i64, i64, i64, vp, ci, ci]
         L.orc_gemm_i8.argtypes = [vp, vp, vp, i64, vp, i64, i64, i64, i64, vp, ci]
         L.orc_rmsnorm_quant_fp8.argtypes = [vp, ci, i64, i64, f, vp, vp]
+        L.orc_swiglu_quant_fp8.argtypes = [vp, ci, i64, i64, vp, vp]
         L.orc_f32_to_f8e4m3.argtypes = [f]
         L.orc_f32_to_f8e4m3.restype = ctypes.c_uint8
         L.orc_f8e4m3_to_f32.argtypes = [ctypes.c_uint8]
@@ -243,6 +244,21 @@ def rmsnorm_quant_fp8(X, x_code, eps=1e-5):
     s = np.zeros(M, dtype=np.float32)
     lib().orc_rmsnorm_quant_fp8(_ptr(np.ascontiguousarray(X)), x_code, M, H, float(eps), _ptr(Q), _ptr(s))
     return Q, s
+
+
+def swiglu_quant_fp8(GU, x_code):
+    M, I2 = GU.shape
+    Q = np.zeros((M, I2 // 2), dtype=np.uint8)
+    s = np.zeros(M, dtype=np.float32)
+    lib().orc_swiglu_quant_fp8(_ptr(np.ascontiguousarray(GU)), x_code, M, I2 // 2, _ptr(Q), _ptr(s))
+    return Q, s
+
+
+def f8_to_f32(bits: np.ndarray) -> np.ndarray:
+    """e4m3 bit patterns -> float32 values."""
+    L = lib()
+    lut = np.array([L.orc_f8e4m3_to_f32(i) for i in range(256)], dtype=np.float32)
+    return lut[bits]
 
 
 def unpack_i4(p: np.ndarray, n: int) -> np.ndarray:

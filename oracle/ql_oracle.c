@@ -398,6 +398,27 @@ int orc_rmsnorm_quant_fp8(const void *X, int x_dtype, int64_t M, int64_t H, floa
 /* SwiGLU: a = silu(g) * u with g, u given as f32 */
 float orc_silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
 
+/* SwiGLU then per-token e4m3 quantization: a = silu(g) * u (f32), s_m = max|a_m| / 448, q = e4m3(a / s_m).
+ * GU is [M, 2I] = [gate | up].  Defined by the benchmark configuration, not by a reference operator. */
+int orc_swiglu_quant_fp8(const void *GU, int x_dtype, int64_t M, int64_t I, uint8_t *Q, float *scale) {
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; m++) {
+    float amax = 0.0f;
+    for (int64_t i = 0; i < I; i++) {
+      float a = orc_silu_mul(load_as_f32(GU, x_dtype, m * 2 * I + i), load_as_f32(GU, x_dtype, m * 2 * I + I + i));
+      amax = fmaxf(amax, fabsf(a));
+    }
+    float s = amax / 448.0f;
+    if (s == 0.0f) s = 1.0f;
+    scale[m] = s;
+    for (int64_t i = 0; i < I; i++) {
+      float a = orc_silu_mul(load_as_f32(GU, x_dtype, m * 2 * I + i), load_as_f32(GU, x_dtype, m * 2 * I + I + i));
+      Q[m * I + i] = orc_f32_to_f8e4m3(a / s);
+    }
+  }
+  return 0;
+}
+
 int orc_num_threads(void) {
   int n = 1;
 #ifdef _OPENMP

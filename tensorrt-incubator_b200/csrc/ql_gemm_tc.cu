@@ -162,8 +162,22 @@ struct GemmArgs {
   int num_kb;      // K blocks of 128 bytes (the last may be partial: TMA fills zeros)
   int k_elems_per_block;
   int tiles_m, tiles_n;
+  int group_m;     // m-tiles per scheduling group (see tile_coords)
   int *status;
 };
+
+// Tile order.  Consecutive tile indices (which run concurrently on neighbouring SMs) walk a band
+// of `group_m` row tiles across all column tiles before moving to the next band, so the A rows of
+// the band stay in L2 while every B tile is streamed through once per band.
+__device__ __forceinline__ void tile_coords(const GemmArgs &a, int tile, int *mt, int *nt) {
+  const int per_group = a.group_m * a.tiles_n;
+  const int grp = tile / per_group;
+  const int first_m = grp * a.group_m;
+  const int gsz = min(a.group_m, a.tiles_m - first_m);
+  const int local = tile - grp * per_group;
+  *mt = first_m + local % gsz;
+  *nt = local / gsz;
+}
 
 template <int BN> struct SmemLayout {
   static constexpr int kBStage = BN * BK_BYTES;
@@ -226,7 +240,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       long long issued = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % args.tiles_m) * BM, n0 = (tile / args.tiles_m) * BN;
+        int mt, nt;
+        tile_coords(args, tile, &mt, &nt);
+        const int m0 = mt * BM, n0 = nt * BN;
         for (int kb = 0; kb < args.num_kb; kb++) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           const uint32_t a_dst = smem_base + stage * L::kStage, b_dst = a_dst + A_STAGE_BYTES;
@@ -290,7 +306,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, it++) {
       const int buf = it & 1;
-      const int m0 = (tile % args.tiles_m) * BM, n0 = (tile / args.tiles_m) * BN;
+      int mt, nt;
+      tile_coords(args, tile, &mt, &nt);
+      const int m0 = mt * BM, n0 = nt * BN;
       if (!mbar_wait(tfull_bar(buf), (it >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const int m = m0 + quad * 32 + lane;
@@ -318,7 +336,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int j = 0; j < 32; j += 8) {
               uint4 o = make_uint4(pack2<OutT>(v[j], v[j + 1]), pack2<OutT>(v[j + 2], v[j + 3]),
                                    pack2<OutT>(v[j + 4], v[j + 5]), pack2<OutT>(v[j + 6], v[j + 7]));
-              *reinterpret_cast<uint4 *>(row + j) = o;
+              __stcs(reinterpret_cast<uint4 *>(row + j), o); // written once, never re-read here: keep it out of L2's way
             }
           } else {
             for (int j = 0; j < 32 && n + j < args.N; j++) row[j] = FloatIO<OutT>::from_f32(v[j]);
@@ -467,6 +485,12 @@ int run_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_te
   args.num_kb = (int)((K * esize + BK_BYTES - 1) / BK_BYTES);
   args.tiles_m = (int)((M + BM - 1) / BM);
   args.tiles_n = 0;
+  {
+    // a band of A of about 16 MiB stays L2-resident while B streams through
+    const int64_t band = (16ll << 20) / ((int64_t)BM * K * esize);
+    args.group_m = (int)(band < 4 ? 4 : band);
+    if (args.group_m > args.tiles_m) args.group_m = args.tiles_m;
+  }
   args.status = device_status_word();
   if (!args.status) return set_error(QL_ERR_CUDA, "%s: could not allocate the device status word", op);
   cudaStream_t st = (cudaStream_t)stream;

@@ -1,0 +1,187 @@
+// Row kernels of the quantized Llama-style MLP block (benchmark config 5): RMSNorm fused with the
+// dynamic per-token e4m3 quantization of the activations, and SwiGLU fused with the per-token
+// re-quantization that feeds the down projection.  Neither is a reference operator; they are the
+// compositions reduce/rsqrt/multiply -> tensorrt.quantize and logistic/multiply ->
+// tensorrt.quantize that a StableHLO program for the block would contain, with the quantize step
+// keeping the reference's arithmetic (f32 division by the scale, saturating e4m3 conversion).
+// Both stream each row once from HBM (the second pass over a row hits L1/L2) and are bounded by
+// HBM bandwidth.
+#include "ql_common.cuh"
+
+namespace ql {
+namespace {
+
+constexpr int kRowThreads = 256;
+
+__device__ __forceinline__ double warp_sum_f64(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// One block per token.  r = x * rsqrt(mean(x^2) + eps); s = max|r| / 448; q = e4m3(r / s).
+// mean(x^2) is accumulated in f64 so that the result does not depend on how the row is split
+// over threads (up to the last bit of the f64 sum).
+template <typename XT>
+__global__ void __launch_bounds__(kRowThreads)
+rmsnorm_quant_fp8_kernel(const XT *__restrict__ X, uint8_t *__restrict__ Q, float *__restrict__ S, int H, float eps) {
+  constexpr int kPer16 = 16 / sizeof(XT);
+  const int64_t row = blockIdx.x;
+  const XT *x = X + row * H;
+  uint8_t *q = Q + row * H;
+  const int n_words = H / kPer16; // H % 16 == 0 is checked by the host
+  double ss = 0.0;
+  float amax = 0.f;
+  for (int w = threadIdx.x; w < n_words; w += kRowThreads) {
+    float v[kPer16];
+    load_vec_f32<XT, kPer16>(x + w * kPer16, v);
+#pragma unroll
+    for (int j = 0; j < kPer16; j++) {
+      ss += (double)v[j] * (double)v[j];
+      amax = fmaxf(amax, fabsf(v[j]));
+    }
+  }
+  __shared__ double part_ss[kRowThreads / 32];
+  __shared__ float part_mx[kRowThreads / 32];
+  __shared__ float s_rinv, s_scale;
+  ss = warp_sum_f64(ss);
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) {
+    part_ss[threadIdx.x >> 5] = ss;
+    part_mx[threadIdx.x >> 5] = amax;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    float m = 0.f;
+    for (int i = 0; i < kRowThreads / 32; i++) {
+      t += part_ss[i];
+      m = fmaxf(m, part_mx[i]);
+    }
+    const float rinv = (float)(1.0 / sqrt(t / (double)H + (double)eps));
+    // rounding is monotonic, so max|x * rinv| over the row is |x|max * rinv rounded once
+    float s = __fdiv_rn(__fmul_rn(m, rinv), 448.f);
+    if (s == 0.f) s = 1.f;
+    s_rinv = rinv;
+    s_scale = s;
+    S[row] = s;
+  }
+  __syncthreads();
+  const float rinv = s_rinv, s = s_scale;
+  // second pass: the row is still in L1/L2; 16 values -> one 16-byte store
+  const int n_chunks = H / 16;
+  for (int c = threadIdx.x; c < n_chunks; c += kRowThreads) {
+    float v[16];
+    load_vec_f32<XT, 16>(x + c * 16, v);
+    uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; j += 2) {
+      const float a = __fdiv_rn(__fmul_rn(v[j], rinv), s), b = __fdiv_rn(__fmul_rn(v[j + 1], rinv), s);
+      w[j >> 2] |= (f32x2_to_e4m3x2(a, b) & 0xFFFFu) << (8 * (j & 3));
+    }
+    __stcs(reinterpret_cast<uint4 *>(q) + c, make_uint4(w[0], w[1], w[2], w[3]));
+  }
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdiv_rn(g, 1.f + expf(-g)) * u; }
+
+// One block per token.  GU holds [gate | up] (I columns each); a = silu(gate) * up in f32;
+// s = max|a| / 448; q = e4m3(a / s).
+template <typename XT>
+__global__ void __launch_bounds__(kRowThreads)
+swiglu_quant_fp8_kernel(const XT *__restrict__ GU, uint8_t *__restrict__ Q, float *__restrict__ S, int I) {
+  const int64_t row = blockIdx.x;
+  const XT *g = GU + row * 2 * I, *u = g + I;
+  uint8_t *q = Q + row * I;
+  const int n_chunks = I / 16;
+  float amax = 0.f;
+  for (int c = threadIdx.x; c < n_chunks; c += kRowThreads) {
+    float gv[16], uv[16];
+    load_vec_f32<XT, 16>(g + c * 16, gv);
+    load_vec_f32<XT, 16>(u + c * 16, uv);
+#pragma unroll
+    for (int j = 0; j < 16; j++) amax = fmaxf(amax, fabsf(silu_mul(gv[j], uv[j])));
+  }
+  __shared__ float part[kRowThreads / 32];
+  __shared__ float s_scale;
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m = 0.f;
+    for (int i = 0; i < kRowThreads / 32; i++) m = fmaxf(m, part[i]);
+    float s = __fdiv_rn(m, 448.f);
+    if (s == 0.f) s = 1.f;
+    s_scale = s;
+    S[row] = s;
+  }
+  __syncthreads();
+  const float s = s_scale;
+  for (int c = threadIdx.x; c < n_chunks; c += kRowThreads) {
+    float gv[16], uv[16];
+    load_vec_f32<XT, 16>(g + c * 16, gv);
+    load_vec_f32<XT, 16>(u + c * 16, uv);
+    uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; j += 2) {
+      const float a = __fdiv_rn(silu_mul(gv[j], uv[j]), s), b = __fdiv_rn(silu_mul(gv[j + 1], uv[j + 1]), s);
+      w[j >> 2] |= (f32x2_to_e4m3x2(a, b) & 0xFFFFu) << (8 * (j & 3));
+    }
+    __stcs(reinterpret_cast<uint4 *>(q) + c, make_uint4(w[0], w[1], w[2], w[3]));
+  }
+}
+
+int check_rows(const char *op, const ql_tensor *x, const ql_tensor *q, const ql_tensor *s, int64_t cols_in, int64_t cols_out) {
+  if (!x || !q || !s) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: null tensor", op);
+  if (x->rank != 2 || q->rank != 2 || s->rank != 1) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: expected x [T,C], q [T,C'], scale [T]", op);
+  if (!(x->dtype == QL_BF16 || x->dtype == QL_F16)) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: x must be bf16 or f16", op);
+  if (q->dtype != QL_F8E4M3 || s->dtype != QL_F32) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: q must be e4m3 and scale f32", op);
+  if (x->shape[1] != cols_in || q->shape[1] != cols_out || q->shape[0] != x->shape[0] || s->shape[0] != x->shape[0])
+    return set_error(QL_ERR_INVALID_ARGUMENT, "%s: shapes do not agree", op);
+  if (cols_out % 16 != 0) return set_error(QL_ERR_UNSUPPORTED, "%s: the row length must be a multiple of 16 (got %lld)", op, (long long)cols_out);
+  if (!aligned16(x->data) || !aligned16(q->data)) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: x and q must be 16-byte aligned", op);
+  if (x->shape[0] > INT32_MAX || cols_in > INT32_MAX) return set_error(QL_ERR_UNSUPPORTED, "%s: dimension too large", op);
+  return QL_OK;
+}
+
+} // namespace
+} // namespace ql
+
+using namespace ql;
+
+extern "C" {
+
+int ql_rmsnorm_quant_fp8(const ql_tensor *x, float eps, ql_tensor *q, ql_tensor *scale, void *stream) {
+  const char *op = "rmsnorm_quant_fp8";
+  if (!x) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: null tensor", op);
+  int rc = check_rows(op, x, q, scale, x->rank == 2 ? x->shape[1] : 0, x->rank == 2 ? x->shape[1] : 0);
+  if (rc != QL_OK) return rc;
+  const int64_t T = x->shape[0], H = x->shape[1];
+  if (T == 0) return QL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (x->dtype == QL_BF16)
+    rmsnorm_quant_fp8_kernel<__nv_bfloat16><<<(unsigned)T, kRowThreads, 0, st>>>(static_cast<const __nv_bfloat16 *>(x->data), static_cast<uint8_t *>(q->data), static_cast<float *>(scale->data), (int)H, eps);
+  else
+    rmsnorm_quant_fp8_kernel<__half><<<(unsigned)T, kRowThreads, 0, st>>>(static_cast<const __half *>(x->data), static_cast<uint8_t *>(q->data), static_cast<float *>(scale->data), (int)H, eps);
+  count_launches(1);
+  QL_CUDA_TRY(cudaGetLastError());
+  return QL_OK;
+}
+
+int ql_swiglu_quant_fp8(const ql_tensor *gate_up, ql_tensor *q, ql_tensor *scale, void *stream) {
+  const char *op = "swiglu_quant_fp8";
+  if (!gate_up || !q) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: null tensor", op);
+  int rc = check_rows(op, gate_up, q, scale, q->rank == 2 ? 2 * q->shape[1] : 0, q->rank == 2 ? q->shape[1] : 0);
+  if (rc != QL_OK) return rc;
+  const int64_t T = gate_up->shape[0], I = q->shape[1];
+  if (T == 0) return QL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (gate_up->dtype == QL_BF16)
+    swiglu_quant_fp8_kernel<__nv_bfloat16><<<(unsigned)T, kRowThreads, 0, st>>>(static_cast<const __nv_bfloat16 *>(gate_up->data), static_cast<uint8_t *>(q->data), static_cast<float *>(scale->data), (int)I);
+  else
+    swiglu_quant_fp8_kernel<__half><<<(unsigned)T, kRowThreads, 0, st>>>(static_cast<const __half *>(gate_up->data), static_cast<uint8_t *>(q->data), static_cast<float *>(scale->data), (int)I);
+  count_launches(1);
+  QL_CUDA_TRY(cudaGetLastError());
+  return QL_OK;
+}
+}

@@ -160,95 +160,120 @@ wo_linear_kernel(const XT *__restrict__ X, const uint8_t *__restrict__ W, const 
     const int g = lane >> 2, t = lane & 3;
     const int row_a = min(n0 + g, N - 1), row_b = min(n0 + g + 8, N - 1);
     const int nb = (WBITS == 4) ? K / block : 0;
+    constexpr int XV = T::kElemsPerLane * 2 / 16; // 16-byte words of X per lane, row and iteration
     float acc[NT][4];
 #pragma unroll
     for (int i = 0; i < NT; i++)
 #pragma unroll
       for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
 
-    bool ok = true;
-    for (int st = 0; st < n_stages && ok; st++) {
-      const int slot = st % kStagesWo;
-      if (!wo_wait(full_bar(slot), (st / kStagesWo) & 1)) {
-        if (lane == 0) { atomicCAS(status, 0, 12); gave_up = 1; }
-        ok = false;
-        break;
-      }
-      const uint8_t *stage = ring + slot * kStageBytesWo;
+    // X does not depend on the weights arriving: the fragments of the next iteration are requested
+    // before the current one is computed, so their L1/L2 latency hides behind the math
+    auto load_x = [&](int it, uint4(&xb)[NT][XV]) {
 #pragma unroll
-      for (int half = 0; half < kItersPerStage / kWarps; half++) {
-        const int it_in = warp + half * kWarps;            // iteration inside the stage
-        const int it = st * kItersPerStage + it_in;        // iteration over the whole K
-        if (it >= n_iters) break;
-        const int kb = it * T::kStep;
-        const uint4 wa = *reinterpret_cast<const uint4 *>(stage + g * kRowPitch + it_in * 64 + t * 16);
-        const uint4 wb = *reinterpret_cast<const uint4 *>(stage + (g + 8) * kRowPitch + it_in * 64 + t * 16);
-        const uint32_t wav[4] = {wa.x, wa.y, wa.z, wa.w};
-        const uint32_t wbv[4] = {wb.x, wb.y, wb.z, wb.w};
-
-        if constexpr (WBITS == 8) {
-          uint32_t a[4][4];
+      for (int nt = 0; nt < NT; nt++) {
+        const int m = nt * 8 + g;
+        if (m < M) {
+          const uint4 *xp = reinterpret_cast<const uint4 *>(X + (int64_t)m * K + it * T::kStep + t * T::kElemsPerLane);
 #pragma unroll
-          for (int j = 0; j < 4; j++) {
-            uint32_t ua = wav[j] ^ 0x80808080u, ub = wbv[j] ^ 0x80808080u;
-            a[j][0] = int8_pair<XT, 0>(ua);
-            a[j][1] = int8_pair<XT, 0>(ub);
-            a[j][2] = int8_pair<XT, 2>(ua);
-            a[j][3] = int8_pair<XT, 2>(ub);
-          }
-#pragma unroll
-          for (int nt = 0; nt < NT; nt++) {
-            const int m = nt * 8 + g;
-            uint32_t xw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            if (m < M) {
-              const uint4 *xp = reinterpret_cast<const uint4 *>(X + (int64_t)m * K + kb + t * 16);
-              uint4 x0 = __ldg(xp), x1 = __ldg(xp + 1);
-              xw[0] = x0.x; xw[1] = x0.y; xw[2] = x0.z; xw[3] = x0.w;
-              xw[4] = x1.x; xw[5] = x1.y; xw[6] = x1.z; xw[7] = x1.w;
-            }
-#pragma unroll
-            for (int j = 0; j < 4; j++) mma16816<XT>(acc[nt], a[j][0], a[j][1], a[j][2], a[j][3], xw[2 * j], xw[2 * j + 1]);
-          }
+          for (int v = 0; v < XV; v++) xb[nt][v] = __ldg(xp + v);
         } else {
-          // int4: one iteration (128 k) lies inside one scale block (block % 128 == 0)
-          const float sa = load_scale(scale, sdt, (int64_t)row_a * nb + kb / block);
-          const float sb = load_scale(scale, sdt, (int64_t)row_b * nb + kb / block);
-          float part[NT][4];
 #pragma unroll
-          for (int i = 0; i < NT; i++)
-#pragma unroll
-            for (int j = 0; j < 4; j++) part[i][j] = 0.f;
-#pragma unroll
-          for (int j = 0; j < 4; j++) { // word j = elements 8j .. 8j+7 of this lane's 32
-            uint32_t a_lo[4], a_hi[4];
-            a_lo[0] = int4_pair<XT, 0>(wav[j]); a_lo[1] = int4_pair<XT, 0>(wbv[j]);
-            a_lo[2] = int4_pair<XT, 1>(wav[j]); a_lo[3] = int4_pair<XT, 1>(wbv[j]);
-            a_hi[0] = int4_pair<XT, 2>(wav[j]); a_hi[1] = int4_pair<XT, 2>(wbv[j]);
-            a_hi[2] = int4_pair<XT, 3>(wav[j]); a_hi[3] = int4_pair<XT, 3>(wbv[j]);
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-              const int m = nt * 8 + g;
-              uint4 xv = make_uint4(0, 0, 0, 0);
-              if (m < M) xv = __ldg(reinterpret_cast<const uint4 *>(X + (int64_t)m * K + kb + t * 32 + j * 8));
-              // x pairs (0,4) (1,5) (2,6) (3,7) to line up with the weight pairs
-              uint32_t p04 = __byte_perm(xv.x, xv.z, 0x5410), p15 = __byte_perm(xv.x, xv.z, 0x7632);
-              uint32_t p26 = __byte_perm(xv.y, xv.w, 0x5410), p37 = __byte_perm(xv.y, xv.w, 0x7632);
-              mma16816<XT>(part[nt], a_lo[0], a_lo[1], a_lo[2], a_lo[3], p04, p15);
-              mma16816<XT>(part[nt], a_hi[0], a_hi[1], a_hi[2], a_hi[3], p26, p37);
-            }
-          }
-#pragma unroll
-          for (int nt = 0; nt < NT; nt++) {
-            acc[nt][0] = fmaf(part[nt][0], sa, acc[nt][0]);
-            acc[nt][1] = fmaf(part[nt][1], sa, acc[nt][1]);
-            acc[nt][2] = fmaf(part[nt][2], sb, acc[nt][2]);
-            acc[nt][3] = fmaf(part[nt][3], sb, acc[nt][3]);
-          }
+          for (int v = 0; v < XV; v++) xb[nt][v] = make_uint4(0, 0, 0, 0);
         }
       }
-      // this warp is done with the slot: let the producer refill it
-      __syncwarp();
-      if (lane == 0 && st + kStagesWo < n_stages) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_bar(slot)) : "memory");
+    };
+    constexpr bool kPrefetch = NT * XV <= 8; // beyond that the second buffer would spill
+    uint4 xcur[NT][XV], xnext[kPrefetch ? NT : 1][XV];
+    if (kPrefetch && warp < n_iters) load_x(warp, xcur);
+    int cur_stage = -1;
+    for (int it = warp; it < n_iters; it += kWarps) {
+      const int st = it / kItersPerStage, slot = st % kStagesWo;
+      const bool more = kPrefetch && it + kWarps < n_iters;
+      if constexpr (kPrefetch) {
+        if (more) load_x(it + kWarps, xnext);
+      } else {
+        load_x(it, xcur);
+      }
+      if (st != cur_stage) {
+        if (cur_stage >= 0 && cur_stage + kStagesWo < n_stages) {
+          // this warp is done with the previous slot: let the producer refill it
+          __syncwarp();
+          if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_bar(cur_stage % kStagesWo)) : "memory");
+        }
+        if (!wo_wait(full_bar(slot), (st / kStagesWo) & 1)) {
+          if (lane == 0) { atomicCAS(status, 0, 12); gave_up = 1; }
+          break;
+        }
+        cur_stage = st;
+      }
+      const uint8_t *stage = ring + slot * kStageBytesWo;
+      const int it_in = it - st * kItersPerStage; // iteration inside the stage
+      const int kb = it * T::kStep;
+      const uint4 wa = *reinterpret_cast<const uint4 *>(stage + g * kRowPitch + it_in * 64 + t * 16);
+      const uint4 wb = *reinterpret_cast<const uint4 *>(stage + (g + 8) * kRowPitch + it_in * 64 + t * 16);
+      const uint32_t wav[4] = {wa.x, wa.y, wa.z, wa.w};
+      const uint32_t wbv[4] = {wb.x, wb.y, wb.z, wb.w};
+
+      if constexpr (WBITS == 8) {
+        uint32_t a[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          uint32_t ua = wav[j] ^ 0x80808080u, ub = wbv[j] ^ 0x80808080u;
+          a[j][0] = int8_pair<XT, 0>(ua);
+          a[j][1] = int8_pair<XT, 0>(ub);
+          a[j][2] = int8_pair<XT, 2>(ua);
+          a[j][3] = int8_pair<XT, 2>(ub);
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          const uint32_t xw[8] = {xcur[nt][0].x, xcur[nt][0].y, xcur[nt][0].z, xcur[nt][0].w,
+                                  xcur[nt][1].x, xcur[nt][1].y, xcur[nt][1].z, xcur[nt][1].w};
+#pragma unroll
+          for (int j = 0; j < 4; j++) mma16816<XT>(acc[nt], a[j][0], a[j][1], a[j][2], a[j][3], xw[2 * j], xw[2 * j + 1]);
+        }
+      } else {
+        // int4: one iteration (128 k) lies inside one scale block (block % 128 == 0)
+        const float sa = load_scale(scale, sdt, (int64_t)row_a * nb + kb / block);
+        const float sb = load_scale(scale, sdt, (int64_t)row_b * nb + kb / block);
+        float part[NT][4];
+#pragma unroll
+        for (int i = 0; i < NT; i++)
+#pragma unroll
+          for (int j = 0; j < 4; j++) part[i][j] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; j++) { // word j = elements 8j .. 8j+7 of this lane's 32
+          uint32_t a_lo[4], a_hi[4];
+          a_lo[0] = int4_pair<XT, 0>(wav[j]); a_lo[1] = int4_pair<XT, 0>(wbv[j]);
+          a_lo[2] = int4_pair<XT, 1>(wav[j]); a_lo[3] = int4_pair<XT, 1>(wbv[j]);
+          a_hi[0] = int4_pair<XT, 2>(wav[j]); a_hi[1] = int4_pair<XT, 2>(wbv[j]);
+          a_hi[2] = int4_pair<XT, 3>(wav[j]); a_hi[3] = int4_pair<XT, 3>(wbv[j]);
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++) {
+            const uint4 xv = xcur[nt][j];
+            // x pairs (0,4) (1,5) (2,6) (3,7) to line up with the weight pairs
+            uint32_t p04 = __byte_perm(xv.x, xv.z, 0x5410), p15 = __byte_perm(xv.x, xv.z, 0x7632);
+            uint32_t p26 = __byte_perm(xv.y, xv.w, 0x5410), p37 = __byte_perm(xv.y, xv.w, 0x7632);
+            mma16816<XT>(part[nt], a_lo[0], a_lo[1], a_lo[2], a_lo[3], p04, p15);
+            mma16816<XT>(part[nt], a_hi[0], a_hi[1], a_hi[2], a_hi[3], p26, p37);
+          }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          acc[nt][0] = fmaf(part[nt][0], sa, acc[nt][0]);
+          acc[nt][1] = fmaf(part[nt][1], sa, acc[nt][1]);
+          acc[nt][2] = fmaf(part[nt][2], sb, acc[nt][2]);
+          acc[nt][3] = fmaf(part[nt][3], sb, acc[nt][3]);
+        }
+      }
+      if constexpr (kPrefetch) {
+        if (more) {
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int v = 0; v < XV; v++) xcur[nt][v] = xnext[nt][v];
+        }
+      }
     }
 
     // cross-warp reduction: red[warp][row][m]

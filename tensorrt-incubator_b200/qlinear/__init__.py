@@ -5,3 +5,4 @@ from .dtypes import bfloat16, float8, float16, float32, int4, int8  # noqa: F401
 from .linear import Linear, gemm_16, gemm_fp8, gemm_i8, linear_w4a16, linear_w8a16  # noqa: F401
 from .ops import QuantizeError, amax_scale, dequantize, quantize, quantize_dequantize, quantize_to  # noqa: F401
 from .tensor import Int4Tensor  # noqa: F401
+from .mlp import QuantizedMLP, quantize_per_channel_fp8, rmsnorm_quant_fp8, shard_range, swiglu_quant_fp8  # noqa: F401

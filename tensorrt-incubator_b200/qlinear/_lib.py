@@ -58,6 +58,8 @@ SIGNATURES = {
     "ql_gemm_fp8": ([_T, _T, _T, _T, _T, _S], ctypes.c_int),
     "ql_gemm_i8": ([_T, _T, _T, _T, _T, _S], ctypes.c_int),
     "ql_gemm_16": ([_T, _T, _T, _T, _S], ctypes.c_int),
+    "ql_rmsnorm_quant_fp8": ([_T, ctypes.c_float, _T, _T, _S], ctypes.c_int),
+    "ql_swiglu_quant_fp8": ([_T, _T, _T, _S], ctypes.c_int),
     "ql_gemm_status": ([ctypes.POINTER(ctypes.c_int32)], ctypes.c_int),
 }
 

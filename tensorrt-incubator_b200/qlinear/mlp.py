@@ -1,0 +1,110 @@
+"""Quantized Llama-style MLP block (benchmark config 5), tensor-parallel over the GPUs of one box.
+
+    x -> RMSNorm (eps, weight 1) + per-token e4m3 quantize
+      -> gate/up projection (fp8 GEMM, per-token x per-output-channel scales in the epilogue)
+      -> SwiGLU + per-token e4m3 re-quantize
+      -> down projection (fp8 GEMM)  -> sum over ranks (NCCL all-reduce)
+
+Sharding follows the usual column-/row-parallel split: every rank holds `inter / world` columns of
+the gate and up projections (no exchange needed before SwiGLU) and the matching rows of the down
+projection, whose partial results are summed.  The per-token scale of the re-quantized activation
+is local to each rank's columns and is folded into that rank's down-projection epilogue, so no
+extra collective is needed.  The reference has no such block operator; its pieces are
+tensorrt.quantize / dequantize / matrix_multiply (see include/qlinear_b200.h) composed as
+tripy/nvtripy/frontend/module/linear.py:127-151 composes them."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from . import dtypes as dt
+from . import ops
+from .linear import gemm_fp8
+from .tensor import current_stream, ql_view
+
+
+def shard_range(n: int, world: int, rank: int):
+    """[begin, end) of the slice of `n` columns rank `rank` of `world` owns (n % world == 0)."""
+    if n % world:
+        raise ValueError(f"{n} columns do not split evenly over {world} ranks")
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+def quantize_per_channel_fp8(w: torch.Tensor):
+    """e4m3 weights with one f32 scale per output channel (row): scale = max|row| / 448."""
+    s = ops.amax_scale(w, dt.float8, dim=0, scale_dtype=dt.float32)
+    q = torch.empty(w.shape, dtype=torch.float8_e4m3fn, device=w.device)
+    ops.quantize_to(w, s, q, dim=0)
+    return q, s
+
+
+def rmsnorm_quant_fp8(x: torch.Tensor, eps: float, q=None, scale=None):
+    T, H = x.shape
+    q = q if q is not None else torch.empty((T, H), dtype=torch.float8_e4m3fn, device=x.device)
+    scale = scale if scale is not None else torch.empty((T,), dtype=torch.float32, device=x.device)
+    tx, tq, ts = ql_view(x), ql_view(q), ql_view(scale)
+    _lib.check(_lib.lib().ql_rmsnorm_quant_fp8(tx, float(eps), tq, ts, current_stream(x.device)))
+    return q, scale
+
+
+def swiglu_quant_fp8(gate_up: torch.Tensor, q=None, scale=None):
+    T, I2 = gate_up.shape
+    q = q if q is not None else torch.empty((T, I2 // 2), dtype=torch.float8_e4m3fn, device=gate_up.device)
+    scale = scale if scale is not None else torch.empty((T,), dtype=torch.float32, device=gate_up.device)
+    tg, tq, ts = ql_view(gate_up), ql_view(q), ql_view(scale)
+    _lib.check(_lib.lib().ql_swiglu_quant_fp8(tg, tq, ts, current_stream(gate_up.device)))
+    return q, scale
+
+
+class QuantizedMLP:
+    """One rank's shard of the block.  `w_gate`, `w_up`: [inter_local, hidden]; `w_down`: [hidden, inter_local]
+    (bf16 / f16, Linear's [out, in] layout).  Weights are quantized once, here."""
+
+    def __init__(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, eps: float = 1e-5, group=None):
+        self.eps, self.group = eps, group
+        self.hidden, self.inter_local = w_gate.shape[1], w_gate.shape[0]
+        self.out_dtype = dt.from_torch(w_gate.dtype)
+        self.wq_gu, self.s_gu = quantize_per_channel_fp8(torch.cat([w_gate, w_up], dim=0).contiguous())
+        self.wq_d, self.s_d = quantize_per_channel_fp8(w_down.contiguous())
+        self._buf = {}
+
+    def _buffers(self, T, device):
+        if self._buf.get("T") != T:
+            H, I = self.hidden, self.inter_local
+            od = self.out_dtype.torch
+            self._buf = {"T": T,
+                         "xq": torch.empty((T, H), dtype=torch.float8_e4m3fn, device=device), "sx": torch.empty((T,), dtype=torch.float32, device=device),
+                         "gu": torch.empty((T, 2 * I), dtype=od, device=device),
+                         "aq": torch.empty((T, I), dtype=torch.float8_e4m3fn, device=device), "sa": torch.empty((T,), dtype=torch.float32, device=device),
+                         "y": torch.empty((T, H), dtype=od, device=device)}
+        return self._buf
+
+    # the four local stages, separately callable so that a benchmark can time them
+    def stage_norm_quant(self, x, b):
+        rmsnorm_quant_fp8(x, self.eps, b["xq"], b["sx"])
+
+    def stage_gate_up(self, b):
+        gemm_fp8(b["xq"], self.wq_gu, b["sx"], self.s_gu, out_dtype=self.out_dtype, out=b["gu"])
+
+    def stage_swiglu_quant(self, b):
+        swiglu_quant_fp8(b["gu"], b["aq"], b["sa"])
+
+    def stage_down(self, b):
+        gemm_fp8(b["aq"], self.wq_d, b["sa"], self.s_d, out_dtype=self.out_dtype, out=b["y"])
+
+    def stage_all_reduce(self, b):
+        if self.group is not None:
+            import torch.distributed as dist
+            dist.all_reduce(b["y"], group=self.group)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        b = self._buffers(x.shape[0], x.device)
+        self.stage_norm_quant(x, b)
+        self.stage_gate_up(b)
+        self.stage_swiglu_quant(b)
+        self.stage_down(b)
+        self.stage_all_reduce(b)
+        return b["y"]
+
+    __call__ = forward
