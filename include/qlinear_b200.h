@@ -99,6 +99,24 @@ QL_API int ql_quantize_dequantize(const ql_tensor *input, const ql_tensor *scale
 QL_API int ql_amax_scale(const ql_tensor *input, ql_tensor *scale, const ql_qdq_attrs *attrs,
                          float maxbound, void *stream);
 
+/* No counterpart in the reference.  Same result as ql_amax_scale, for callers that are not allowed
+ * to allocate device memory while they run -- a runtime that planned and accounted for every buffer
+ * before execution started, or a latency-bound serving loop where an allocation might block or fail.
+ * ql_amax_scale parks its f32 max|x| accumulators in stream-ordered scratch memory when the scales
+ * are 16-bit; this variant parks them in a fixed array inside the library instead and calls no
+ * allocator of any kind.
+ *   - At most QL_NOALLOC_MAX_SCALES scales (groups) per call; more is rejected with
+ *     QL_ERR_UNSUPPORTED and a message naming the limit.  The array costs that many floats
+ *     (256 KiB) on every GPU that loads the library, until the process exits.
+ *   - The first call on each device looks up the array's device address; make that first call
+ *     before starting any stream capture on that device.
+ *   - All calls on a device share the one array (it is re-zeroed at the start of each call), so two
+ *     calls whose GPU work may overlap -- different streams without an ordering between them --
+ *     race on it.  Order them, or use ql_amax_scale for one of them. */
+#define QL_NOALLOC_MAX_SCALES 65536
+QL_API int ql_amax_scale_noalloc(const ql_tensor *input, ql_tensor *scale, const ql_qdq_attrs *attrs,
+                                 float maxbound, void *stream);
+
 /* Weight-only linear layers, Y[M,N] = X[M,K] . dequantize(W)[N,K]^T with f32 accumulation
  * (linear.py:140-151 with quant_dtype set and no input scale).
  *   w8: W int8 [N,K], scale [N] per output channel (weight_quant_dim = 0)

@@ -53,6 +53,7 @@ SIGNATURES = {
     "ql_dequantize": ([_T, _T, _T, _A, _S], ctypes.c_int),
     "ql_quantize_dequantize": ([_T, _T, _T, _T, _A, _S], ctypes.c_int),
     "ql_amax_scale": ([_T, _T, _A, ctypes.c_float, _S], ctypes.c_int),
+    "ql_amax_scale_noalloc": ([_T, _T, _A, ctypes.c_float, _S], ctypes.c_int),
     "ql_linear_w8a16": ([_T, _T, _T, _T, _S], ctypes.c_int),
     "ql_linear_w4a16": ([_T, _T, _T, _T, _S], ctypes.c_int),
     "ql_gemm_fp8": ([_T, _T, _T, _T, _T, _S], ctypes.c_int),
