@@ -366,7 +366,65 @@ class Fp8Gemm(Workload):
                 "l2": "operands and output (>= 600 MiB per GPU) exceed the 126 MiB L2", "seed": 1004}
 
 
-WORKLOADS = {"c1": QdqInt8, "c2": W8A16Linear, "c3": W4A16Linear, "c4": Fp8Gemm}
+class Fp8Mlp(Workload):
+    """Config 5: Llama-style MLP block, hidden 8192, intermediate 28672, 4096 tokens, bf16 activations,
+    fp8 e4m3 per-output-channel gate/up/down weights ~ N(0,0.02).  RMSNorm(eps 1e-5, weight 1) fused with
+    per-token fp8 quantize -> gate/up GEMM -> SwiGLU + re-quantize -> down GEMM.  With g GPUs: gate/up
+    column-parallel, down row-parallel, one NCCL all-reduce of the bf16 result (strong scaling)."""
+
+    name = "config5_fp8_mlp_block"
+    metric = "quantized GEMM TFLOP/s (config 5: fp8 e4m3 Llama-style MLP block, 4096 tokens, 8192 -> 28672 -> 8192)"
+    unit = "TFLOP/s"
+    dtype = "e4m3 x e4m3 -> f32 accumulate -> bf16"
+    T, H, I = 4096, 8192, 28672
+    use_graphs = False
+    scaling = "strong"
+
+    def __init__(self, torch, ql, device, dist=None, seed=1005):
+        self.torch, self.ql, self.device, self.dist = torch, ql, device, dist
+        self.world = dist.get_world_size() if dist is not None else 1
+        self.rank = dist.get_rank() if dist is not None else 0
+        self.parallelism = f"tensor-parallel over {self.world} GPUs: gate/up column-parallel, down row-parallel, NCCL all-reduce"
+        il = self.I // self.world
+        self.il = il
+        g = torch.Generator(device=device).manual_seed(seed * 100 + self.rank)   # this rank's shard of the random weights
+        def w(shape):
+            return (torch.randn(shape, generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        self.mlp = ql.QuantizedMLP(w((il, self.H)), w((il, self.H)), w((self.H, il)), eps=1e-5, group=(dist.group.WORLD if dist is not None else None))
+        gx = torch.Generator(device="cpu").manual_seed(seed)
+        self.x_host = torch.randn((self.T, self.H), generator=gx, dtype=torch.float32).to(torch.bfloat16).pin_memory()
+        self.x = self.x_host.to(device)
+        self.buf = self.mlp._buffers(self.T, device)
+        self.y_host = torch.empty((self.T, self.H), dtype=torch.bfloat16).pin_memory()
+
+    def parts(self):
+        T, H, il = self.T, self.H, self.il
+        ps = [("rmsnorm_quant", lambda: self.mlp.stage_norm_quant(self.x, self.buf), 0, 3 * T * H + 4 * T, "hbm"),
+              ("gate_up_gemm", lambda: self.mlp.stage_gate_up(self.buf), 2 * T * H * 2 * il, T * H + 2 * il * H + 2 * T * 2 * il, "tensor_fp8"),
+              ("swiglu_quant", lambda: self.mlp.stage_swiglu_quant(self.buf), 0, 2 * T * 2 * il + T * il, "hbm"),
+              ("down_gemm", lambda: self.mlp.stage_down(self.buf), 2 * T * il * H, T * il + H * il + 2 * T * H, "tensor_fp8")]
+        if self.world > 1:
+            ps.append(("all_reduce_y", lambda: self.mlp.stage_all_reduce(self.buf), 0, 2 * 2 * T * H * (self.world - 1) // self.world, "nvlink"))
+        return ps
+
+    def step_flops_global(self):
+        return 3 * 2 * self.T * self.H * self.I
+
+    def e2e_step(self):
+        self.x.copy_(self.x_host, non_blocking=True)
+        y = self.mlp(self.x)
+        self.y_host.copy_(y, non_blocking=True)
+
+    def e2e_bytes(self):
+        return self.T * self.H * 2, self.T * self.H * 2
+
+    def config(self):
+        return {"workload": self.name, "tokens": self.T, "hidden": self.H, "intermediate": self.I, "intermediate_per_gpu": self.il,
+                "weights": "e4m3 per output channel, quantized once", "activations": "per-token e4m3, scale = row amax/448",
+                "l2": "weights and activations (>= 150 MiB per GPU) exceed the 126 MiB L2", "seed": 1005}
+
+
+WORKLOADS = {"c1": QdqInt8, "c2": W8A16Linear, "c3": W4A16Linear, "c4": Fp8Gemm, "c5": Fp8Mlp}
 
 
 # ----------------------------------------------------------------------------------------------
@@ -430,6 +488,26 @@ def cpu_reference(workload: str, budget_s: float = 12.0):
         mm, nn = int(min(M, max(m_s, m_s * grow))), int(min(N, max(n_s, n_s * grow)))
         dt = sample(mm, nn)
         return 2.0 * mm * nn * K / dt / 1e12, "TFLOP/s", cores, f"{mm} of {M} rows x {nn} of {N} columns x K={K}, f32 accumulation, {dt:.1f} s"
+    if workload == "c5":
+        T, H, I = 4096, 8192, 28672
+        t_s, i_s = 16, 128
+        def sample(tt, ii):
+            x = orc.from_f32(rng.standard_normal((tt, H)).astype(np.float32), orc.BF16)
+            wgu = rng.integers(0, 0x70, size=(2 * ii, H), dtype=np.uint8)
+            wd = rng.integers(0, 0x70, size=(H, ii), dtype=np.uint8)
+            sgu = np.full(2 * ii, 1e-3, dtype=np.float32)
+            sd = np.full(H, 1e-3, dtype=np.float32)
+            t0 = time.perf_counter()
+            xq, sx = orc.rmsnorm_quant_fp8(x, orc.BF16, 1e-5)
+            gu = orc.gemm_fp8(xq, wgu, sx, sgu, orc.BF16, acc64=False)
+            aq, sa = orc.swiglu_quant_fp8(gu, orc.BF16)
+            orc.gemm_fp8(aq, wd, sa, sd, orc.BF16, acc64=False)
+            return time.perf_counter() - t0
+        t1 = sample(t_s, i_s)
+        grow = (budget_s / max(t1, 1e-4)) ** 0.5
+        tt, ii = int(min(T, max(t_s, t_s * grow))), int(min(I, max(i_s, i_s * grow)))
+        dt = sample(tt, ii)
+        return 3 * 2.0 * tt * H * ii / dt / 1e12, "TFLOP/s", cores, f"{tt} of {T} tokens x {ii} of {I} intermediate columns, hidden {H}, f32 accumulation, {dt:.1f} s"
     if workload == "c1":
         n = 1 << 22
         x = rng.standard_normal(n).astype(np.float32)

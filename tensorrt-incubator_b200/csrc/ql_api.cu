@@ -79,8 +79,13 @@ int launch_scale_from_amax(const float *amax, void *scale, int sdt, int64_t n, f
 int launch_wo_linear(int wbits, int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M,
                      int N, int K, int block, cudaStream_t st);
 
-int launch_w8a16_large(int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M, int N, int K,
+// ql_gemm_w8a16.cu
+int launch_w8a16_fused(int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M, int N, int K,
                        cudaStream_t st);
+int launch_w8a16_widen(int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M, int N, int K,
+                       cudaStream_t st);
+// Above this many rows the product is compute-bound and the separate widening pass is the cheaper route.
+constexpr int kFusedWidenMaxRows = 256;
 // ql_gemm_tc.cu
 int gemm16_device(int dtype, const void *X, const void *W, const float *sb, int sb_n, void *Y, int M, int N, int K,
                   cudaStream_t st);
@@ -333,8 +338,11 @@ int ql_linear_w8a16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *sca
                      "%s: For per-channel quantization, expected the scales tensor dimension to match the "
                      "quantization axis dimension of input tensor", op);
   if (K % 64 != 0) return set_error(QL_ERR_UNSUPPORTED, "%s: K must be a multiple of 64 (got %lld)", op, (long long)K);
+  if (M > kFusedWidenMaxRows)
+    return launch_w8a16_widen(x->dtype, x->data, w->data, scale->data, scale->dtype, y->data, (int)M, (int)N, (int)K,
+                              (cudaStream_t)stream);
   if (M > kWeightOnlyMaxRows)
-    return launch_w8a16_large(x->dtype, x->data, w->data, scale->data, scale->dtype, y->data, (int)M, (int)N, (int)K,
+    return launch_w8a16_fused(x->dtype, x->data, w->data, scale->data, scale->dtype, y->data, (int)M, (int)N, (int)K,
                               (cudaStream_t)stream);
   return launch_wo_linear(8, x->dtype, x->data, w->data, scale->data, scale->dtype, y->data, (int)M, (int)N, (int)K, 0,
                           (cudaStream_t)stream);

@@ -17,141 +17,18 @@
 // Every wait is bounded: when a limit runs out the kernel records a code in `status`, stops
 // issuing work, drains what it issued and returns.
 #include <cuda.h>
+#include <cstdlib>
 
 #include "ql_common.cuh"
+#include "ql_tc_common.cuh"
 
 namespace ql {
 namespace {
 
-enum { KIND_F8 = 0, KIND_I8 = 1, KIND_BF16 = 2, KIND_F16 = 3 };
-
-constexpr int BM = 128;
-constexpr int BK_BYTES = 128; // one 128-byte swizzle row of K per stage
 constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * BK_BYTES;
 constexpr int kGemmThreads = 192;
-constexpr long long kWaitLimitCycles = 1ll << 31; // about a second
 
-// status codes written by the kernel
-enum { ST_OK = 0, ST_TIMEOUT_EMPTY = 1, ST_TIMEOUT_FULL = 2, ST_TIMEOUT_TMEM_EMPTY = 3, ST_TIMEOUT_TMEM_FULL = 4, ST_TIMEOUT_DRAIN = 5 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile("{\n\t.reg .pred p;\n\t"
-               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-               "selp.b32 %0, 1, 0, p;\n\t}"
-               : "=r"(done)
-               : "r"(bar), "r"(parity)
-               : "memory");
-  return done != 0;
-}
-// Bounded wait.  Gives up after kWaitLimitCycles or as soon as another role has given up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (*abort_flag != 0) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
-      *abort_flag = code;
-      atomicCAS(status, 0, code);
-      return false;
-    }
-  }
-  return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
-               : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte
-// swizzle TMA applies: groups of 8 rows are 1024 bytes apart (stride byte offset), the leading
-// byte offset is unused for swizzled K-major layouts, descriptor version 1, layout type 2.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr >> 4) & 0x3FFF);
-  d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-
-template <int KIND, int BN>
-__device__ __forceinline__ uint32_t make_instr_desc() {
-  uint32_t d = 0;
-  if (KIND == KIND_I8) {
-    d |= 2u << 4;              // accumulate in s32
-    d |= 1u << 7 | 1u << 10;   // signed 8-bit A and B
-  } else {
-    d |= 1u << 4;              // accumulate in f32
-    if (KIND == KIND_BF16) d |= 1u << 7 | 1u << 10;
-    // e4m3 and f16 are format 0 of their kinds
-  }
-  // both operands K-major: bits 15 and 16 stay 0
-  d |= (uint32_t)(BN >> 3) << 17;
-  d |= (uint32_t)(BM >> 4) << 24;
-  return d;
-}
-
-template <int KIND>
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  if constexpr (KIND == KIND_F8) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-  } else if constexpr (KIND == KIND_I8) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-  } else {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-  }
-}
-
-__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-               : "r"(taddr)
-               : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-template <typename OutT> __device__ __forceinline__ uint32_t pack2(float a, float b);
-template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t *>(&v);
-}
-template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
-  __half2 v = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t *>(&v);
-}
 
 struct GemmArgs {
   void *Y;
@@ -360,39 +237,295 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // ----------------------------------------------------------------------------------------------
 // host side
 // ----------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// ----------------------------------------------------------------------------------------------
+// Two-CTA variant (cta_group::2): a pair of CTAs on neighbouring SMs forms a cluster and computes a
+// 256 x 256 tile with one M=256 MMA stream issued by the pair's leader.  Each CTA loads its own 128
+// rows of A and its own half (128 rows) of the B tile, so a stage is 32 KiB instead of 48 KiB: six
+// stages fit, and L2 -> shared-memory traffic per flop drops by a third.  No load is multicast: every
+// CTA fetches what it needs itself and signals the leader's "full" barrier (the .cta_group::2 form of
+// the tile load allows the barrier to live in the pair's other CTA).
+// ----------------------------------------------------------------------------------------------
+constexpr int STAGES2 = 6;
+constexpr int BN2 = 256;
+constexpr int B2_STAGE_BYTES = (BN2 / 2) * BK_BYTES;
+constexpr int STAGE2_BYTES = A_STAGE_BYTES + B2_STAGE_BYTES;
 
-int get_encode_fn(EncodeTiledFn *out) {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void *p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    QL_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
-    if (q != cudaDriverEntryPointSuccess || !p) return set_error(QL_ERR_NO_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
-    fn = reinterpret_cast<EncodeTiledFn>(p);
+struct Smem2 {
+  static constexpr int kTiles = STAGES2 * STAGE2_BYTES;
+  static constexpr int kBarriers = kTiles;                   // full[S], empty[S], tfull[2], tempty[2], drain
+  static constexpr int kTmemPtr = kBarriers + (2 * STAGES2 + 5) * 8;
+  static constexpr int kAbort = kTmemPtr + 4;
+  static constexpr int kTotal = kAbort + 4;
+  static constexpr int kDynamic = kTotal + 1024;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t leader_bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+template <int KIND>
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  if constexpr (KIND == KIND_F8) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  } else if constexpr (KIND == KIND_I8) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  } else {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
   }
-  *out = fn;
-  return QL_OK;
 }
 
-// [rows, K] row-major matrix of `esize`-byte elements, box = [box_rows, 128 bytes], 128-byte swizzle
-int make_map(CUtensorMap *map, int kind, const void *ptr, int64_t rows, int64_t K, int box_rows) {
-  EncodeTiledFn enc;
-  int rc = get_encode_fn(&enc);
-  if (rc != QL_OK) return rc;
-  const int esize = (kind == KIND_F8 || kind == KIND_I8) ? 1 : 2;
-  CUtensorMapDataType dt = (kind == KIND_F8 || kind == KIND_I8) ? CU_TENSOR_MAP_DATA_TYPE_UINT8
-                           : (kind == KIND_BF16)                ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)K * esize};
-  cuuint32_t box[2] = {(cuuint32_t)(BK_BYTES / esize), (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return set_error(QL_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+template <int KIND>
+__device__ __forceinline__ uint32_t make_instr_desc_pair() {
+  // same fields as the one-CTA descriptor with M = 256
+  uint32_t d = make_instr_desc<KIND, BN2>();
+  d &= ~(0x1Fu << 24);
+  d |= (uint32_t)(256 >> 4) << 24;
+  return d;
+}
+
+// args.tiles_m counts 256-row tiles here; args.tiles_n counts 256-column tiles.
+template <int KIND, typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs args) {
+  using L = Smem2;
+  constexpr uint32_t kTmemCols = 512; // two 256-column accumulators
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::kBarriers;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES2 + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES2 + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES2 + 2 + b); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * STAGES2 + 4);
+  volatile uint32_t *tmem_ptr_smem = reinterpret_cast<volatile uint32_t *>(smem + L::kTmemPtr);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  const int num_tiles = args.tiles_m * args.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; s++) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 8); // four epilogue warps in each CTA of the pair
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_ptr_smem)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all(); // the partner's barriers exist before anything is signalled across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        int mt, nt;
+        tile_coords(args, tile, &mt, &nt);
+        const int m0 = mt * 256 + (int)rank * BM, n0 = nt * BN2 + (int)rank * (BN2 / 2);
+        for (int kb = 0; kb < args.num_kb; kb++) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          const uint32_t a_dst = smem_base + stage * STAGE2_BYTES, b_dst = a_dst + A_STAGE_BYTES;
+          const uint32_t leader_full = map_to_cta(full_bar(stage), 0);
+          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * STAGE2_BYTES); // both CTAs' bytes land on the leader's barrier
+          tma_load_2d_pair(a_dst, &map_a, leader_full, kb * args.k_elems_per_block, m0);
+          tma_load_2d_pair(b_dst, &map_b, leader_full, kb * args.k_elems_per_block, n0);
+          issued++;
+          if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+        }
+      }
+      (void)issued;
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_instr_desc_pair<KIND>();
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, it++) {
+        const int buf = it & 1;
+        if (!mbar_wait(tempty_bar(buf), ((it >> 1) & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN2);
+        for (int kb = 0; kb < args.num_kb; kb++) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * STAGE2_BYTES;
+          const uint64_t adesc = make_smem_desc(a_addr), bdesc = make_smem_desc(a_addr + A_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK_BYTES / 32; k++)
+            tc_mma_pair<KIND>(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          // the stage is free in both CTAs once these MMAs have read it
+          tc_commit_pair(map_to_cta(empty_bar(stage), 0));
+          tc_commit_pair(map_to_cta(empty_bar(stage), 1));
+          if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+        }
+        if (ok) {
+          tc_commit_pair(map_to_cta(tfull_bar(buf), 0));
+          tc_commit_pair(map_to_cta(tfull_bar(buf), 1));
+        }
+      }
+      tc_commit_pair(map_to_cta(drain_bar, 0));
+      const long long t0 = clock64();
+      while (!mbar_try_wait(drain_bar, 0)) {
+        if (clock64() - t0 > kWaitLimitCycles) { atomicCAS(args.status, 0, ST_TIMEOUT_DRAIN); break; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quad = warp & 3;
+    OutT *Y = static_cast<OutT *>(args.Y);
+    const bool vec_ok = (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
+    int it = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, it++) {
+      const int buf = it & 1;
+      int mt, nt;
+      tile_coords(args, tile, &mt, &nt);
+      const int m0 = mt * 256 + (int)rank * BM, n0 = nt * BN2;
+      if (!mbar_wait(tfull_bar(buf), (it >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int m = m0 + quad * 32 + lane;
+      float sa = 1.f;
+      if (args.sa) sa = (args.sa_n == 1) ? __ldg(args.sa) : (m < args.M ? __ldg(args.sa + m) : 0.f);
+      const float sb_scalar = (args.sb && args.sb_n == 1) ? __ldg(args.sb) : 1.f;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN2);
+#pragma unroll 1
+      for (int c = 0; c < BN2 / 32; c++) {
+        uint32_t r[32];
+        tmem_load_32(taddr + c * 32, r);
+        const int n = n0 + c * 32;
+        if (m < args.M && n < args.N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            float acc = (KIND == KIND_I8) ? (float)(int)r[j] : __uint_as_float(r[j]);
+            float s = sa * sb_scalar;
+            if (args.sb && args.sb_n != 1) s = sa * ((n + j < args.N) ? __ldg(args.sb + n + j) : 0.f);
+            v[j] = acc * s;
+          }
+          OutT *row = Y + (size_t)m * args.N + n;
+          if (vec_ok && n + 32 <= args.N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 o = make_uint4(pack2<OutT>(v[j], v[j + 1]), pack2<OutT>(v[j + 2], v[j + 3]),
+                                   pack2<OutT>(v[j + 4], v[j + 5]), pack2<OutT>(v[j + 6], v[j + 7]));
+              __stcs(reinterpret_cast<uint4 *>(row + j), o);
+            }
+          } else {
+            for (int j = 0; j < 32 && n + j < args.N; j++) row[j] = FloatIO<OutT>::from_f32(v[j]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0)); // the leader owns the accumulator hand-over
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all(); // neither CTA may leave while the pair's MMAs or barriers can still touch it
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// Largest number of CTA pairs that can be resident at once on this device (0 = pairs unavailable).
+template <int KIND, typename OutT>
+int max_resident_pairs() {
+  static int cached[64] = {0};
+  static bool known[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (!known[dev]) {
+    auto kern = gemm_tc2_kernel<KIND, OutT>;
+    int n = 0;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2::kDynamic) == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2 * sm_count(), 1, 1);
+      cfg.blockDim = dim3(kGemmThreads, 1, 1);
+      cfg.dynamicSmemBytes = Smem2::kDynamic;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) n = 0;
+      cudaGetLastError();
+    }
+    cached[dev] = n;
+    known[dev] = true;
+  }
+  return cached[dev];
+}
+
+template <int KIND, typename OutT>
+int launch_gemm_pair(const void *A, const void *B, GemmArgs args, int64_t K, int pairs, cudaStream_t st) {
+  CUtensorMap ma, mb;
+  int rc;
+  if ((rc = make_map(&ma, KIND, A, args.M, K, BM)) != QL_OK) return rc;
+  if ((rc = make_map(&mb, KIND, B, args.N, K, BN2 / 2)) != QL_OK) return rc;
+  args.tiles_m = (args.M + 255) / 256;
+  args.tiles_n = (args.N + BN2 - 1) / BN2;
+  args.group_m = (args.group_m + 1) / 2; // bands were sized in 128-row tiles
+  if (args.group_m < 1) args.group_m = 1;
+  if (args.group_m > args.tiles_m) args.group_m = args.tiles_m;
+  const int tiles = args.tiles_m * args.tiles_n;
+  const int clusters = tiles < pairs ? tiles : pairs;
+  gemm_tc2_kernel<KIND, OutT><<<2 * clusters, kGemmThreads, Smem2::kDynamic, st>>>(ma, mb, args);
+  count_launches(1);
+  QL_CUDA_TRY(cudaGetLastError());
   return QL_OK;
 }
 
@@ -419,6 +552,11 @@ int launch_gemm_bn(const CUtensorMap &ma, const CUtensorMap &mb, GemmArgs args, 
 template <int KIND, typename OutT>
 int launch_gemm_kind(const void *A, const void *B, GemmArgs args, int64_t K, cudaStream_t st) {
   const int sms = sm_count();
+  if (args.M > 256 && args.N >= 512 && !getenv("QL_GEMM_ONE_CTA")) {
+    const int pairs = max_resident_pairs<KIND, OutT>();
+    const long long tiles2 = (long long)((args.M + 255) / 256) * ((args.N + BN2 - 1) / BN2);
+    if (pairs > 0 && tiles2 >= pairs) return launch_gemm_pair<KIND, OutT>(A, B, args, K, pairs, st);
+  }
   int bn = 32;
   for (int cand : {256, 128, 64}) {
     if ((int64_t)args.tiles_m * ((args.N + cand - 1) / cand) >= sms) { bn = cand; break; }

@@ -1,0 +1,389 @@
+// W8A16 linear for large batches on the tcgen05 tensor cores, weights dequantized inside the kernel:
+//     Y[M,N] = (X[M,K] . Wq[N,K]^T) * scale[n],  X bf16|f16, Wq int8, f32 accumulation in tensor memory.
+// The int8 weights are read from HBM exactly once, as int8.  Per pipeline stage TMA brings a
+// [128 x 64] tile of X (128-byte swizzle) and the raw [BN x 64] int8 tile of W; four converter warps
+// widen the weights to the activation type (exact: |q| <= 128 fits the significand) and store them in
+// the 128-byte-swizzled K-major layout the MMA's shared-memory descriptor expects, fence the writes
+// for the async proxy and signal the MMA warp.  The per-channel scale is applied to the f32
+// accumulator in the epilogue, which equals scaling every weight first up to f32 rounding
+// (reference composition: quantize -> dequantize -> matmul, tripy/nvtripy/frontend/module/linear.py:140-151).
+//
+// Warps: 0 TMA producer, 1 TMEM owner + MMA issuer, 2-5 epilogue, 6-9 converters.  All waits bounded.
+#include <cuda/std/type_traits>
+
+#include "ql_common.cuh"
+#include "ql_tc_common.cuh"
+
+namespace ql {
+namespace {
+
+constexpr int kW8Threads = 320;
+constexpr int kConvThreads = 128;
+constexpr int BKE = 64; // k elements per stage: 128 bytes of X, 64 bytes of int8 W
+
+template <int BN> struct W8Smem {
+  static constexpr int kA = BM * BK_BYTES;
+  static constexpr int kConv = BN * BK_BYTES;
+  static constexpr int kRaw = BN * BKE;
+  static constexpr int kStage = kA + kConv + kRaw; // a multiple of 1024 for BN % 16 == 0
+  static constexpr int kStagesFit = (200 * 1024) / kStage;
+  static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
+  static constexpr int kTiles = kStages * kStage;
+  static constexpr int kBarriers = kTiles;                       // full[S], empty[S], ready[S], tfull[2], tempty[2], drain
+  static constexpr int kTmemPtr = kBarriers + (3 * kStages + 5) * 8;
+  static constexpr int kAbort = kTmemPtr + 4;
+  static constexpr int kTotal = kAbort + 4;
+  static constexpr int kDynamic = kTotal + 1024;
+};
+
+struct W8Args {
+  void *Y;
+  const void *scale; // per output channel, f32 | f16 | bf16
+  int sdt;
+  int M, N, num_kb;
+  int tiles_m, tiles_n, group_m;
+  int *status;
+};
+
+__device__ __forceinline__ void w8_tile_coords(const W8Args &a, int tile, int *mt, int *nt) {
+  const int per_group = a.group_m * a.tiles_n;
+  const int grp = tile / per_group;
+  const int first_m = grp * a.group_m;
+  const int gsz = min(a.group_m, a.tiles_m - first_m);
+  const int local = tile - grp * per_group;
+  *mt = first_m + local % gsz;
+  *nt = local / gsz;
+}
+
+// bytes I, I+1 of u (int8 + 128) -> exact pair of XT (same trick as the small-batch kernel)
+template <typename XT, int I>
+__device__ __forceinline__ uint32_t widen_pair(uint32_t u) {
+  if constexpr (cuda::std::is_same<XT, __half>::value) {
+    uint32_t v = __byte_perm(u, 0x64646464u, 0x4040 | I | ((I + 1) << 8));
+    __half2 h = __hsub2(*reinterpret_cast<__half2 *>(&v), __half2half2(__ushort_as_half(0x6480)));
+    return *reinterpret_cast<uint32_t *>(&h);
+  } else {
+    float lo = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540 | I)) - 8388736.f;
+    float hi = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540 | (I + 1))) - 8388736.f;
+    __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&b);
+  }
+}
+
+template <typename XT, int BN>
+__global__ void __launch_bounds__(kW8Threads, 1)
+gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const W8Args args) {
+  using L = W8Smem<BN>;
+  constexpr int S = L::kStages;
+  constexpr int KIND = cuda::std::is_same<XT, __half>::value ? KIND_F16 : KIND_BF16;
+  constexpr uint32_t kTmemCols = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::kBarriers;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
+  auto ready_bar = [&](int s) { return bar_base + 8u * (2 * S + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (3 * S + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (3 * S + 2 + b); };
+  const uint32_t drain_bar = bar_base + 8u * (3 * S + 4);
+  volatile uint32_t *tmem_ptr_smem = reinterpret_cast<volatile uint32_t *>(smem + L::kTmemPtr);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = args.tiles_m * args.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; s++) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+      mbar_init(ready_bar(s), kConvThreads / 32); // one arrival per converter warp
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 4);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_ptr_smem)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int mt, nt;
+        w8_tile_coords(args, tile, &mt, &nt);
+        for (int kb = 0; kb < args.num_kb; kb++) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          const uint32_t a_dst = smem_base + stage * L::kStage, raw_dst = a_dst + L::kA + L::kConv;
+          mbar_expect_tx(full_bar(stage), L::kA + L::kRaw);
+          tma_load_2d(a_dst, &map_x, full_bar(stage), kb * BKE, mt * BM);
+          tma_load_2d(raw_dst, &map_w, full_bar(stage), kb * BKE, nt * BN);
+          issued++;
+          if (++stage == S) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        const long long pending = issued < S ? issued : S;
+        for (long long i = 0; i < pending; i++) {
+          stage = (stage == 0) ? S - 1 : stage - 1;
+          if (stage == S - 1) phase ^= 1;
+          const long long t0 = clock64();
+          while (!mbar_try_wait(full_bar(stage), phase) && clock64() - t0 < kWaitLimitCycles) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_instr_desc<KIND, BN>();
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, it++) {
+        const int buf = it & 1;
+        if (!mbar_wait(tempty_bar(buf), ((it >> 1) & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < args.num_kb; kb++) {
+          if (!mbar_wait(ready_bar(stage), phase, abort_flag, args.status, ST_TIMEOUT_READY)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * L::kStage;
+          const uint64_t adesc = make_smem_desc(a_addr), bdesc = make_smem_desc(a_addr + L::kA);
+#pragma unroll
+          for (int k = 0; k < BK_BYTES / 32; k++)
+            tc_mma<KIND>(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          tc_commit(empty_bar(stage));
+          if (++stage == S) { stage = 0; phase ^= 1; }
+        }
+        if (ok) tc_commit(tfull_bar(buf));
+      }
+      tc_commit(drain_bar);
+      const long long t0 = clock64();
+      while (!mbar_try_wait(drain_bar, 0)) {
+        if (clock64() - t0 > kWaitLimitCycles) { atomicCAS(args.status, 0, ST_TIMEOUT_DRAIN); break; }
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------------ converters (warps 6..9)
+    const int ctid = threadIdx.x - 6 * 32;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int kb = 0; kb < args.num_kb; kb++) {
+        if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+        uint8_t *conv = smem + stage * L::kStage + L::kA;
+        const uint8_t *raw = conv + L::kConv;
+#pragma unroll 2
+        for (int idx = ctid; idx < BN * 4; idx += kConvThreads) {
+          const int r = idx >> 2, c = idx & 3;
+          const uint4 w = *reinterpret_cast<const uint4 *>(raw + r * BKE + c * 16);
+          const uint32_t u0 = w.x ^ 0x80808080u, u1 = w.y ^ 0x80808080u, u2 = w.z ^ 0x80808080u, u3 = w.w ^ 0x80808080u;
+          const uint4 lo = make_uint4(widen_pair<XT, 0>(u0), widen_pair<XT, 2>(u0), widen_pair<XT, 0>(u1), widen_pair<XT, 2>(u1));
+          const uint4 hi = make_uint4(widen_pair<XT, 0>(u2), widen_pair<XT, 2>(u2), widen_pair<XT, 0>(u3), widen_pair<XT, 2>(u3));
+          uint8_t *row = conv + r * BK_BYTES;
+          const int sw = r & 7; // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
+          *reinterpret_cast<uint4 *>(row + (((2 * c) ^ sw) << 4)) = lo;
+          *reinterpret_cast<uint4 *>(row + (((2 * c + 1) ^ sw) << 4)) = hi;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ready_bar(stage));
+        if (++stage == S) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;
+    XT *Y = static_cast<XT *>(args.Y);
+    const bool vec_ok = (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, it++) {
+      const int buf = it & 1;
+      int mt, nt;
+      w8_tile_coords(args, tile, &mt, &nt);
+      const int m0 = mt * BM, n0 = nt * BN;
+      if (!mbar_wait(tfull_bar(buf), (it >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int m = m0 + quad * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 16; c++) {
+        uint32_t r[16];
+        tmem_load_16(taddr + c * 16, r);
+        const int n = n0 + c * 16;
+        if (m < args.M && n < args.N) {
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]) * ((n + j < args.N) ? load_scale(args.scale, args.sdt, n + j) : 0.f);
+          XT *row = Y + (size_t)m * args.N + n;
+          if (vec_ok && n + 16 <= args.N) {
+            __stcs(reinterpret_cast<uint4 *>(row), make_uint4(pack2<XT>(v[0], v[1]), pack2<XT>(v[2], v[3]), pack2<XT>(v[4], v[5]), pack2<XT>(v[6], v[7])));
+            __stcs(reinterpret_cast<uint4 *>(row + 8), make_uint4(pack2<XT>(v[8], v[9]), pack2<XT>(v[10], v[11]), pack2<XT>(v[12], v[13]), pack2<XT>(v[14], v[15])));
+          } else {
+            for (int j = 0; j < 16 && n + j < args.N; j++) row[j] = FloatIO<XT>::from_f32(v[j]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(buf));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+template <typename XT, int BN>
+int launch_w8_bn(const CUtensorMap &mx, const CUtensorMap &mw, W8Args args, cudaStream_t st) {
+  using L = W8Smem<BN>;
+  auto kern = gemm_w8a16_kernel<XT, BN>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  QL_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    QL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic));
+    configured[dev] = true;
+  }
+  const int tiles = args.tiles_m * args.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, kW8Threads, L::kDynamic, st>>>(mx, mw, args);
+  count_launches(1);
+  QL_CUDA_TRY(cudaGetLastError());
+  return QL_OK;
+}
+
+template <typename XT>
+int launch_w8_t(const void *X, const void *W, const void *scale, int sdt, void *Y, int M, int N, int K, cudaStream_t st) {
+  constexpr int KIND = cuda::std::is_same<XT, __half>::value ? KIND_F16 : KIND_BF16;
+  W8Args args;
+  args.Y = Y;
+  args.scale = scale;
+  args.sdt = sdt;
+  args.M = M;
+  args.N = N;
+  args.num_kb = K / BKE;
+  args.tiles_m = (M + BM - 1) / BM;
+  args.status = device_status_word();
+  if (!args.status) return set_error(QL_ERR_CUDA, "linear_w8a16: could not allocate the device status word");
+  // pick the column-tile width: waves of tiles over the SMs times the bytes a tile pulls per k-block
+  const int sms = sm_count();
+  int best_bn = 256;
+  long long best_cost = -1;
+  for (int bn : {256, 128, 96, 80, 64, 48, 32}) {
+    const long long tiles = (long long)args.tiles_m * ((N + bn - 1) / bn);
+    const long long waves = (tiles + sms - 1) / sms;
+    const long long cost = waves * (BM + bn);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_bn = bn; }
+  }
+  args.tiles_n = (N + best_bn - 1) / best_bn;
+  {
+    const long long band = (16ll << 20) / ((long long)BM * K * 2);
+    args.group_m = (int)(band < 4 ? 4 : band);
+    if (args.group_m > args.tiles_m) args.group_m = args.tiles_m;
+  }
+  CUtensorMap mx, mw;
+  int rc;
+  if ((rc = make_map(&mx, KIND, X, M, K, BM)) != QL_OK) return rc;
+  if ((rc = make_map_bytes(&mw, W, N, K, BKE, best_bn)) != QL_OK) return rc;
+  switch (best_bn) {
+  case 256: return launch_w8_bn<XT, 256>(mx, mw, args, st);
+  case 128: return launch_w8_bn<XT, 128>(mx, mw, args, st);
+  case 96: return launch_w8_bn<XT, 96>(mx, mw, args, st);
+  case 80: return launch_w8_bn<XT, 80>(mx, mw, args, st);
+  case 64: return launch_w8_bn<XT, 64>(mx, mw, args, st);
+  case 48: return launch_w8_bn<XT, 48>(mx, mw, args, st);
+  default: return launch_w8_bn<XT, 32>(mx, mw, args, st);
+  }
+}
+
+// int8 -> f16 / bf16, exact; 16 values per thread
+template <typename XT>
+__global__ void __launch_bounds__(256) widen_i8_kernel(const uint8_t *__restrict__ w, XT *__restrict__ out, int64_t n16) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n16) return;
+  const uint4 raw = __ldcs(reinterpret_cast<const uint4 *>(w) + i);
+  const uint32_t v[4] = {raw.x ^ 0x80808080u, raw.y ^ 0x80808080u, raw.z ^ 0x80808080u, raw.w ^ 0x80808080u};
+  reinterpret_cast<uint4 *>(out)[2 * i] = make_uint4(widen_pair<XT, 0>(v[0]), widen_pair<XT, 2>(v[0]), widen_pair<XT, 0>(v[1]), widen_pair<XT, 2>(v[1]));
+  reinterpret_cast<uint4 *>(out)[2 * i + 1] = make_uint4(widen_pair<XT, 0>(v[2]), widen_pair<XT, 2>(v[2]), widen_pair<XT, 0>(v[3]), widen_pair<XT, 2>(v[3]));
+}
+
+__global__ void __launch_bounds__(256) scale_to_f32_kernel(const void *__restrict__ s, int sdt, float *__restrict__ out, int n) {
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i < n) out[i] = load_scale(s, sdt, i);
+}
+
+// Grow-only scratch buffer per device for the widened weights (allocated with cudaMalloc on first
+// use or growth, so the first call of a given size must not happen inside a stream capture; calls
+// on different streams that may overlap would share it and must be ordered by the caller).
+int widen_workspace(size_t bytes, uint8_t **out) {
+  static uint8_t *buf[64] = {nullptr};
+  static size_t cap[64] = {0};
+  int dev = 0;
+  QL_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return set_error(QL_ERR_UNSUPPORTED, "linear_w8a16: device index %d out of range", dev);
+  if (cap[dev] < bytes) {
+    if (buf[dev]) QL_CUDA_TRY(cudaFree(buf[dev]));
+    buf[dev] = nullptr;
+    cap[dev] = 0;
+    QL_CUDA_TRY(cudaMalloc(&buf[dev], bytes));
+    cap[dev] = bytes;
+  }
+  *out = buf[dev];
+  return QL_OK;
+}
+
+} // namespace
+
+int gemm16_device(int dtype, const void *X, const void *W, const float *sb, int sb_n, void *Y, int M, int N, int K,
+                  cudaStream_t st);
+
+// Compute-bound batches: widen the weights once per call into scratch (exact) and run the plain 16-bit
+// tcgen05 GEMM with the per-channel scales in its epilogue.  The in-kernel conversion above is bound by
+// its converter warps once the MMA work per weight grows, so it serves the memory-bound range only.
+int launch_w8a16_widen(int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M, int N, int K,
+                       cudaStream_t st) {
+  const int64_t n = (int64_t)N * K;
+  const size_t wide_bytes = (size_t)n * 2, scale_off = (wide_bytes + 255) & ~size_t(255);
+  uint8_t *scratch = nullptr;
+  int rc = widen_workspace(scale_off + (size_t)N * sizeof(float), &scratch);
+  if (rc != QL_OK) return rc;
+  float *sf = reinterpret_cast<float *>(scratch + scale_off);
+  const int64_t n16 = n / 16; // K % 64 == 0
+  if (xdt == QL_F16) widen_i8_kernel<__half><<<(unsigned)((n16 + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t *>(W), reinterpret_cast<__half *>(scratch), n16);
+  else widen_i8_kernel<__nv_bfloat16><<<(unsigned)((n16 + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t *>(W), reinterpret_cast<__nv_bfloat16 *>(scratch), n16);
+  scale_to_f32_kernel<<<(N + 255) / 256, 256, 0, st>>>(scale, sdt, sf, N);
+  count_launches(2);
+  QL_CUDA_TRY(cudaGetLastError());
+  return gemm16_device(xdt, X, scratch, sf, N, Y, M, N, K, st);
+}
+
+// Y = (X . Wq^T) * scale[n] with the int8 -> 16-bit conversion inside the kernel (K % 64 == 0).
+int launch_w8a16_fused(int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M, int N, int K,
+                       cudaStream_t st) {
+  if (xdt == QL_F16) return launch_w8_t<__half>(X, W, scale, sdt, Y, M, N, K, st);
+  return launch_w8_t<__nv_bfloat16>(X, W, scale, sdt, Y, M, N, K, st);
+}
+
+} // namespace ql

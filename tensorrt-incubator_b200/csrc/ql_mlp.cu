@@ -86,10 +86,12 @@ rmsnorm_quant_fp8_kernel(const XT *__restrict__ X, uint8_t *__restrict__ Q, floa
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdiv_rn(g, 1.f + expf(-g)) * u; }
 
 // One block per token.  GU holds [gate | up] (I columns each); a = silu(gate) * up in f32;
-// s = max|a| / 448; q = e4m3(a / s).
-template <typename XT>
+// s = max|a| / 448; q = e4m3(a / s).  The f32 products of the first pass are parked in shared
+// memory (kCache) so that expf runs once per element; rows too long for that are recomputed.
+template <typename XT, bool kCache>
 __global__ void __launch_bounds__(kRowThreads)
 swiglu_quant_fp8_kernel(const XT *__restrict__ GU, uint8_t *__restrict__ Q, float *__restrict__ S, int I) {
+  extern __shared__ __align__(16) float a_cache[];
   const int64_t row = blockIdx.x;
   const XT *g = GU + row * 2 * I, *u = g + I;
   uint8_t *q = Q + row * I;
@@ -100,7 +102,15 @@ swiglu_quant_fp8_kernel(const XT *__restrict__ GU, uint8_t *__restrict__ Q, floa
     load_vec_f32<XT, 16>(g + c * 16, gv);
     load_vec_f32<XT, 16>(u + c * 16, uv);
 #pragma unroll
-    for (int j = 0; j < 16; j++) amax = fmaxf(amax, fabsf(silu_mul(gv[j], uv[j])));
+    for (int j = 0; j < 16; j++) {
+      const float a = silu_mul(gv[j], uv[j]);
+      amax = fmaxf(amax, fabsf(a));
+      gv[j] = a;
+    }
+    if constexpr (kCache) {
+#pragma unroll
+      for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4 *>(a_cache + c * 16 + j) = make_float4(gv[j], gv[j + 1], gv[j + 2], gv[j + 3]);
+    }
   }
   __shared__ float part[kRowThreads / 32];
   __shared__ float s_scale;
@@ -118,17 +128,48 @@ swiglu_quant_fp8_kernel(const XT *__restrict__ GU, uint8_t *__restrict__ Q, floa
   __syncthreads();
   const float s = s_scale;
   for (int c = threadIdx.x; c < n_chunks; c += kRowThreads) {
-    float gv[16], uv[16];
-    load_vec_f32<XT, 16>(g + c * 16, gv);
-    load_vec_f32<XT, 16>(u + c * 16, uv);
+    float av[16];
+    if constexpr (kCache) {
+#pragma unroll
+      for (int j = 0; j < 16; j += 4) {
+        const float4 t = *reinterpret_cast<const float4 *>(a_cache + c * 16 + j);
+        av[j] = t.x; av[j + 1] = t.y; av[j + 2] = t.z; av[j + 3] = t.w;
+      }
+    } else {
+      float gv[16], uv[16];
+      load_vec_f32<XT, 16>(g + c * 16, gv);
+      load_vec_f32<XT, 16>(u + c * 16, uv);
+#pragma unroll
+      for (int j = 0; j < 16; j++) av[j] = silu_mul(gv[j], uv[j]);
+    }
     uint32_t w[4] = {0, 0, 0, 0};
 #pragma unroll
-    for (int j = 0; j < 16; j += 2) {
-      const float a = __fdiv_rn(silu_mul(gv[j], uv[j]), s), b = __fdiv_rn(silu_mul(gv[j + 1], uv[j + 1]), s);
-      w[j >> 2] |= (f32x2_to_e4m3x2(a, b) & 0xFFFFu) << (8 * (j & 3));
-    }
+    for (int j = 0; j < 16; j += 2)
+      w[j >> 2] |= (f32x2_to_e4m3x2(__fdiv_rn(av[j], s), __fdiv_rn(av[j + 1], s)) & 0xFFFFu) << (8 * (j & 3));
     __stcs(reinterpret_cast<uint4 *>(q) + c, make_uint4(w[0], w[1], w[2], w[3]));
   }
+}
+
+template <typename XT>
+int launch_swiglu(const void *gu, void *q, void *s, int64_t T, int64_t I, cudaStream_t st) {
+  const size_t cache_bytes = (size_t)I * sizeof(float);
+  const XT *g = static_cast<const XT *>(gu);
+  if (cache_bytes <= 200 * 1024) {
+    auto kern = swiglu_quant_fp8_kernel<XT, true>;
+    static bool configured[64] = {false};
+    int dev = 0;
+    QL_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+      QL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      configured[dev] = true;
+    }
+    kern<<<(unsigned)T, kRowThreads, cache_bytes, st>>>(g, static_cast<uint8_t *>(q), static_cast<float *>(s), (int)I);
+  } else {
+    swiglu_quant_fp8_kernel<XT, false><<<(unsigned)T, kRowThreads, 0, st>>>(g, static_cast<uint8_t *>(q), static_cast<float *>(s), (int)I);
+  }
+  count_launches(1);
+  QL_CUDA_TRY(cudaGetLastError());
+  return QL_OK;
 }
 
 int check_rows(const char *op, const ql_tensor *x, const ql_tensor *q, const ql_tensor *s, int64_t cols_in, int64_t cols_out) {
@@ -176,12 +217,7 @@ int ql_swiglu_quant_fp8(const ql_tensor *gate_up, ql_tensor *q, ql_tensor *scale
   const int64_t T = gate_up->shape[0], I = q->shape[1];
   if (T == 0) return QL_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  if (gate_up->dtype == QL_BF16)
-    swiglu_quant_fp8_kernel<__nv_bfloat16><<<(unsigned)T, kRowThreads, 0, st>>>(static_cast<const __nv_bfloat16 *>(gate_up->data), static_cast<uint8_t *>(q->data), static_cast<float *>(scale->data), (int)I);
-  else
-    swiglu_quant_fp8_kernel<__half><<<(unsigned)T, kRowThreads, 0, st>>>(static_cast<const __half *>(gate_up->data), static_cast<uint8_t *>(q->data), static_cast<float *>(scale->data), (int)I);
-  count_launches(1);
-  QL_CUDA_TRY(cudaGetLastError());
-  return QL_OK;
+  if (gate_up->dtype == QL_BF16) return launch_swiglu<__nv_bfloat16>(gate_up->data, q->data, scale->data, T, I, st);
+  return launch_swiglu<__half>(gate_up->data, q->data, scale->data, T, I, st);
 }
 }

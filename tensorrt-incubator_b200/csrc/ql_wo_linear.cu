@@ -9,12 +9,13 @@
 // extracts (elements e and e+4 of a word) are matched by permuting the X registers.
 //
 // One block owns 16 output channels.  A producer warp streams their weights into a shared-memory
-// ring with bulk asynchronous copies; 8 consumer warps split K and reduce through shared memory.
+// ring with TMA tile loads; 8 consumer warps split K and reduce through shared memory.
 // Reference composition this implements: tripy/nvtripy/frontend/module/linear.py:140-151
 // (quantize -> dequantize -> x @ transpose(w)) with the dequantize folded into the product.
 #include <cuda/std/type_traits>
 
 #include "ql_common.cuh"
+#include "ql_tc_common.cuh"
 
 namespace ql {
 namespace {
@@ -75,11 +76,12 @@ template <int WBITS> struct WoTraits {
   static constexpr int kStep = 4 * kElemsPerLane;         // k covered by one warp iteration (64 bytes of a row)
 };
 
-// Shared-memory ring of weight slabs.  A stage holds kChunkBytes of each of the 16 rows; rows are
-// padded by 64 bytes so that the two rows one quarter-warp reads fall into different banks.
+// Shared-memory ring of weight slabs.  A stage holds kChunkBytes of each of the 16 rows, brought by
+// one TMA tile request (a [16 x 1024 B] box; many small requests would be bound by the copy engine's
+// per-request cost, not by HBM).
 constexpr int kStagesWo = 4;
 constexpr int kChunkBytes = 1024;
-constexpr int kRowPitch = kChunkBytes + 64;
+constexpr int kRowPitch = kChunkBytes;
 constexpr int kStageBytesWo = kRowsPerBlock * kRowPitch;
 constexpr int kItersPerStage = kChunkBytes / 64;
 constexpr long long kWoWaitLimit = 1ll << 31;
@@ -101,17 +103,16 @@ __device__ __forceinline__ bool wo_wait(uint32_t bar, uint32_t parity) {
 }
 
 // NT = number of 8-row tiles of X handled at once (M <= 8 * NT).
-// Warps 0..7 consume; warp 8 streams the block's 16 weight rows from HBM into the ring with bulk
-// asynchronous copies (one per row and stage), so HBM latency is hidden by the copy engine's
-// queue instead of by registers.
+// Warps 0..7 consume; warp 8 streams the block's 16 weight rows from HBM into the ring with one TMA
+// tile request per stage, so HBM latency is hidden by the copy engine's queue instead of by registers.
 template <typename XT, int WBITS, int NT>
 __global__ void __launch_bounds__(kThreadsWo + 32)
-wo_linear_kernel(const XT *__restrict__ X, const uint8_t *__restrict__ W, const void *__restrict__ scale, int sdt,
+wo_linear_kernel(const __grid_constant__ CUtensorMap map_w, const XT *__restrict__ X, const void *__restrict__ scale, int sdt,
                  XT *__restrict__ Y, int M, int N, int K, int block, int *status) {
   using T = WoTraits<WBITS>;
-  extern __shared__ __align__(128) uint8_t wo_smem[];
-  uint8_t *ring = wo_smem;
-  float(*red)[kRowsPerBlock][NT * 8 + 1] = reinterpret_cast<float(*)[kRowsPerBlock][NT * 8 + 1]>(wo_smem + kStagesWo * kStageBytesWo);
+  extern __shared__ uint8_t wo_smem_raw[];
+  uint8_t *ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(wo_smem_raw) + 127) & ~uintptr_t(127));
+  float(*red)[kRowsPerBlock][NT * 8 + 1] = reinterpret_cast<float(*)[kRowsPerBlock][NT * 8 + 1]>(ring + kStagesWo * kStageBytesWo);
   __shared__ __align__(8) uint64_t bars[2 * kStagesWo];
   __shared__ int gave_up;
 
@@ -143,16 +144,9 @@ wo_linear_kernel(const XT *__restrict__ X, const uint8_t *__restrict__ W, const 
           atomicCAS(status, 0, 11);
           break;
         }
-        const int64_t off = (int64_t)st * kChunkBytes;
-        const uint32_t bytes = (uint32_t)((row_bytes - off) < kChunkBytes ? (row_bytes - off) : kChunkBytes);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_bar(slot)), "r"(bytes * kRowsPerBlock) : "memory");
-        for (int r = 0; r < kRowsPerBlock; r++) {
-          const int row = min(n0 + r, N - 1);
-          const uint8_t *src = W + (int64_t)row * row_bytes + off;
-          const uint32_t dst = wo_smem_u32(ring + slot * kStageBytesWo + r * kRowPitch);
-          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                       ::"r"(dst), "l"(src), "r"(bytes), "r"(full_bar(slot)) : "memory");
-        }
+        // out-of-range rows and bytes past the end of a row arrive as zeros; the whole box counts as bytes
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_bar(slot)), "r"((uint32_t)kStageBytesWo) : "memory");
+        tma_load_2d(wo_smem_u32(ring + slot * kStageBytesWo), &map_w, full_bar(slot), st * (kChunkBytes / 4), n0);
       }
     }
   } else {
@@ -299,10 +293,10 @@ wo_linear_kernel(const XT *__restrict__ X, const uint8_t *__restrict__ W, const 
   }
 }
 
-template <int NT> constexpr int wo_dynamic_smem() { return kStagesWo * kStageBytesWo + kWarps * kRowsPerBlock * (NT * 8 + 1) * 4; }
+template <int NT> constexpr int wo_dynamic_smem() { return 128 + kStagesWo * kStageBytesWo + kWarps * kRowsPerBlock * (NT * 8 + 1) * 4; }
 
 template <typename XT, int WBITS, int NT>
-int launch_wo_nt(const XT *xp, const uint8_t *wp, const void *scale, int sdt, XT *yp, int mc, int N, int K, int block,
+int launch_wo_nt(const CUtensorMap &map_w, const XT *xp, const void *scale, int sdt, XT *yp, int mc, int N, int K, int block,
                  int *status, unsigned grid, cudaStream_t st) {
   auto kern = wo_linear_kernel<XT, WBITS, NT>;
   constexpr int smem = wo_dynamic_smem<NT>();
@@ -313,7 +307,7 @@ int launch_wo_nt(const XT *xp, const uint8_t *wp, const void *scale, int sdt, XT
     QL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured[dev] = true;
   }
-  kern<<<grid, kThreadsWo + 32, smem, st>>>(xp, wp, scale, sdt, yp, mc, N, K, block, status);
+  kern<<<grid, kThreadsWo + 32, smem, st>>>(map_w, xp, scale, sdt, yp, mc, N, K, block, status);
   count_launches(1);
   return QL_OK;
 }
@@ -324,65 +318,38 @@ int launch_wo_t(const void *X, const void *W, const void *scale, int sdt, void *
   const unsigned grid = (unsigned)((N + kRowsPerBlock - 1) / kRowsPerBlock);
   int *status = device_status_word();
   if (!status) return set_error(QL_ERR_CUDA, "weight-only linear: could not allocate the device status word");
+  // the weights as a [N, row_bytes / 4] matrix of 32-bit words: one box = 16 rows x 1024 bytes
+  CUtensorMap map_w;
+  {
+    EncodeTiledFn enc;
+    int rc = get_encode_fn(&enc);
+    if (rc != QL_OK) return rc;
+    const int64_t row_bytes = (int64_t)K * WBITS / 8;
+    cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 4), (cuuint64_t)N};
+    cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)(kChunkBytes / 4), (cuuint32_t)kRowsPerBlock};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(W), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(QL_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  }
   // batches larger than 32 rows are walked in slices; the weights of the later slices come from L2
   for (int m0 = 0; m0 < M; m0 += 32) {
     const int mc = min(32, M - m0);
     const XT *xp = static_cast<const XT *>(X) + (int64_t)m0 * K;
     XT *yp = static_cast<XT *>(Y) + (int64_t)m0 * N;
-    const uint8_t *wp = static_cast<const uint8_t *>(W);
     int rc;
-    if (mc <= 8) rc = launch_wo_nt<XT, WBITS, 1>(xp, wp, scale, sdt, yp, mc, N, K, block, status, grid, st);
-    else if (mc <= 16) rc = launch_wo_nt<XT, WBITS, 2>(xp, wp, scale, sdt, yp, mc, N, K, block, status, grid, st);
-    else rc = launch_wo_nt<XT, WBITS, 4>(xp, wp, scale, sdt, yp, mc, N, K, block, status, grid, st);
+    if (mc <= 8) rc = launch_wo_nt<XT, WBITS, 1>(map_w, xp, scale, sdt, yp, mc, N, K, block, status, grid, st);
+    else if (mc <= 16) rc = launch_wo_nt<XT, WBITS, 2>(map_w, xp, scale, sdt, yp, mc, N, K, block, status, grid, st);
+    else rc = launch_wo_nt<XT, WBITS, 4>(map_w, xp, scale, sdt, yp, mc, N, K, block, status, grid, st);
     if (rc != QL_OK) return rc;
   }
   QL_CUDA_TRY(cudaGetLastError());
   return QL_OK;
 }
 
-// int8 -> f16 / bf16, exact (|v| <= 128 fits both significands); 16 values per thread
-template <typename XT>
-__global__ void __launch_bounds__(256) widen_i8_kernel(const uint8_t *__restrict__ w, XT *__restrict__ out, int64_t n16) {
-  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-  if (i >= n16) return;
-  const uint4 raw = __ldcs(reinterpret_cast<const uint4 *>(w) + i);
-  const uint32_t v[4] = {raw.x ^ 0x80808080u, raw.y ^ 0x80808080u, raw.z ^ 0x80808080u, raw.w ^ 0x80808080u};
-  uint4 lo = make_uint4(int8_pair<XT, 0>(v[0]), int8_pair<XT, 2>(v[0]), int8_pair<XT, 0>(v[1]), int8_pair<XT, 2>(v[1]));
-  uint4 hi = make_uint4(int8_pair<XT, 0>(v[2]), int8_pair<XT, 2>(v[2]), int8_pair<XT, 0>(v[3]), int8_pair<XT, 2>(v[3]));
-  reinterpret_cast<uint4 *>(out)[2 * i] = lo;
-  reinterpret_cast<uint4 *>(out)[2 * i + 1] = hi;
-}
-
-__global__ void __launch_bounds__(256) scale_to_f32_kernel(const void *__restrict__ s, int sdt, float *__restrict__ out, int n) {
-  const int i = blockIdx.x * 256 + threadIdx.x;
-  if (i < n) out[i] = load_scale(s, sdt, i);
-}
-
 } // namespace
-
-// Large batches: the weights are widened to the activation type in scratch memory (exact) and the
-// product runs on the tcgen05 GEMM with the per-channel scales in its epilogue.
-int gemm16_device(int dtype, const void *X, const void *W, const float *sb, int sb_n, void *Y, int M, int N, int K,
-                  cudaStream_t st);
-
-int launch_w8a16_large(int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M, int N, int K,
-                       cudaStream_t st) {
-  const int64_t n = (int64_t)N * K;
-  const size_t wide_bytes = (size_t)n * 2, scale_off = (wide_bytes + 255) & ~size_t(255);
-  uint8_t *scratch = nullptr;
-  keep_scratch_pool_warm();
-  QL_CUDA_TRY(cudaMallocAsync(&scratch, scale_off + (size_t)N * sizeof(float), st));
-  float *sf = reinterpret_cast<float *>(scratch + scale_off);
-  const int64_t n16 = n / 16; // K % 64 == 0
-  if (xdt == QL_F16) widen_i8_kernel<__half><<<(unsigned)((n16 + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t *>(W), reinterpret_cast<__half *>(scratch), n16);
-  else widen_i8_kernel<__nv_bfloat16><<<(unsigned)((n16 + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t *>(W), reinterpret_cast<__nv_bfloat16 *>(scratch), n16);
-  scale_to_f32_kernel<<<(N + 255) / 256, 256, 0, st>>>(scale, sdt, sf, N);
-  count_launches(2);
-  int rc = gemm16_device(xdt, X, scratch, sf, N, Y, M, N, K, st);
-  cudaError_t fe = cudaFreeAsync(scratch, st);
-  if (rc == QL_OK && fe != cudaSuccess) return cuda_error(fe, "cudaFreeAsync");
-  return rc;
-}
 
 int launch_wo_linear(int wbits, int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M,
                      int N, int K, int block, cudaStream_t st) {

