@@ -7,7 +7,7 @@
 // both quantized, and of tensorrt.matrix_multiply (TensorRTOps.td:1986-2080) for 16-bit operands.
 //
 // One persistent CTA per SM, 6 warps:
-//   warp 0   one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
+//   warp 0   one lane issues TMA tile loads (128-byte swizzle; every CTA fetches its own tiles)
 //            into a 4-stage ring of [128 x 128 B] A tiles and [BN x 128 B] B tiles
 //   warp 1   allocates tensor memory; one lane issues tcgen05.mma (M=128, N=BN, K=32 bytes) from
 //            shared-memory descriptors and commits to the ring's "empty" barriers and to the
@@ -241,7 +241,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // Two-CTA variant (cta_group::2): a pair of CTAs on neighbouring SMs forms a cluster and computes a
 // 256 x 256 tile with one M=256 MMA stream issued by the pair's leader.  Each CTA loads its own 128
 // rows of A and its own half (128 rows) of the B tile, so a stage is 32 KiB instead of 48 KiB: six
-// stages fit, and L2 -> shared-memory traffic per flop drops by a third.  No load is multicast: every
+// stages fit, and L2 -> shared-memory traffic per flop drops by a third.  Every
 // CTA fetches what it needs itself and signals the leader's "full" barrier (the .cta_group::2 form of
 // the tile load allows the barrier to live in the pair's other CTA).
 // ----------------------------------------------------------------------------------------------
@@ -627,6 +627,7 @@ int run_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_te
     // a band of A of about 16 MiB stays L2-resident while B streams through
     const int64_t band = (16ll << 20) / ((int64_t)BM * K * esize);
     args.group_m = (int)(band < 4 ? 4 : band);
+    if (const char *e = getenv("QL_GEMM_GROUP_M")) args.group_m = atoi(e) > 0 ? atoi(e) : args.group_m; // tuning aid
     if (args.group_m > args.tiles_m) args.group_m = args.tiles_m;
   }
   args.status = device_status_word();
