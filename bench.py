@@ -351,6 +351,29 @@ class Fp8Gemm(Workload):
     def step_flops_global(self):
         return 2 * self.M * self.K * self.N
 
+    def compare(self, steps):
+        """Library kernels on the same operands, same box, same run (comparison only, never the product
+        path): cuBLASLt fp8 through torch._scaled_mm."""
+        torch = self.torch
+        out = {}
+        try:
+            one = torch.tensor(1.0, device=self.device)
+            fn = lambda: torch._scaled_mm(self.xq, self.wq.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            for _ in range(3):
+                fn()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            for _ in range(steps):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / steps
+            out["cublaslt_fp8_scaled_mm"] = {"ms": ms, "TFLOP/s": 2 * self.M * self.K * self.nl / ms / 1e9}
+        except Exception as e:  # comparison is best effort
+            out["cublaslt_fp8_scaled_mm"] = {"error": repr(e)[:200]}
+        return out
+
     def e2e_step(self):
         self.x.copy_(self.x_host, non_blocking=True)
         for _, fn, _, _, _ in self.parts():
@@ -559,6 +582,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--compare", action="store_true", help="also time library kernels on the same operands (comparison only)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -615,12 +639,14 @@ def main():
                 run_step()
             launches_per_step = L.ql_launch_count() - c0
             step_graphs.append(g)
+        # per part: one graph holding `rot` launches, one per buffer rotation, so that launches sit back to
+        # back on the device as they do inside a real program's graph
         for p, (_, fn, _, _, _) in enumerate(parts):
-            for _ in range(rot):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(rot):
                     fn()
-                part_graphs[p].append(g)
+            part_graphs[p] = g
         stream = torch.cuda.current_stream(device)
         for g in step_graphs:  # one untimed replay each
             g.replay()
@@ -650,15 +676,23 @@ def main():
     for p, (_, fn, _, _, _) in enumerate(parts):
         a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
-        a_.record(stream)
-        for s_ in range(K):
-            if part_graphs:
-                part_graphs[p][s_ % rot].replay()
-            else:
+        if part_graphs:
+            reps = max(1, (K + rot - 1) // rot)
+            part_graphs[p].replay()
+            barrier()
+            a_.record(stream)
+            for _ in range(reps):
+                part_graphs[p].replay()
+            b_.record(stream)
+            barrier()
+            part_ms.append(a_.elapsed_time(b_) / (reps * rot))
+        else:
+            a_.record(stream)
+            for _ in range(K):
                 fn()
-        b_.record(stream)
-        barrier()
-        part_ms.append(a_.elapsed_time(b_) / K)
+            b_.record(stream)
+            barrier()
+            part_ms.append(a_.elapsed_time(b_) / K)
     clock_info = clocks.stop()
 
     # -------- end to end: inputs from pinned host memory, results read back, every step
@@ -723,6 +757,8 @@ def main():
             "clocks": clock_info, "gpu_launches": int(launches),
             "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / K},
             "roofline": roofline, "parts": per_part}
+    if args.compare and hasattr(wl, "compare"):
+        line["comparison"] = wl.compare(K)
     if not args.no_cpu_baseline and world == 1:
         v, u, cores, sample = cpu_reference(args.workload)
         line["cpu_baseline"] = {"value": v, "unit": u, "cores": cores, "kind": "port", "sample": sample}

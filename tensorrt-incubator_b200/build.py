@@ -73,5 +73,36 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+TVMFFI_LIB = os.path.join(HERE, "lib", "libqlinear_b200_tvmffi.so")
+
+
+def build_tvm_ffi_plugin(force: bool = False):
+    """The TVM-FFI plug-in library (csrc_tvmffi/), built only where the tvm_ffi package is installed.
+    It links libqlinear_b200.so and libtvm_ffi.so; returns its path or None."""
+    try:
+        import tvm_ffi
+    except Exception:
+        return None
+    root = os.path.dirname(tvm_ffi.__file__)
+    inc, libdir = os.path.join(root, "include"), os.path.join(root, "lib")
+    src = os.path.join(HERE, "csrc_tvmffi", "ql_tvm_ffi.cc")
+    if not (os.path.exists(os.path.join(inc, "tvm", "ffi", "c_api.h")) and os.path.exists(os.path.join(libdir, "libtvm_ffi.so"))):
+        return None
+    if not force and _newer(TVMFFI_LIB, [src, LIB, os.path.join(ROOT, "include", "qlinear_b200.h")]):
+        return TVMFFI_LIB
+    gxx = shutil.which("g++") or "g++"
+    cmd = [gxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-I", inc, "-I", os.path.join(ROOT, "include"),
+           src, "-o", TVMFFI_LIB, "-L", os.path.dirname(LIB), "-lqlinear_b200", "-L", libdir, "-ltvm_ffi",
+           "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + libdir]
+    env = dict(os.environ)
+    env.pop("CC", None)
+    env.pop("CXX", None)
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("building the TVM-FFI plug-in failed:\n" + r.stdout + r.stderr)
+    return TVMFFI_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_tvm_ffi_plugin(force="--force" in sys.argv))

@@ -55,18 +55,19 @@ __device__ __forceinline__ void w8_tile_coords(const W8Args &a, int tile, int *m
   *nt = local / gsz;
 }
 
-// bytes I, I+1 of u (int8 + 128) -> exact pair of XT (same trick as the small-batch kernel)
+// bytes I, I+1 of w (two's-complement int8) -> exact pair of XT (same tricks as the small-batch kernel)
 template <typename XT, int I>
-__device__ __forceinline__ uint32_t widen_pair(uint32_t u) {
+__device__ __forceinline__ uint32_t widen_pair(uint32_t w) {
   if constexpr (cuda::std::is_same<XT, __half>::value) {
-    uint32_t v = __byte_perm(u, 0x64646464u, 0x4040 | I | ((I + 1) << 8));
+    uint32_t v = __byte_perm(w ^ 0x80808080u, 0x64646464u, 0x4040 | I | ((I + 1) << 8));
     __half2 h = __hsub2(*reinterpret_cast<__half2 *>(&v), __half2half2(__ushort_as_half(0x6480)));
     return *reinterpret_cast<uint32_t *>(&h);
   } else {
-    float lo = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540 | I)) - 8388736.f;
-    float hi = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540 | (I + 1))) - 8388736.f;
-    __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&b);
+    const uint32_t w16 = __byte_perm(w, 0u, 0x4140 + I * 0x0101);
+    uint32_t y = (w16 & 0x007F007Fu) | 0x43004300u; // 128 + low seven bits
+    uint32_t c = (w16 & 0x00800080u) | 0x43004300u; // 128, or 256 when the sign bit is set
+    __nv_bfloat162 d = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&y), *reinterpret_cast<__nv_bfloat162 *>(&c));
+    return *reinterpret_cast<uint32_t *>(&d);
   }
 }
 
@@ -193,7 +194,7 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         for (int idx = ctid; idx < BN * 4; idx += kConvThreads) {
           const int r = idx >> 2, c = idx & 3;
           const uint4 w = *reinterpret_cast<const uint4 *>(raw + r * BKE + c * 16);
-          const uint32_t u0 = w.x ^ 0x80808080u, u1 = w.y ^ 0x80808080u, u2 = w.z ^ 0x80808080u, u3 = w.w ^ 0x80808080u;
+          const uint32_t u0 = w.x, u1 = w.y, u2 = w.z, u3 = w.w;
           const uint4 lo = make_uint4(widen_pair<XT, 0>(u0), widen_pair<XT, 2>(u0), widen_pair<XT, 0>(u1), widen_pair<XT, 2>(u1));
           const uint4 hi = make_uint4(widen_pair<XT, 0>(u2), widen_pair<XT, 2>(u2), widen_pair<XT, 0>(u3), widen_pair<XT, 2>(u3));
           uint8_t *row = conv + r * BK_BYTES;
@@ -324,7 +325,7 @@ __global__ void __launch_bounds__(256) widen_i8_kernel(const uint8_t *__restrict
   const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
   if (i >= n16) return;
   const uint4 raw = __ldcs(reinterpret_cast<const uint4 *>(w) + i);
-  const uint32_t v[4] = {raw.x ^ 0x80808080u, raw.y ^ 0x80808080u, raw.z ^ 0x80808080u, raw.w ^ 0x80808080u};
+  const uint32_t v[4] = {raw.x, raw.y, raw.z, raw.w};
   reinterpret_cast<uint4 *>(out)[2 * i] = make_uint4(widen_pair<XT, 0>(v[0]), widen_pair<XT, 2>(v[0]), widen_pair<XT, 0>(v[1]), widen_pair<XT, 2>(v[1]));
   reinterpret_cast<uint4 *>(out)[2 * i + 1] = make_uint4(widen_pair<XT, 0>(v[2]), widen_pair<XT, 2>(v[2]), widen_pair<XT, 0>(v[3]), widen_pair<XT, 2>(v[3]));
 }
