@@ -550,6 +550,8 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun pins OMP_NUM_THREADS=1 for its children; this arm is meant to use every host thread
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     wl = WORKLOADS[args.workload]
     vals = []
     sample = ""

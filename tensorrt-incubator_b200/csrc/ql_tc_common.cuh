@@ -40,11 +40,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                : "memory");
   return done != 0;
 }
+// try_wait with a suspend-time hint: the thread may sleep in hardware for up to `ns` nanoseconds and is
+// woken as soon as the phase completes, instead of re-issuing the probe in a tight loop.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t done;
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+               "selp.b32 %0, 1, 0, p;\n\t}"
+               : "=r"(done)
+               : "r"(bar), "r"(parity), "r"(ns)
+               : "memory");
+  return done != 0;
+}
 // Bounded wait.  Gives up after kWaitLimitCycles or as soon as another role has given up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
+  while (!mbar_try_wait_hint(bar, parity, 20000u)) {
     if (*abort_flag != 0) return false;
     if (clock64() - t0 > kWaitLimitCycles) {
       *abort_flag = code;
