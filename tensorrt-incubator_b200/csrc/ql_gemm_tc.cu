@@ -240,12 +240,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // ----------------------------------------------------------------------------------------------
 // Two-CTA variant (cta_group::2): a pair of CTAs on neighbouring SMs forms a cluster and computes a
 // 256 x 256 tile with one M=256 MMA stream issued by the pair's leader.  Each CTA loads its own 128
-// rows of A and its own half (128 rows) of the B tile, so a stage is 32 KiB instead of 48 KiB: six
+// rows of A and its own half (128 rows) of the B tile, so a stage is 32 KiB instead of 48 KiB: seven
 // stages fit, and L2 -> shared-memory traffic per flop drops by a third.  Every
 // CTA fetches what it needs itself and signals the leader's "full" barrier (the .cta_group::2 form of
 // the tile load allows the barrier to live in the pair's other CTA).
 // ----------------------------------------------------------------------------------------------
-constexpr int STAGES2 = 6;
+constexpr int STAGES2 = 7;
 constexpr int BN2 = 256;
 constexpr int B2_STAGE_BYTES = (BN2 / 2) * BK_BYTES;
 constexpr int STAGE2_BYTES = A_STAGE_BYTES + B2_STAGE_BYTES;
