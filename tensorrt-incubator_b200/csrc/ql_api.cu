@@ -3,6 +3,7 @@
 // entry returns QL_ERR_NO_DEVICE / QL_ERR_CUDA.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <atomic>
 #include <mutex>
@@ -338,7 +339,9 @@ int ql_linear_w8a16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *sca
                      "%s: For per-channel quantization, expected the scales tensor dimension to match the "
                      "quantization axis dimension of input tensor", op);
   if (K % 64 != 0) return set_error(QL_ERR_UNSUPPORTED, "%s: K must be a multiple of 64 (got %lld)", op, (long long)K);
-  if (M > kFusedWidenMaxRows)
+  int fused_max = kFusedWidenMaxRows;
+  if (const char *e = getenv("QL_W8_FUSED_MAX_M")) fused_max = atoi(e); // tuning aid
+  if (M > fused_max)
     return launch_w8a16_widen(x->dtype, x->data, w->data, scale->data, scale->dtype, y->data, (int)M, (int)N, (int)K,
                               (cudaStream_t)stream);
   if (M > kWeightOnlyMaxRows)

@@ -479,21 +479,224 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   }
 }
 
-// Largest number of CTA pairs that can be resident at once on this device (0 = pairs unavailable).
+// ----------------------------------------------------------------------------------------------
+// Wide two-CTA variant: the pair computes a 256 x 512 tile as two 256-column halves that share the
+// A tile.  The one-tile-per-pair kernel above is bound by L2 -> shared-memory bandwidth (about 10 TB/s
+// measured on B200: 64 KiB per 2*256*256*128 MACs); doubling the tile's width moves 96 KiB per twice
+// the work, a quarter less per flop.  Tensor memory then holds exactly one accumulator (512 columns),
+// so instead of two buffers the two halves are handed over separately: the epilogue frees half 0 while
+// it still drains half 1, and the next tile's MMAs into half 0 may start.
+// ----------------------------------------------------------------------------------------------
+constexpr int STAGESW = 4;
+constexpr int STAGEW_BYTES = A_STAGE_BYTES + 2 * B2_STAGE_BYTES; // A + both halves' share of B = 48 KiB
+
+struct SmemW {
+  static constexpr int kTiles = STAGESW * STAGEW_BYTES;
+  static constexpr int kBarriers = kTiles;                   // full[S], empty[S], tfull[2], tempty[2], drain
+  static constexpr int kTmemPtr = kBarriers + (2 * STAGESW + 5) * 8;
+  static constexpr int kAbort = kTmemPtr + 4;
+  static constexpr int kTotal = kAbort + 4;
+  static constexpr int kDynamic = kTotal + 1024;
+};
+
+// args.tiles_m counts 256-row tiles, args.tiles_n 512-column tiles.
 template <int KIND, typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_tc2w_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs args) {
+  using L = SmemW;
+  constexpr uint32_t kTmemCols = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::kBarriers;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGESW + s); };
+  auto tfull_bar = [&](int h) { return bar_base + 8u * (2 * STAGESW + h); };
+  auto tempty_bar = [&](int h) { return bar_base + 8u * (2 * STAGESW + 2 + h); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * STAGESW + 4);
+  volatile uint32_t *tmem_ptr_smem = reinterpret_cast<volatile uint32_t *>(smem + L::kTmemPtr);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  const int num_tiles = args.tiles_m * args.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGESW; s++) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int h = 0; h < 2; h++) {
+      mbar_init(tfull_bar(h), 1);
+      mbar_init(tempty_bar(h), 8);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_ptr_smem)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  // a tile whose second half lies entirely beyond N uses one half only
+  auto halves_of = [&](int nt) { return (nt * 512 + 256 < args.N) ? 2 : 1; };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        int mt, nt;
+        tile_coords(args, tile, &mt, &nt);
+        const int halves = halves_of(nt);
+        const int m0 = mt * 256 + (int)rank * BM, n0 = nt * 512 + (int)rank * (BN2 / 2);
+        for (int kb = 0; kb < args.num_kb; kb++) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          const uint32_t a_dst = smem_base + stage * STAGEW_BYTES, b_dst = a_dst + A_STAGE_BYTES;
+          const uint32_t leader_full = map_to_cta(full_bar(stage), 0);
+          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * (A_STAGE_BYTES + halves * B2_STAGE_BYTES));
+          const int x = kb * args.k_elems_per_block;
+          tma_load_2d_pair(a_dst, &map_a, leader_full, x, m0);
+          tma_load_2d_pair(b_dst, &map_b, leader_full, x, n0);
+          if (halves == 2) tma_load_2d_pair(b_dst + B2_STAGE_BYTES, &map_b, leader_full, x, n0 + 256);
+          if (++stage == STAGESW) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_instr_desc_pair<KIND>();
+      int stage = 0;
+      uint32_t phase = 0;
+      int use[2] = {0, 0}; // how often each accumulator half has been used so far
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        int mt, nt;
+        tile_coords(args, tile, &mt, &nt);
+        const int halves = halves_of(nt);
+        for (int kb = 0; kb < args.num_kb && ok; kb++) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * STAGEW_BYTES;
+          const uint64_t adesc = make_smem_desc(a_addr);
+          for (int h = 0; h < halves; h++) {
+            if (kb == 0) { // the epilogue must have drained this half of the previous tile
+              if (!mbar_wait(tempty_bar(h), (use[h] & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+              tc_fence_after();
+            }
+            const uint64_t bdesc = make_smem_desc(a_addr + A_STAGE_BYTES + h * B2_STAGE_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK_BYTES / 32; k++)
+              tc_mma_pair<KIND>(tmem_base + (uint32_t)(h * BN2), adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          if (!ok) break;
+          tc_commit_pair(map_to_cta(empty_bar(stage), 0));
+          tc_commit_pair(map_to_cta(empty_bar(stage), 1));
+          if (++stage == STAGESW) { stage = 0; phase ^= 1; }
+        }
+        if (ok) {
+          for (int h = 0; h < halves; h++) {
+            tc_commit_pair(map_to_cta(tfull_bar(h), 0));
+            tc_commit_pair(map_to_cta(tfull_bar(h), 1));
+            use[h]++;
+          }
+        }
+      }
+      tc_commit_pair(map_to_cta(drain_bar, 0));
+      const long long t0 = clock64();
+      while (!mbar_try_wait(drain_bar, 0)) {
+        if (clock64() - t0 > kWaitLimitCycles) { atomicCAS(args.status, 0, ST_TIMEOUT_DRAIN); break; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quad = warp & 3;
+    OutT *Y = static_cast<OutT *>(args.Y);
+    const bool vec_ok = (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
+    int use[2] = {0, 0};
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      int mt, nt;
+      tile_coords(args, tile, &mt, &nt);
+      const int halves = halves_of(nt);
+      const int m = mt * 256 + (int)rank * BM + quad * 32 + lane;
+      float sa = 1.f;
+      if (args.sa) sa = (args.sa_n == 1) ? __ldg(args.sa) : (m < args.M ? __ldg(args.sa + m) : 0.f);
+      const float sb_scalar = (args.sb && args.sb_n == 1) ? __ldg(args.sb) : 1.f;
+      for (int h = 0; h < halves && ok; h++) {
+        if (!mbar_wait(tfull_bar(h), use[h] & 1, abort_flag, args.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(h * BN2);
+#pragma unroll 1
+        for (int c = 0; c < BN2 / 32; c++) {
+          uint32_t r[32];
+          tmem_load_32(taddr + c * 32, r);
+          const int n = nt * 512 + h * BN2 + c * 32;
+          if (m < args.M && n < args.N) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+              float acc = (KIND == KIND_I8) ? (float)(int)r[j] : __uint_as_float(r[j]);
+              float sc = sa * sb_scalar;
+              if (args.sb && args.sb_n != 1) sc = sa * ((n + j < args.N) ? __ldg(args.sb + n + j) : 0.f);
+              v[j] = acc * sc;
+            }
+            OutT *row = Y + (size_t)m * args.N + n;
+            if (vec_ok && n + 32 <= args.N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 o = make_uint4(pack2<OutT>(v[j], v[j + 1]), pack2<OutT>(v[j + 2], v[j + 3]),
+                                     pack2<OutT>(v[j + 4], v[j + 5]), pack2<OutT>(v[j + 6], v[j + 7]));
+                __stcs(reinterpret_cast<uint4 *>(row + j), o);
+              }
+            } else {
+              for (int j = 0; j < 32 && n + j < args.N; j++) row[j] = FloatIO<OutT>::from_f32(v[j]);
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(h), 0));
+        use[h]++;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// Largest number of CTA pairs that can be resident at once on this device (0 = pairs unavailable).
+template <int KIND, typename OutT, bool kWide>
 int max_resident_pairs() {
   static int cached[64] = {0};
   static bool known[64] = {false};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
   if (!known[dev]) {
-    auto kern = gemm_tc2_kernel<KIND, OutT>;
+    auto kern = kWide ? gemm_tc2w_kernel<KIND, OutT> : gemm_tc2_kernel<KIND, OutT>;
+    const int smem_bytes = kWide ? SmemW::kDynamic : Smem2::kDynamic;
     int n = 0;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2::kDynamic) == cudaSuccess) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) == cudaSuccess) {
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(2 * sm_count(), 1, 1);
       cfg.blockDim = dim3(kGemmThreads, 1, 1);
-      cfg.dynamicSmemBytes = Smem2::kDynamic;
+      cfg.dynamicSmemBytes = smem_bytes;
       cudaLaunchAttribute attr;
       attr.id = cudaLaunchAttributeClusterDimension;
       attr.val.clusterDim.x = 2;
@@ -510,20 +713,22 @@ int max_resident_pairs() {
   return cached[dev];
 }
 
-template <int KIND, typename OutT>
+template <int KIND, typename OutT, bool kWide>
 int launch_gemm_pair(const void *A, const void *B, GemmArgs args, int64_t K, int pairs, cudaStream_t st) {
   CUtensorMap ma, mb;
   int rc;
   if ((rc = make_map(&ma, KIND, A, args.M, K, BM)) != QL_OK) return rc;
   if ((rc = make_map(&mb, KIND, B, args.N, K, BN2 / 2)) != QL_OK) return rc;
+  constexpr int kTileN = kWide ? 512 : BN2;
   args.tiles_m = (args.M + 255) / 256;
-  args.tiles_n = (args.N + BN2 - 1) / BN2;
+  args.tiles_n = (args.N + kTileN - 1) / kTileN;
   args.group_m = (args.group_m + 1) / 2; // bands were sized in 128-row tiles
   if (args.group_m < 1) args.group_m = 1;
   if (args.group_m > args.tiles_m) args.group_m = args.tiles_m;
   const int tiles = args.tiles_m * args.tiles_n;
   const int clusters = tiles < pairs ? tiles : pairs;
-  gemm_tc2_kernel<KIND, OutT><<<2 * clusters, kGemmThreads, Smem2::kDynamic, st>>>(ma, mb, args);
+  if (kWide) gemm_tc2w_kernel<KIND, OutT><<<2 * clusters, kGemmThreads, SmemW::kDynamic, st>>>(ma, mb, args);
+  else gemm_tc2_kernel<KIND, OutT><<<2 * clusters, kGemmThreads, Smem2::kDynamic, st>>>(ma, mb, args);
   count_launches(1);
   QL_CUDA_TRY(cudaGetLastError());
   return QL_OK;
@@ -553,9 +758,17 @@ template <int KIND, typename OutT>
 int launch_gemm_kind(const void *A, const void *B, GemmArgs args, int64_t K, cudaStream_t st) {
   const int sms = sm_count();
   if (args.M > 256 && args.N >= 512 && !getenv("QL_GEMM_ONE_CTA")) {
-    const int pairs = max_resident_pairs<KIND, OutT>();
+    // Wide (256 x 512) tiles are opt-in: they cut L2 traffic per flop by a quarter, but with a single
+    // accumulator the hand-over between tiles is exposed, and on B200 that cost more than the traffic
+    // saved (1.51 ms against 1.44 ms for 8192 x 28672 x 8192 fp8).
+    if (getenv("QL_GEMM_WIDE_PAIR")) {
+      const long long tiles_w = (long long)((args.M + 255) / 256) * ((args.N + 511) / 512);
+      const int pairs_w = max_resident_pairs<KIND, OutT, true>();
+      if (pairs_w > 0 && tiles_w >= 4ll * pairs_w) return launch_gemm_pair<KIND, OutT, true>(A, B, args, K, pairs_w, st);
+    }
+    const int pairs = max_resident_pairs<KIND, OutT, false>();
     const long long tiles2 = (long long)((args.M + 255) / 256) * ((args.N + BN2 - 1) / BN2);
-    if (pairs > 0 && tiles2 >= pairs) return launch_gemm_pair<KIND, OutT>(A, B, args, K, pairs, st);
+    if (pairs > 0 && tiles2 >= pairs) return launch_gemm_pair<KIND, OutT, false>(A, B, args, K, pairs, st);
   }
   int bn = 32;
   for (int cand : {256, 128, 64}) {

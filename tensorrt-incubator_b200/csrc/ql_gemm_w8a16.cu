@@ -1,15 +1,17 @@
 // W8A16 linear for large batches on the tcgen05 tensor cores, weights dequantized inside the kernel:
 //     Y[M,N] = (X[M,K] . Wq[N,K]^T) * scale[n],  X bf16|f16, Wq int8, f32 accumulation in tensor memory.
-// The int8 weights are read from HBM exactly once, as int8.  Per pipeline stage TMA brings a
-// [128 x 64] tile of X (128-byte swizzle) and the raw [BN x 64] int8 tile of W; four converter warps
+// The int8 weights are read from HBM exactly once, as int8.  Per k-block TMA brings a
+// [128 x 64] tile of X (128-byte swizzle) and the raw [BN x 64] int8 tile of W; eight converter warps
 // widen the weights to the activation type (exact: |q| <= 128 fits the significand) and store them in
 // the 128-byte-swizzled K-major layout the MMA's shared-memory descriptor expects, fence the writes
 // for the async proxy and signal the MMA warp.  The per-channel scale is applied to the f32
 // accumulator in the epilogue, which equals scaling every weight first up to f32 rounding
 // (reference composition: quantize -> dequantize -> matmul, tripy/nvtripy/frontend/module/linear.py:140-151).
 //
-// Warps: 0 TMA producer, 1 TMEM owner + MMA issuer, 2-5 epilogue, 6-9 converters.  All waits bounded.
+// Warps: 0 TMA producer (W), 1 TMEM owner + MMA issuer, 2-5 epilogue, 6-13 converters, 14 TMA producer (X).
+// All waits bounded.
 #include <cuda/std/type_traits>
+#include <cstdlib>
 
 #include "ql_common.cuh"
 #include "ql_tc_common.cuh"
@@ -17,23 +19,33 @@
 namespace ql {
 namespace {
 
-constexpr int kW8Threads = 320;
-constexpr int kConvThreads = 128;
+constexpr int kConvWarps = 8;
+constexpr int kConvThreads = kConvWarps * 32;
+constexpr int kW8Threads = (6 + kConvWarps + 1) * 32; // TMA(W), MMA, 4 epilogue, converters, TMA(X)
+constexpr int kWarpXProducer = 6 + kConvWarps;
 constexpr int BKE = 64; // k elements per stage: 128 bytes of X, 64 bytes of int8 W
 
+// Three rings, so that each resource is held only as long as it is needed: the small raw int8 tiles
+// sit in a deep ring (their HBM latency is the one to hide), X tiles in a 4-deep ring released by the
+// MMA, and the widened tiles in a 2- or 3-deep ring between the converters and the MMA.
 template <int BN> struct W8Smem {
   static constexpr int kA = BM * BK_BYTES;
   static constexpr int kConv = BN * BK_BYTES;
   static constexpr int kRaw = BN * BKE;
-  static constexpr int kStage = kA + kConv + kRaw; // a multiple of 1024 for BN % 16 == 0
-  static constexpr int kStagesFit = (200 * 1024) / kStage;
-  static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
-  static constexpr int kTiles = kStages * kStage;
-  static constexpr int kBarriers = kTiles;                       // full[S], empty[S], ready[S], tfull[2], tempty[2], drain
-  static constexpr int kTmemPtr = kBarriers + (3 * kStages + 5) * 8;
+  static constexpr int NA = (BN <= 128) ? 6 : 4;
+  static constexpr int NC = (BN >= 256) ? 2 : 3;
+  static constexpr int kRawFit = (200 * 1024 - NA * kA - NC * kConv) / kRaw;
+  static constexpr int NR = kRawFit > 16 ? 16 : kRawFit;
+  static constexpr int kOffA = 0;
+  static constexpr int kOffConv = NA * kA;
+  static constexpr int kOffRaw = kOffConv + NC * kConv;
+  static constexpr int kBarriers = kOffRaw + NR * kRaw; // raw_full[NR] raw_empty[NR] a_full[NA] a_empty[NA] conv_ready[NC] conv_empty[NC] tfull[2] tempty[2] drain
+  static constexpr int kNumBarriers = 2 * NR + 2 * NA + 2 * NC + 5;
+  static constexpr int kTmemPtr = kBarriers + kNumBarriers * 8;
   static constexpr int kAbort = kTmemPtr + 4;
   static constexpr int kTotal = kAbort + 4;
   static constexpr int kDynamic = kTotal + 1024;
+  static_assert(NR >= 2, "raw ring too shallow");
 };
 
 struct W8Args {
@@ -71,23 +83,42 @@ __device__ __forceinline__ uint32_t widen_pair(uint32_t w) {
   }
 }
 
+// Every CTA walks the k-blocks in the same cyclic order but starts at a different one, so that the CTAs
+// which share an X tile (all of them, when M fits one row tile) do not ask L2 for the same lines at the
+// same moment.  The sum over k does not depend on the order beyond f32 rounding.
+__device__ __forceinline__ int rotated_kb(int kb, int num_kb) {
+  const int v = kb + (int)((blockIdx.x * 7u) % (unsigned)num_kb);
+  return v >= num_kb ? v - num_kb : v;
+}
+
+struct Ring {
+  int stage = 0;
+  uint32_t phase = 0;
+  __device__ __forceinline__ void advance(int n) {
+    if (++stage == n) { stage = 0; phase ^= 1; }
+  }
+};
+
 template <typename XT, int BN>
 __global__ void __launch_bounds__(kW8Threads, 1)
 gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const W8Args args) {
   using L = W8Smem<BN>;
-  constexpr int S = L::kStages;
+  constexpr int NR = L::NR, NA = L::NA, NC = L::NC;
   constexpr int KIND = cuda::std::is_same<XT, __half>::value ? KIND_F16 : KIND_BF16;
   constexpr uint32_t kTmemCols = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_base = smem_base + L::kBarriers;
-  auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
-  auto ready_bar = [&](int s) { return bar_base + 8u * (2 * S + s); };
-  auto tfull_bar = [&](int b) { return bar_base + 8u * (3 * S + b); };
-  auto tempty_bar = [&](int b) { return bar_base + 8u * (3 * S + 2 + b); };
-  const uint32_t drain_bar = bar_base + 8u * (3 * S + 4);
+  auto raw_full = [&](int s) { return bar_base + 8u * s; };
+  auto raw_empty = [&](int s) { return bar_base + 8u * (NR + s); };
+  auto a_full = [&](int s) { return bar_base + 8u * (2 * NR + s); };
+  auto a_empty = [&](int s) { return bar_base + 8u * (2 * NR + NA + s); };
+  auto conv_ready = [&](int s) { return bar_base + 8u * (2 * NR + 2 * NA + s); };
+  auto conv_empty = [&](int s) { return bar_base + 8u * (2 * NR + 2 * NA + NC + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * NR + 2 * NA + 2 * NC + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * NR + 2 * NA + 2 * NC + 2 + b); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * NR + 2 * NA + 2 * NC + 4);
   volatile uint32_t *tmem_ptr_smem = reinterpret_cast<volatile uint32_t *>(smem + L::kTmemPtr);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
 
@@ -95,10 +126,17 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   const int num_tiles = args.tiles_m * args.tiles_n;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < S; s++) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
-      mbar_init(ready_bar(s), kConvThreads / 32); // one arrival per converter warp
+    for (int s = 0; s < NR; s++) {
+      mbar_init(raw_full(s), 1);
+      mbar_init(raw_empty(s), kConvWarps);
+    }
+    for (int s = 0; s < NA; s++) {
+      mbar_init(a_full(s), 1);
+      mbar_init(a_empty(s), 1);
+    }
+    for (int s = 0; s < NC; s++) {
+      mbar_init(conv_ready(s), kConvWarps);
+      mbar_init(conv_empty(s), 1);
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(tfull_bar(b), 1);
@@ -118,32 +156,34 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   const uint32_t tmem_base = *tmem_ptr_smem;
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA producer, raw int8 weights
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      long long issued = 0;
+      Ring r;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int mt, nt;
         w8_tile_coords(args, tile, &mt, &nt);
         for (int kb = 0; kb < args.num_kb; kb++) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
-          const uint32_t a_dst = smem_base + stage * L::kStage, raw_dst = a_dst + L::kA + L::kConv;
-          mbar_expect_tx(full_bar(stage), L::kA + L::kRaw);
-          tma_load_2d(a_dst, &map_x, full_bar(stage), kb * BKE, mt * BM);
-          tma_load_2d(raw_dst, &map_w, full_bar(stage), kb * BKE, nt * BN);
-          issued++;
-          if (++stage == S) { stage = 0; phase ^= 1; }
+          if (!mbar_wait(raw_empty(r.stage), r.phase ^ 1, abort_flag, args.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          mbar_expect_tx(raw_full(r.stage), L::kRaw);
+          tma_load_2d(smem_base + L::kOffRaw + r.stage * L::kRaw, &map_w, raw_full(r.stage), rotated_kb(kb, args.num_kb) * BKE, nt * BN);
+          r.advance(NR);
         }
       }
-      if (!ok) {
-        const long long pending = issued < S ? issued : S;
-        for (long long i = 0; i < pending; i++) {
-          stage = (stage == 0) ? S - 1 : stage - 1;
-          if (stage == S - 1) phase ^= 1;
-          const long long t0 = clock64();
-          while (!mbar_try_wait(full_bar(stage), phase) && clock64() - t0 < kWaitLimitCycles) {}
+    }
+  } else if (warp == kWarpXProducer) {
+    // ------------------------------------------------------------------ TMA producer, X tiles
+    if (lane == 0) {
+      Ring r;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int mt, nt;
+        w8_tile_coords(args, tile, &mt, &nt);
+        for (int kb = 0; kb < args.num_kb; kb++) {
+          if (!mbar_wait(a_empty(r.stage), r.phase ^ 1, abort_flag, args.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          mbar_expect_tx(a_full(r.stage), L::kA);
+          tma_load_2d(smem_base + L::kOffA + r.stage * L::kA, &map_x, a_full(r.stage), rotated_kb(kb, args.num_kb) * BKE, mt * BM);
+          r.advance(NA);
         }
       }
     }
@@ -151,8 +191,7 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = make_instr_desc<KIND, BN>();
-      int stage = 0;
-      uint32_t phase = 0;
+      Ring ra, rc;
       int it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, it++) {
@@ -161,15 +200,18 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
         for (int kb = 0; kb < args.num_kb; kb++) {
-          if (!mbar_wait(ready_bar(stage), phase, abort_flag, args.status, ST_TIMEOUT_READY)) { ok = false; break; }
+          if (!mbar_wait(a_full(ra.stage), ra.phase, abort_flag, args.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+          if (!mbar_wait(conv_ready(rc.stage), rc.phase, abort_flag, args.status, ST_TIMEOUT_READY)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = smem_base + stage * L::kStage;
-          const uint64_t adesc = make_smem_desc(a_addr), bdesc = make_smem_desc(a_addr + L::kA);
+          const uint64_t adesc = make_smem_desc(smem_base + L::kOffA + ra.stage * L::kA);
+          const uint64_t bdesc = make_smem_desc(smem_base + L::kOffConv + rc.stage * L::kConv);
 #pragma unroll
           for (int k = 0; k < BK_BYTES / 32; k++)
             tc_mma<KIND>(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-          tc_commit(empty_bar(stage));
-          if (++stage == S) { stage = 0; phase ^= 1; }
+          tc_commit(a_empty(ra.stage));
+          tc_commit(conv_empty(rc.stage));
+          ra.advance(NA);
+          rc.advance(NC);
         }
         if (ok) tc_commit(tfull_bar(buf));
       }
@@ -180,23 +222,22 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       }
     }
   } else if (warp >= 6) {
-    // ------------------------------------------------------------------ converters (warps 6..9)
+    // ------------------------------------------------------------------ converters
     const int ctid = threadIdx.x - 6 * 32;
-    int stage = 0;
-    uint32_t phase = 0;
+    Ring rr, rc;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       for (int kb = 0; kb < args.num_kb; kb++) {
-        if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, ST_TIMEOUT_FULL)) { ok = false; break; }
-        uint8_t *conv = smem + stage * L::kStage + L::kA;
-        const uint8_t *raw = conv + L::kConv;
+        if (!mbar_wait(raw_full(rr.stage), rr.phase, abort_flag, args.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+        if (!mbar_wait(conv_empty(rc.stage), rc.phase ^ 1, abort_flag, args.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+        const uint8_t *raw = smem + L::kOffRaw + rr.stage * L::kRaw;
+        uint8_t *conv = smem + L::kOffConv + rc.stage * L::kConv;
 #pragma unroll 2
         for (int idx = ctid; idx < BN * 4; idx += kConvThreads) {
           const int r = idx >> 2, c = idx & 3;
           const uint4 w = *reinterpret_cast<const uint4 *>(raw + r * BKE + c * 16);
-          const uint32_t u0 = w.x, u1 = w.y, u2 = w.z, u3 = w.w;
-          const uint4 lo = make_uint4(widen_pair<XT, 0>(u0), widen_pair<XT, 2>(u0), widen_pair<XT, 0>(u1), widen_pair<XT, 2>(u1));
-          const uint4 hi = make_uint4(widen_pair<XT, 0>(u2), widen_pair<XT, 2>(u2), widen_pair<XT, 0>(u3), widen_pair<XT, 2>(u3));
+          const uint4 lo = make_uint4(widen_pair<XT, 0>(w.x), widen_pair<XT, 2>(w.x), widen_pair<XT, 0>(w.y), widen_pair<XT, 2>(w.y));
+          const uint4 hi = make_uint4(widen_pair<XT, 0>(w.z), widen_pair<XT, 2>(w.z), widen_pair<XT, 0>(w.w), widen_pair<XT, 2>(w.w));
           uint8_t *row = conv + r * BK_BYTES;
           const int sw = r & 7; // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
           *reinterpret_cast<uint4 *>(row + (((2 * c) ^ sw) << 4)) = lo;
@@ -204,8 +245,12 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(ready_bar(stage));
-        if (++stage == S) { stage = 0; phase ^= 1; }
+        if (lane == 0) {
+          mbar_arrive(conv_ready(rc.stage));
+          mbar_arrive(raw_empty(rr.stage));
+        }
+        rr.advance(NR);
+        rc.advance(NC);
       }
     }
   } else {

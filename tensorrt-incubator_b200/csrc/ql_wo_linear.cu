@@ -15,6 +15,7 @@
 // Reference composition this implements: tripy/nvtripy/frontend/module/linear.py:140-151
 // (quantize -> dequantize -> x @ transpose(w)) with the dequantize folded into the product.
 #include <cuda/std/type_traits>
+#include <cstdlib>
 
 #include "ql_common.cuh"
 
@@ -81,8 +82,8 @@ template <int WBITS> struct WoTraits {
 
 // NT = number of 8-row tiles of X handled at once (M <= 8 * NT); U = iterations whose loads are issued
 // together before any of them is consumed.
-template <typename XT, int WBITS, int NT, int U>
-__global__ void __launch_bounds__(kThreadsWo)
+template <typename XT, int WBITS, int NT, int U, int MINB>
+__global__ void __launch_bounds__(kThreadsWo, MINB)
 wo_linear_kernel(const XT *__restrict__ X, const uint8_t *__restrict__ W, const void *__restrict__ scale, int sdt,
                  XT *__restrict__ Y, int M, int N, int K, int block) {
   using T = WoTraits<WBITS>;
@@ -220,10 +221,17 @@ int launch_wo_t(const void *X, const void *W, const void *scale, int sdt, void *
     const int mc = min(32, M - m0);
     const XT *xp = static_cast<const XT *>(X) + (int64_t)m0 * K;
     XT *yp = static_cast<XT *>(Y) + (int64_t)m0 * N;
-    constexpr int U1 = (WBITS == 8) ? 4 : 2, U2 = (WBITS == 8) ? 2 : 1;
-    if (mc <= 8) wo_linear_kernel<XT, WBITS, 1, U1><<<grid, kThreadsWo, 0, st>>>(xp, wp, scale, sdt, yp, mc, N, K, block);
-    else if (mc <= 16) wo_linear_kernel<XT, WBITS, 2, U2><<<grid, kThreadsWo, 0, st>>>(xp, wp, scale, sdt, yp, mc, N, K, block);
-    else wo_linear_kernel<XT, WBITS, 4, 1><<<grid, kThreadsWo, 0, st>>>(xp, wp, scale, sdt, yp, mc, N, K, block);
+    // (k-steps in flight per warp, minimum resident blocks) per batch width, from timing on B200: many
+    // resident blocks with one step in flight each beat fewer blocks with deeper unrolling
+#define QL_WO_LAUNCH(NT_, U_, MB_) wo_linear_kernel<XT, WBITS, NT_, U_, MB_><<<grid, kThreadsWo, 0, st>>>(xp, wp, scale, sdt, yp, mc, N, K, block)
+    if (mc <= 8) {
+      QL_WO_LAUNCH(1, 1, 6);
+    } else if (mc <= 16) {
+      QL_WO_LAUNCH(2, 2, 3);
+    } else {
+      QL_WO_LAUNCH(4, 1, 2);
+    }
+#undef QL_WO_LAUNCH
     count_launches(1);
   }
   QL_CUDA_TRY(cudaGetLastError());
