@@ -300,7 +300,10 @@ class Fp8Gemm(Workload):
         self.torch, self.ql, self.device, self.dist = torch, ql, device, dist
         self.world = dist.get_world_size() if dist is not None else 1
         self.rank = dist.get_rank() if dist is not None else 0
-        self.parallelism = f"column-parallel over {self.world} GPUs, NCCL all-gather of Y" if self.world > 1 else "1 GPU"
+        self.fused = self.world > 1 and ql.peer.available() and not os.environ.get("QL_BENCH_NCCL")
+        self.parallelism = (f"column-parallel over {self.world} GPUs, " +
+                            ("Y [M,N] assembled on every GPU by the GEMM epilogue (multimem.st through NVSwitch), one barrier per step"
+                             if self.fused else "NCCL all-gather of Y")) if self.world > 1 else "1 GPU"
         nl = self.N // self.world
         self.nl = nl
         g = torch.Generator(device="cpu").manual_seed(seed)
@@ -325,7 +328,10 @@ class Fp8Gemm(Workload):
         self.sx32 = torch.empty((), dtype=torch.float32, device=device)
         self.xq = torch.empty((self.M, self.K), dtype=torch.float8_e4m3fn, device=device)
         self.y_local = torch.empty((self.M, nl), dtype=torch.bfloat16, device=device)
-        self.y_all = torch.empty((self.world, self.M, nl), dtype=torch.bfloat16, device=device) if self.world > 1 else None
+        self.y_all = torch.empty((self.world, self.M, nl), dtype=torch.bfloat16, device=device) if self.world > 1 and not self.fused else None
+        # fused: two full-width outputs used in turn, so that a rank still reading step i is not overwritten by step i+1
+        self.y_peer = [ql.peer.PeerTensor((self.M, self.N), torch.bfloat16) for _ in range(2)] if self.fused else None
+        self.step_no = 0
         self.y_host = torch.empty((self.M, nl), dtype=torch.bfloat16).pin_memory()
 
     def p_scale(self):
@@ -340,12 +346,26 @@ class Fp8Gemm(Workload):
     def p_gather(self):
         self.dist.all_gather_into_tensor(self.y_all, self.y_local)
 
+    def p_gemm_store_all(self):
+        self.ql.peer.gemm_fp8_peer(self.xq, self.wq, self.sx32, self.sw32, self.y_peer[self.step_no % 2], self.ql.peer.STORE_ALL,
+                                   col0=self.rank * self.nl)
+
+    def p_barrier(self):
+        self.y_peer[self.step_no % 2].barrier()
+        self.step_no += 1
+
     def parts(self):
         mk = self.M * self.K
-        ps = [("x_amax_scale", self.p_scale, 0, 2 * mk, "hbm"), ("x_quantize", self.p_quant, 0, 3 * mk, "hbm"),
-              ("fp8_gemm", self.p_gemm, 2 * self.M * self.K * self.nl, mk + self.nl * self.K + 2 * self.M * self.nl, "tensor_fp8")]
-        if self.world > 1:
-            ps.append(("all_gather_y", self.p_gather, 0, 2 * self.M * self.nl * (self.world - 1), "nvlink"))
+        gemm_flops, gemm_bytes = 2 * self.M * self.K * self.nl, mk + self.nl * self.K + 2 * self.M * self.nl
+        ps = [("x_amax_scale", self.p_scale, 0, 2 * mk, "hbm"), ("x_quantize", self.p_quant, 0, 3 * mk, "hbm")]
+        if self.fused:
+            # every rank receives the other ranks' columns while it computes: the slower of the two bounds the kernel
+            ps += [("fp8_gemm_store_all", self.p_gemm_store_all, gemm_flops, gemm_bytes, "tensor_fp8"),
+                   ("barrier", self.p_barrier, 0, 0, "nvlink")]
+        else:
+            ps.append(("fp8_gemm", self.p_gemm, gemm_flops, gemm_bytes, "tensor_fp8"))
+            if self.world > 1:
+                ps.append(("all_gather_y", self.p_gather, 0, 2 * self.M * self.nl * (self.world - 1), "nvlink"))
         return ps
 
     def step_flops_global(self):
@@ -378,7 +398,11 @@ class Fp8Gemm(Workload):
         self.x.copy_(self.x_host, non_blocking=True)
         for _, fn, _, _, _ in self.parts():
             fn()
-        self.y_host.copy_(self.y_local, non_blocking=True)
+        if self.fused:
+            lo = self.rank * self.nl   # this rank reads back its share of the assembled result
+            self.y_host.copy_(self.y_peer[(self.step_no - 1) % 2].local[:, lo:lo + self.nl], non_blocking=True)
+        else:
+            self.y_host.copy_(self.y_local, non_blocking=True)
 
     def e2e_bytes(self):
         return self.M * self.K * 2, self.M * self.nl * 2
@@ -407,13 +431,17 @@ class Fp8Mlp(Workload):
         self.torch, self.ql, self.device, self.dist = torch, ql, device, dist
         self.world = dist.get_world_size() if dist is not None else 1
         self.rank = dist.get_rank() if dist is not None else 0
-        self.parallelism = f"tensor-parallel over {self.world} GPUs: gate/up column-parallel, down row-parallel, NCCL all-reduce"
+        fused = "auto" if not os.environ.get("QL_BENCH_NCCL") else False
         il = self.I // self.world
         self.il = il
         g = torch.Generator(device=device).manual_seed(seed * 100 + self.rank)   # this rank's shard of the random weights
         def w(shape):
             return (torch.randn(shape, generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
-        self.mlp = ql.QuantizedMLP(w((il, self.H)), w((il, self.H)), w((self.H, il)), eps=1e-5, group=(dist.group.WORLD if dist is not None else None))
+        self.mlp = ql.QuantizedMLP(w((il, self.H)), w((il, self.H)), w((self.H, il)), eps=1e-5, group=(dist.group.WORLD if dist is not None else None),
+                                    fused_all_reduce=fused)
+        self.parallelism = (f"tensor-parallel over {self.world} GPUs: gate/up column-parallel, down row-parallel, " +
+                            ("partial results added into every GPU's output by the GEMM epilogue (multimem.red through NVSwitch), one barrier per step"
+                             if self.mlp.fused_all_reduce else "NCCL all-reduce"))
         gx = torch.Generator(device="cpu").manual_seed(seed)
         self.x_host = torch.randn((self.T, self.H), generator=gx, dtype=torch.float32).to(torch.bfloat16).pin_memory()
         self.x = self.x_host.to(device)
@@ -424,11 +452,23 @@ class Fp8Mlp(Workload):
         T, H, il = self.T, self.H, self.il
         ps = [("rmsnorm_quant", lambda: self.mlp.stage_norm_quant(self.x, self.buf), 0, 3 * T * H + 4 * T, "hbm"),
               ("gate_up_gemm", lambda: self.mlp.stage_gate_up(self.buf), 2 * T * H * 2 * il, T * H + 2 * il * H + 2 * T * 2 * il, "tensor_fp8"),
-              ("swiglu_quant", lambda: self.mlp.stage_swiglu_quant(self.buf), 0, 2 * T * 2 * il + T * il, "hbm"),
-              ("down_gemm", lambda: self.mlp.stage_down(self.buf), 2 * T * il * H, T * il + H * il + 2 * T * H, "tensor_fp8")]
-        if self.world > 1:
-            ps.append(("all_reduce_y", lambda: self.mlp.stage_all_reduce(self.buf), 0, 2 * 2 * T * H * (self.world - 1) // self.world, "nvlink"))
+              ("swiglu_quant", lambda: self.mlp.stage_swiglu_quant(self.buf), 0, 2 * T * 2 * il + T * il, "hbm")]
+        down = (2 * T * il * H, T * il + H * il + 2 * T * H, "tensor_fp8")
+        if self.mlp.fused_all_reduce:
+            def finish():
+                self.mlp.stage_barrier(self.buf)
+                self.mlp._step += 1
+            ps += [("down_gemm_add_all", lambda: self.mlp.stage_down_add_all(self.buf)) + down,
+                   ("clear_next_output", lambda: self.mlp.stage_clear_next(self.buf), 0, 2 * T * H, "hbm"),
+                   ("barrier", finish, 0, 0, "nvlink")]
+        else:
+            ps.append(("down_gemm", lambda: self.mlp.stage_down(self.buf)) + down)
+            if self.world > 1:
+                ps.append(("all_reduce_y", lambda: self.mlp.stage_all_reduce(self.buf), 0, 2 * 2 * T * H * (self.world - 1) // self.world, "nvlink"))
         return ps
+
+    def reset(self):
+        self.mlp.reset_peer_buffers()
 
     def step_flops_global(self):
         return 3 * 2 * self.T * self.H * self.I
@@ -698,6 +738,8 @@ def main():
     clock_info = clocks.stop()
 
     # -------- end to end: inputs from pinned host memory, results read back, every step
+    if hasattr(wl, "reset"):
+        wl.reset()   # the per-part loops above ran stages out of turn
     for _ in range(3):
         wl.e2e_step()
     barrier()

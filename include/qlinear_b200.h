@@ -134,6 +134,20 @@ QL_API int ql_gemm_fp8(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor
                        const ql_tensor *sw, ql_tensor *y, void *stream);
 QL_API int ql_gemm_i8(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx,
                       const ql_tensor *sw, ql_tensor *y, void *stream);
+/* The fp8 GEMM with its collective done by the epilogue (tensor-parallel layers over the GPUs of one box).
+ * No reference counterpart: the reference has no multi-GPU execution of this path.
+ * y->data points at element (0, 0) of this rank's [M, N] slice inside a buffer whose rows are `ldy`
+ * elements apart.  With QL_PEER_NONE the buffer is ordinary device memory.  With the other modes it is
+ * an address in an NVSwitch replication group (CUDA multicast object) that maps the same buffer on every
+ * GPU of the group, and each finished 16 bytes go to all of them in one posted write:
+ *   QL_PEER_STORE_ALL  stores the slice in every replica: column-parallel GEMM + all-gather;
+ *   QL_PEER_ADD_ALL    adds the slice into every replica (sum in the output type): row-parallel GEMM +
+ *                      all-reduce; the replicas must hold zeros (or a bias) before any rank starts.
+ * The kernel waits on no peer.  The caller orders it after the buffer is ready on all ranks and puts a
+ * cross-rank barrier after it before anyone reads.  Peer modes need N % 32 == 0 and ldy % 8 == 0. */
+typedef enum { QL_PEER_NONE = 0, QL_PEER_STORE_ALL = 1, QL_PEER_ADD_ALL = 2 } ql_peer_mode;
+QL_API int ql_gemm_fp8_peer(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx,
+                            const ql_tensor *sw, ql_tensor *y, int64_t ldy, int peer_mode, void *stream);
 /* 16-bit GEMM Y = (X . W^T) * sw, X and W both bf16 or both f16 ([M,K], [N,K]); sw may be null. */
 QL_API int ql_gemm_16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *sw, ql_tensor *y,
                       void *stream);

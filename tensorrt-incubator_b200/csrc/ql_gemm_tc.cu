@@ -41,7 +41,32 @@ struct GemmArgs {
   int tiles_m, tiles_n;
   int group_m;     // m-tiles per scheduling group (see tile_coords)
   int *status;
+  int64_t ldy;     // elements between rows of Y (N, or the full width when Y is a column slice)
+  int peer_mode;   // QL_PEER_*: how the epilogue writes Y
 };
+
+// 16 bytes of finished output.  Locally: a streaming store (written once, never re-read here, so it
+// stays out of L2's way).  For the peer modes `p` is an address of an NVSwitch replication group that
+// maps the same buffer on every GPU of the group: one `multimem.st` lands the tile in all of them
+// (an all-gather done by the epilogue), one `multimem.red` adds it into all of them (an all-reduce
+// done by the epilogue, summing in the output type as the collective library does).  Both are posted
+// writes: the kernel waits on no peer, and they are complete when the kernel is.
+template <typename OutT>
+__device__ __forceinline__ void store_out16(OutT *p, const uint4 &o, int peer_mode) {
+  if (peer_mode == QL_PEER_NONE) {
+    __stcs(reinterpret_cast<uint4 *>(p), o);
+  } else if (peer_mode == QL_PEER_STORE_ALL) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(__uint_as_float(o.x)),
+                 "f"(__uint_as_float(o.y)), "f"(__uint_as_float(o.z)), "f"(__uint_as_float(o.w))
+                 : "memory");
+  } else if constexpr (FloatIO<OutT>::kDtype == QL_F16) {
+    asm volatile("multimem.red.relaxed.sys.global.add.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
+                 : "memory");
+  } else {
+    asm volatile("multimem.red.relaxed.sys.global.add.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
+                 : "memory");
+  }
+}
 
 // Tile order.  Consecutive tile indices (which run concurrently on neighbouring SMs) walk a band
 // of `group_m` row tiles across all column tiles before moving to the next band, so the A rows of
@@ -56,6 +81,65 @@ __device__ __forceinline__ void tile_coords(const GemmArgs &a, int tile, int *mt
   *nt = local / gsz;
 }
 
+// Peer modes write through shared memory: in tensor memory a lane owns a row, so a direct store would send
+// 32 separate 16-byte pieces per instruction over NVLink (measured: 69 GB/s).  Each epilogue warp instead parks
+// 32 rows x 64 columns in its own staging rows and sends them out again with 8 lanes per row, 128 contiguous
+// bytes per row and instruction.  Row pitch 144 bytes keeps both directions free of bank conflicts.
+constexpr int kPeerRowBytes = 144;
+constexpr int kPeerStageWarp = 32 * kPeerRowBytes;
+constexpr int kPeerStageBytes = 4 * kPeerStageWarp;
+
+template <typename OutT>
+__device__ __forceinline__ void peer_flush(const uint8_t *stage, int lane, OutT *Y, const GemmArgs &args, int m_base, int n_base, int ncols) {
+  __syncwarp();
+  const int lanes_per_row = ncols / 8, rows_per_instr = 32 / lanes_per_row;
+  const int rsub = lane / lanes_per_row, cw = lane % lanes_per_row;
+  for (int r0 = 0; r0 < 32; r0 += rows_per_instr) {
+    const int r = r0 + rsub, m = m_base + r, n = n_base + cw * 8;
+    const uint4 o = *reinterpret_cast<const uint4 *>(stage + r * kPeerRowBytes + cw * 16);
+    if (m < args.M && n + 8 <= args.N) store_out16<OutT>(Y + (size_t)m * (size_t)args.ldy + n, o, args.peer_mode);
+  }
+  __syncwarp();
+}
+
+// One epilogue warp's 32 rows x 32 columns of accumulators (lane = row m, columns n .. n+31) -> scaled output.
+// `stage` = this warp's staging rows (peer modes only), `c` = index of the chunk within the tile, `last` = no
+// chunk follows in this tile.
+template <int KIND, typename OutT>
+__device__ __forceinline__ void emit_chunk(const GemmArgs &args, OutT *Y, bool vec_ok, const uint32_t (&r)[32], int m, int n, float sa,
+                                           float sb_scalar, uint8_t *stage, int lane, int c, bool last) {
+  const bool peer = args.peer_mode != QL_PEER_NONE; // the same for every thread of the grid
+  if (!peer && !(m < args.M && n < args.N)) return;
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; j++) {
+    float acc = (KIND == KIND_I8) ? (float)(int)r[j] : __uint_as_float(r[j]);
+    float s = sa * sb_scalar;
+    if (args.sb && args.sb_n != 1) s = sa * ((n + j < args.N) ? __ldg(args.sb + n + j) : 0.f);
+    v[j] = acc * s;
+  }
+  if (peer) {
+    uint8_t *p = stage + lane * kPeerRowBytes + (c & 1) * 64;
+#pragma unroll
+    for (int j = 0; j < 32; j += 8)
+      *reinterpret_cast<uint4 *>(p + j * 2) = make_uint4(pack2<OutT>(v[j], v[j + 1]), pack2<OutT>(v[j + 2], v[j + 3]),
+                                                         pack2<OutT>(v[j + 4], v[j + 5]), pack2<OutT>(v[j + 6], v[j + 7]));
+    if ((c & 1) || last) peer_flush<OutT>(stage, lane, Y, args, m - lane, n - (c & 1) * 32, (c & 1) ? 64 : 32);
+    return;
+  }
+  OutT *row = Y + (size_t)m * (size_t)args.ldy + n;
+  if (vec_ok && n + 32 <= args.N) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      uint4 o = make_uint4(pack2<OutT>(v[j], v[j + 1]), pack2<OutT>(v[j + 2], v[j + 3]), pack2<OutT>(v[j + 4], v[j + 5]),
+                           pack2<OutT>(v[j + 6], v[j + 7]));
+      __stcs(reinterpret_cast<uint4 *>(row + j), o); // written once, never re-read here: keep it out of L2's way
+    }
+  } else {
+    for (int j = 0; j < 32 && n + j < args.N; j++) row[j] = FloatIO<OutT>::from_f32(v[j]);
+  }
+}
+
 template <int BN> struct SmemLayout {
   static constexpr int kBStage = BN * BK_BYTES;
   static constexpr int kStage = A_STAGE_BYTES + kBStage;
@@ -63,7 +147,8 @@ template <int BN> struct SmemLayout {
   static constexpr int kBarriers = kTiles;            // full[S], empty[S], tmem_full[2], tmem_empty[2], drain
   static constexpr int kTmemPtr = kBarriers + (2 * STAGES + 5) * 8;
   static constexpr int kAbort = kTmemPtr + 4;
-  static constexpr int kTotal = kAbort + 4;
+  static constexpr int kPeerStage = (kAbort + 4 + 15) & ~15; // staging rows of the peer-mode epilogue
+  static constexpr int kTotal = kPeerStage + kPeerStageBytes;
   static constexpr int kDynamic = kTotal + 1024;      // slack to align the ring to 1024 bytes
 };
 
@@ -178,7 +263,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quad = warp & 3; // tensor-memory lanes [32*quad, 32*quad+32) belong to this warp
     OutT *Y = static_cast<OutT *>(args.Y);
-    const bool vec_ok = (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
+    uint8_t *stage = smem + L::kPeerStage + quad * kPeerStageWarp;
+    const bool vec_ok = (args.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
     int it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, it++) {
@@ -198,27 +284,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t r[32];
         tmem_load_32(taddr + c * 32, r);
         const int n = n0 + c * 32;
-        if (m < args.M && n < args.N) {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; j++) {
-            float acc = (KIND == KIND_I8) ? (float)(int)r[j] : __uint_as_float(r[j]);
-            float s = sa * sb_scalar;
-            if (args.sb && args.sb_n != 1) s = sa * ((n + j < args.N) ? __ldg(args.sb + n + j) : 0.f);
-            v[j] = acc * s;
-          }
-          OutT *row = Y + (size_t)m * args.N + n;
-          if (vec_ok && n + 32 <= args.N) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 o = make_uint4(pack2<OutT>(v[j], v[j + 1]), pack2<OutT>(v[j + 2], v[j + 3]),
-                                   pack2<OutT>(v[j + 4], v[j + 5]), pack2<OutT>(v[j + 6], v[j + 7]));
-              __stcs(reinterpret_cast<uint4 *>(row + j), o); // written once, never re-read here: keep it out of L2's way
-            }
-          } else {
-            for (int j = 0; j < 32 && n + j < args.N; j++) row[j] = FloatIO<OutT>::from_f32(v[j]);
-          }
-        }
+        emit_chunk<KIND, OutT>(args, Y, vec_ok, r, m, n, sa, sb_scalar, stage, lane, c, c == BN / 32 - 1);
       }
       tc_fence_before();
       __syncwarp();
@@ -245,17 +311,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // CTA fetches what it needs itself and signals the leader's "full" barrier (the .cta_group::2 form of
 // the tile load allows the barrier to live in the pair's other CTA).
 // ----------------------------------------------------------------------------------------------
-constexpr int STAGES2 = 7;
 constexpr int BN2 = 256;
 constexpr int B2_STAGE_BYTES = (BN2 / 2) * BK_BYTES;
 constexpr int STAGE2_BYTES = A_STAGE_BYTES + B2_STAGE_BYTES;
 
-struct Smem2 {
-  static constexpr int kTiles = STAGES2 * STAGE2_BYTES;
+// PEER = the instantiation whose epilogue may write to peers: it gives one pipeline stage up for the
+// epilogue's staging rows.
+template <bool PEER> struct Smem2 {
+  static constexpr int kStages = PEER ? 6 : 7;
+  static constexpr int kTiles = kStages * STAGE2_BYTES;
   static constexpr int kBarriers = kTiles;                   // full[S], empty[S], tfull[2], tempty[2], drain
-  static constexpr int kTmemPtr = kBarriers + (2 * STAGES2 + 5) * 8;
+  static constexpr int kTmemPtr = kBarriers + (2 * kStages + 5) * 8;
   static constexpr int kAbort = kTmemPtr + 4;
-  static constexpr int kTotal = kAbort + 4;
+  static constexpr int kPeerStage = (kAbort + 4 + 15) & ~15;
+  static constexpr int kTotal = kPeerStage + (PEER ? kPeerStageBytes : 0);
   static constexpr int kDynamic = kTotal + 1024;
 };
 
@@ -312,10 +381,11 @@ __device__ __forceinline__ uint32_t make_instr_desc_pair() {
 }
 
 // args.tiles_m counts 256-row tiles here; args.tiles_n counts 256-column tiles.
-template <int KIND, typename OutT>
+template <int KIND, typename OutT, bool PEER>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs args) {
-  using L = Smem2;
+  using L = Smem2<PEER>;
+  constexpr int STAGES2 = L::kStages;
   constexpr uint32_t kTmemCols = 512; // two 256-column accumulators
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -422,7 +492,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
     const int quad = warp & 3;
     OutT *Y = static_cast<OutT *>(args.Y);
-    const bool vec_ok = (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
+    uint8_t *stage = PEER ? smem + L::kPeerStage + quad * kPeerStageWarp : nullptr;
+    const bool vec_ok = (args.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
     int it = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, it++) {
@@ -442,27 +513,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         uint32_t r[32];
         tmem_load_32(taddr + c * 32, r);
         const int n = n0 + c * 32;
-        if (m < args.M && n < args.N) {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; j++) {
-            float acc = (KIND == KIND_I8) ? (float)(int)r[j] : __uint_as_float(r[j]);
-            float s = sa * sb_scalar;
-            if (args.sb && args.sb_n != 1) s = sa * ((n + j < args.N) ? __ldg(args.sb + n + j) : 0.f);
-            v[j] = acc * s;
-          }
-          OutT *row = Y + (size_t)m * args.N + n;
-          if (vec_ok && n + 32 <= args.N) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 o = make_uint4(pack2<OutT>(v[j], v[j + 1]), pack2<OutT>(v[j + 2], v[j + 3]),
-                                   pack2<OutT>(v[j + 4], v[j + 5]), pack2<OutT>(v[j + 6], v[j + 7]));
-              __stcs(reinterpret_cast<uint4 *>(row + j), o);
-            }
-          } else {
-            for (int j = 0; j < 32 && n + j < args.N; j++) row[j] = FloatIO<OutT>::from_f32(v[j]);
-          }
-        }
+        emit_chunk<KIND, OutT>(args, Y, vec_ok, r, m, n, sa, sb_scalar, stage, lane, c, c == BN2 / 32 - 1);
       }
       tc_fence_before();
       __syncwarp();
@@ -622,7 +673,7 @@ gemm_tc2w_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
     const int quad = warp & 3;
     OutT *Y = static_cast<OutT *>(args.Y);
-    const bool vec_ok = (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
+    const bool vec_ok = (args.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
     int use[2] = {0, 0};
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
@@ -642,27 +693,7 @@ gemm_tc2w_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           uint32_t r[32];
           tmem_load_32(taddr + c * 32, r);
           const int n = nt * 512 + h * BN2 + c * 32;
-          if (m < args.M && n < args.N) {
-            float v[32];
-#pragma unroll
-            for (int j = 0; j < 32; j++) {
-              float acc = (KIND == KIND_I8) ? (float)(int)r[j] : __uint_as_float(r[j]);
-              float sc = sa * sb_scalar;
-              if (args.sb && args.sb_n != 1) sc = sa * ((n + j < args.N) ? __ldg(args.sb + n + j) : 0.f);
-              v[j] = acc * sc;
-            }
-            OutT *row = Y + (size_t)m * args.N + n;
-            if (vec_ok && n + 32 <= args.N) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 o = make_uint4(pack2<OutT>(v[j], v[j + 1]), pack2<OutT>(v[j + 2], v[j + 3]),
-                                     pack2<OutT>(v[j + 4], v[j + 5]), pack2<OutT>(v[j + 6], v[j + 7]));
-                __stcs(reinterpret_cast<uint4 *>(row + j), o);
-              }
-            } else {
-              for (int j = 0; j < 32 && n + j < args.N; j++) row[j] = FloatIO<OutT>::from_f32(v[j]);
-            }
-          }
+          emit_chunk<KIND, OutT>(args, Y, vec_ok, r, m, n, sa, sb_scalar, nullptr, lane, c, c == BN2 / 32 - 1);
         }
         tc_fence_before();
         __syncwarp();
@@ -681,16 +712,27 @@ gemm_tc2w_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
 }
 
+// The CTA-pair kernels: 0 = 256 x 256 tiles, 1 = 256 x 512 tiles, 2 = 256 x 256 tiles with the peer-mode epilogue.
+enum { PAIR_PLAIN = 0, PAIR_WIDE = 1, PAIR_PEER = 2 };
+template <int KIND, typename OutT, int V>
+auto pair_kernel() {
+  if constexpr (V == PAIR_WIDE) return gemm_tc2w_kernel<KIND, OutT>;
+  else return gemm_tc2_kernel<KIND, OutT, V == PAIR_PEER>;
+}
+template <int V> constexpr int pair_smem() {
+  return V == PAIR_WIDE ? SmemW::kDynamic : V == PAIR_PEER ? Smem2<true>::kDynamic : Smem2<false>::kDynamic;
+}
+
 // Largest number of CTA pairs that can be resident at once on this device (0 = pairs unavailable).
-template <int KIND, typename OutT, bool kWide>
+template <int KIND, typename OutT, int V>
 int max_resident_pairs() {
   static int cached[64] = {0};
   static bool known[64] = {false};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
   if (!known[dev]) {
-    auto kern = kWide ? gemm_tc2w_kernel<KIND, OutT> : gemm_tc2_kernel<KIND, OutT>;
-    const int smem_bytes = kWide ? SmemW::kDynamic : Smem2::kDynamic;
+    auto kern = pair_kernel<KIND, OutT, V>();
+    const int smem_bytes = pair_smem<V>();
     int n = 0;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) == cudaSuccess) {
       cudaLaunchConfig_t cfg = {};
@@ -713,13 +755,13 @@ int max_resident_pairs() {
   return cached[dev];
 }
 
-template <int KIND, typename OutT, bool kWide>
+template <int KIND, typename OutT, int V>
 int launch_gemm_pair(const void *A, const void *B, GemmArgs args, int64_t K, int pairs, cudaStream_t st) {
   CUtensorMap ma, mb;
   int rc;
   if ((rc = make_map(&ma, KIND, A, args.M, K, BM)) != QL_OK) return rc;
   if ((rc = make_map(&mb, KIND, B, args.N, K, BN2 / 2)) != QL_OK) return rc;
-  constexpr int kTileN = kWide ? 512 : BN2;
+  constexpr int kTileN = V == PAIR_WIDE ? 512 : BN2;
   args.tiles_m = (args.M + 255) / 256;
   args.tiles_n = (args.N + kTileN - 1) / kTileN;
   args.group_m = (args.group_m + 1) / 2; // bands were sized in 128-row tiles
@@ -727,8 +769,7 @@ int launch_gemm_pair(const void *A, const void *B, GemmArgs args, int64_t K, int
   if (args.group_m > args.tiles_m) args.group_m = args.tiles_m;
   const int tiles = args.tiles_m * args.tiles_n;
   const int clusters = tiles < pairs ? tiles : pairs;
-  if (kWide) gemm_tc2w_kernel<KIND, OutT><<<2 * clusters, kGemmThreads, SmemW::kDynamic, st>>>(ma, mb, args);
-  else gemm_tc2_kernel<KIND, OutT><<<2 * clusters, kGemmThreads, Smem2::kDynamic, st>>>(ma, mb, args);
+  pair_kernel<KIND, OutT, V>()<<<2 * clusters, kGemmThreads, pair_smem<V>(), st>>>(ma, mb, args);
   count_launches(1);
   QL_CUDA_TRY(cudaGetLastError());
   return QL_OK;
@@ -761,14 +802,22 @@ int launch_gemm_kind(const void *A, const void *B, GemmArgs args, int64_t K, cud
     // Wide (256 x 512) tiles are opt-in: they cut L2 traffic per flop by a quarter, but with a single
     // accumulator the hand-over between tiles is exposed, and on B200 that cost more than the traffic
     // saved (1.51 ms against 1.44 ms for 8192 x 28672 x 8192 fp8).
-    if (getenv("QL_GEMM_WIDE_PAIR")) {
+    if (getenv("QL_GEMM_WIDE_PAIR") && args.peer_mode == QL_PEER_NONE) {
       const long long tiles_w = (long long)((args.M + 255) / 256) * ((args.N + 511) / 512);
-      const int pairs_w = max_resident_pairs<KIND, OutT, true>();
-      if (pairs_w > 0 && tiles_w >= 4ll * pairs_w) return launch_gemm_pair<KIND, OutT, true>(A, B, args, K, pairs_w, st);
+      const int pairs_w = max_resident_pairs<KIND, OutT, PAIR_WIDE>();
+      if (pairs_w > 0 && tiles_w >= 4ll * pairs_w) return launch_gemm_pair<KIND, OutT, PAIR_WIDE>(A, B, args, K, pairs_w, st);
     }
-    const int pairs = max_resident_pairs<KIND, OutT, false>();
     const long long tiles2 = (long long)((args.M + 255) / 256) * ((args.N + BN2 - 1) / BN2);
-    if (pairs > 0 && tiles2 >= pairs) return launch_gemm_pair<KIND, OutT, false>(A, B, args, K, pairs, st);
+    if constexpr (KIND == KIND_F8) {
+      if (args.peer_mode != QL_PEER_NONE) {
+        const int pairs = max_resident_pairs<KIND, OutT, PAIR_PEER>();
+        if (pairs > 0 && tiles2 >= pairs) return launch_gemm_pair<KIND, OutT, PAIR_PEER>(A, B, args, K, pairs, st);
+      }
+    }
+    if (args.peer_mode == QL_PEER_NONE) {
+      const int pairs = max_resident_pairs<KIND, OutT, PAIR_PLAIN>();
+      if (pairs > 0 && tiles2 >= pairs) return launch_gemm_pair<KIND, OutT, PAIR_PLAIN>(A, B, args, K, pairs, st);
+    }
   }
   int bn = 32;
   for (int cand : {256, 128, 64}) {
@@ -818,7 +867,7 @@ int check_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_
 
 template <int KIND>
 int run_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_tensor *sa, const ql_tensor *sb, ql_tensor *y,
-             void *stream) {
+             void *stream, int64_t ldy = 0, int peer_mode = QL_PEER_NONE) {
   const int64_t M = a->shape[0], K = a->shape[1], N = b->shape[0];
   if (M == 0 || N == 0) return QL_OK;
   const int esize = (KIND == KIND_F8 || KIND == KIND_I8) ? 1 : 2;
@@ -843,6 +892,8 @@ int run_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_te
     if (const char *e = getenv("QL_GEMM_GROUP_M")) args.group_m = atoi(e) > 0 ? atoi(e) : args.group_m; // tuning aid
     if (args.group_m > args.tiles_m) args.group_m = args.tiles_m;
   }
+  args.ldy = ldy > 0 ? ldy : N;
+  args.peer_mode = peer_mode;
   args.status = device_status_word();
   if (!args.status) return set_error(QL_ERR_CUDA, "%s: could not allocate the device status word", op);
   cudaStream_t st = (cudaStream_t)stream;
@@ -871,6 +922,21 @@ int ql_gemm_fp8(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx, c
   int rc = check_gemm("gemm_fp8", xq, wq, sx, sw, y, QL_F8E4M3, QL_F8E4M3);
   if (rc != QL_OK) return rc;
   return run_gemm<KIND_F8>("gemm_fp8", xq, wq, sx, sw, y, stream);
+}
+
+int ql_gemm_fp8_peer(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx, const ql_tensor *sw, ql_tensor *y,
+                     int64_t ldy, int peer_mode, void *stream) {
+  int rc = check_gemm("gemm_fp8_peer", xq, wq, sx, sw, y, QL_F8E4M3, QL_F8E4M3);
+  if (rc != QL_OK) return rc;
+  if (peer_mode != QL_PEER_NONE && peer_mode != QL_PEER_STORE_ALL && peer_mode != QL_PEER_ADD_ALL)
+    return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_fp8_peer: unknown peer mode %d", peer_mode);
+  if (ldy < y->shape[1]) return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_fp8_peer: ldy (%lld) is smaller than N (%lld)", (long long)ldy, (long long)y->shape[1]);
+  if (peer_mode != QL_PEER_NONE) {
+    // the peer stores exist as 16-byte vectors only
+    if (y->shape[1] % 32 != 0 || ldy % 8 != 0 || !aligned16(y->data))
+      return set_error(QL_ERR_UNSUPPORTED, "gemm_fp8_peer: peer modes need N %% 32 == 0, ldy %% 8 == 0 and a 16-byte aligned y");
+  }
+  return run_gemm<KIND_F8>("gemm_fp8_peer", xq, wq, sx, sw, y, stream, ldy, peer_mode);
 }
 
 int ql_gemm_i8(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx, const ql_tensor *sw, ql_tensor *y, void *stream) {

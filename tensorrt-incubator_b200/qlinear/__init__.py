@@ -6,3 +6,4 @@ from .linear import Linear, gemm_16, gemm_fp8, gemm_i8, linear_w4a16, linear_w8a
 from .ops import QuantizeError, amax_scale, dequantize, quantize, quantize_dequantize, quantize_to  # noqa: F401
 from .tensor import Int4Tensor  # noqa: F401
 from .mlp import QuantizedMLP, quantize_per_channel_fp8, rmsnorm_quant_fp8, shard_range, swiglu_quant_fp8  # noqa: F401
+from . import peer, stablehlo  # noqa: F401,E402

@@ -40,6 +40,8 @@ class QlQdqAttrs(ctypes.Structure):
     _fields_ = [("has_axis", ctypes.c_int32), ("axis", ctypes.c_int32), ("fp8_mode", ctypes.c_int32)]
 
 
+PEER_NONE, PEER_STORE_ALL, PEER_ADD_ALL = 0, 1, 2  # ql_peer_mode
+
 # every symbol include/qlinear_b200.h declares, with its ctypes signature
 _T = ctypes.POINTER(QlTensor)
 _A = ctypes.POINTER(QlQdqAttrs)
@@ -57,6 +59,7 @@ SIGNATURES = {
     "ql_linear_w8a16": ([_T, _T, _T, _T, _S], ctypes.c_int),
     "ql_linear_w4a16": ([_T, _T, _T, _T, _S], ctypes.c_int),
     "ql_gemm_fp8": ([_T, _T, _T, _T, _T, _S], ctypes.c_int),
+    "ql_gemm_fp8_peer": ([_T, _T, _T, _T, _T, ctypes.c_int64, ctypes.c_int, _S], ctypes.c_int),
     "ql_gemm_i8": ([_T, _T, _T, _T, _T, _S], ctypes.c_int),
     "ql_gemm_16": ([_T, _T, _T, _T, _S], ctypes.c_int),
     "ql_rmsnorm_quant_fp8": ([_T, ctypes.c_float, _T, _T, _S], ctypes.c_int),

@@ -3,7 +3,8 @@
     x -> RMSNorm (eps, weight 1) + per-token e4m3 quantize
       -> gate/up projection (fp8 GEMM, per-token x per-output-channel scales in the epilogue)
       -> SwiGLU + per-token e4m3 re-quantize
-      -> down projection (fp8 GEMM)  -> sum over ranks (NCCL all-reduce)
+      -> down projection (fp8 GEMM)  -> sum over ranks (added into every rank's output by the GEMM's
+         epilogue through NVSwitch replication, or an NCCL all-reduce where that is unavailable)
 
 Sharding follows the usual column-/row-parallel split: every rank holds `inter / world` columns of
 the gate and up projections (no exchange needed before SwiGLU) and the matching rows of the down
@@ -19,6 +20,7 @@ import torch
 from . import _lib
 from . import dtypes as dt
 from . import ops
+from . import peer
 from .linear import gemm_fp8
 from .tensor import current_stream, ql_view
 
@@ -61,8 +63,16 @@ class QuantizedMLP:
     """One rank's shard of the block.  `w_gate`, `w_up`: [inter_local, hidden]; `w_down`: [hidden, inter_local]
     (bf16 / f16, Linear's [out, in] layout).  Weights are quantized once, here."""
 
-    def __init__(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, eps: float = 1e-5, group=None):
+    def __init__(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, eps: float = 1e-5, group=None,
+                 fused_all_reduce="auto"):
+        """`fused_all_reduce`: True = the down projection's epilogue adds its partial result into every rank's
+        output through NVSwitch replication (qlinear.peer); False = NCCL all-reduce after the GEMM; "auto" =
+        fused when the box supports it and the group has several ranks."""
         self.eps, self.group = eps, group
+        if fused_all_reduce == "auto":
+            fused_all_reduce = group is not None and peer.available(group)
+        self.fused_all_reduce = bool(fused_all_reduce) and group is not None
+        self._step = 0
         self.hidden, self.inter_local = w_gate.shape[1], w_gate.shape[0]
         self.out_dtype = dt.from_torch(w_gate.dtype)
         self.wq_gu, self.s_gu = quantize_per_channel_fp8(torch.cat([w_gate, w_up], dim=0).contiguous())
@@ -78,6 +88,10 @@ class QuantizedMLP:
                          "gu": torch.empty((T, 2 * I), dtype=od, device=device),
                          "aq": torch.empty((T, I), dtype=torch.float8_e4m3fn, device=device), "sa": torch.empty((T,), dtype=torch.float32, device=device),
                          "y": torch.empty((T, H), dtype=od, device=device)}
+            if self.fused_all_reduce:
+                # two output buffers, used in turn: while the ranks add into one, the other is cleared for
+                # the next call, and one barrier per call separates "all added" from "anyone reads"
+                self._buf["y_peer"] = [peer.PeerTensor((T, H), od, self.group) for _ in range(2)]
         return self._buf
 
     # the four local stages, separately callable so that a benchmark can time them
@@ -98,11 +112,35 @@ class QuantizedMLP:
             import torch.distributed as dist
             dist.all_reduce(b["y"], group=self.group)
 
+    # the fused form of the last two stages
+    def stage_down_add_all(self, b):
+        peer.gemm_fp8_peer(b["aq"], self.wq_d, b["sa"], self.s_d, b["y_peer"][self._step % 2], peer.ADD_ALL)
+
+    def stage_clear_next(self, b):
+        b["y_peer"][(self._step + 1) % 2].local.zero_()
+
+    def stage_barrier(self, b):
+        b["y_peer"][self._step % 2].barrier()
+
+    def reset_peer_buffers(self):
+        """Zero both output buffers on every rank (after anything that added into them out of turn)."""
+        for t in self._buf.get("y_peer", []):
+            t.local.zero_()
+        for t in self._buf.get("y_peer", [])[:1]:
+            t.barrier()
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         b = self._buffers(x.shape[0], x.device)
         self.stage_norm_quant(x, b)
         self.stage_gate_up(b)
         self.stage_swiglu_quant(b)
+        if self.fused_all_reduce:
+            self.stage_down_add_all(b)
+            self.stage_clear_next(b)
+            self.stage_barrier(b)
+            y = b["y_peer"][self._step % 2].local
+            self._step += 1
+            return y
         self.stage_down(b)
         self.stage_all_reduce(b)
         return b["y"]

@@ -1,0 +1,96 @@
+"""One rank of the multi-GPU check of the fused GEMM + collective (run by tests/test_peer_gpu.py under
+torchrun, one process per GPU).  Every rank draws the same operands from the same seed, so each can
+compute the unsharded result by itself with the ordinary single-GPU GEMM and compare."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(ROOT, "tensorrt-incubator_b200"))
+import qlinear as ql  # noqa: E402
+from qlinear import peer  # noqa: E402
+
+
+def fp8(shape, seed, std, device):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(shape, generator=g) * std).to(torch.float8_e4m3fn).to(device)
+
+
+def rel_err(got, want):
+    got, want = got.float(), want.float()
+    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-6))
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    if not peer.available():
+        if rank == 0:
+            print("PEER UNAVAILABLE")
+        dist.destroy_process_group()
+        return
+
+    for (M, N, K) in [(256, 512, 512), (2048, 4096, 1024)]:     # one-CTA kernel; CTA-pair kernel
+        xq, wq = fp8((M, K), 11, 1.0, dev), fp8((N, K), 12, 1.0, dev)
+        sx = torch.rand(M, generator=torch.Generator().manual_seed(13)).add(0.5).to(dev)
+        sw = torch.rand(N, generator=torch.Generator().manual_seed(14)).add(0.5).mul(1e-2).to(dev)
+        full = ql.gemm_fp8(xq, wq, sx, sw)
+
+        # column-parallel + store into every replica: bit-exact with the unsharded GEMM
+        nl = N // world
+        dest = peer.PeerTensor((M, N), torch.bfloat16)
+        peer.gemm_fp8_peer(xq, wq[rank * nl:(rank + 1) * nl].contiguous(), sx, sw[rank * nl:(rank + 1) * nl].contiguous(),
+                           dest, peer.STORE_ALL, col0=rank * nl)
+        dest.barrier()
+        torch.cuda.synchronize()
+        assert torch.equal(dest.local, full), f"rank {rank}: STORE_ALL differs for {(M, N, K)}"
+
+        # row-parallel (K split) + add into every replica: equals the unsharded GEMM up to bf16 rounding of the partial sums
+        kl = K // world
+        acc = peer.PeerTensor((M, N), torch.bfloat16)
+        for _ in range(2):   # twice, to check the clear / barrier protocol as well
+            acc.local.zero_()
+            acc.barrier()
+            peer.gemm_fp8_peer(xq[:, rank * kl:(rank + 1) * kl].contiguous(), wq[:, rank * kl:(rank + 1) * kl].contiguous(),
+                               sx, sw, acc, peer.ADD_ALL)
+            acc.barrier()
+            torch.cuda.synchronize()
+            e = rel_err(acc.local, full)
+            assert e < 2e-2, f"rank {rank}: ADD_ALL off by {e} for {(M, N, K)}"
+        # every rank holds the same sum, bit for bit
+        mine = acc.local.view(torch.int16).to(torch.int32).sum(dtype=torch.int64).reshape(1)
+        lo, hi = mine.clone(), mine.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        assert int(lo) == int(hi), "replicas differ after ADD_ALL"
+
+    # the MLP block: fused all-reduce against the NCCL all-reduce on the same shards
+    T, H, I = 512, 1024, 2048
+    il = I // world
+    g = torch.Generator(device="cpu").manual_seed(100 + rank)
+    def w(shape):
+        return (torch.randn(shape, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+    wg, wu, wd = w((il, H)), w((il, H)), w((H, il))
+    x = (torch.randn((T, H), generator=torch.Generator().manual_seed(5))).to(torch.bfloat16).to(dev)
+    fused = ql.QuantizedMLP(wg, wu, wd, group=dist.group.WORLD, fused_all_reduce=True)
+    plain = ql.QuantizedMLP(wg, wu, wd, group=dist.group.WORLD, fused_all_reduce=False)
+    want = plain(x).clone()
+    for i in range(3):
+        got = fused(x)
+        torch.cuda.synchronize()
+        e = rel_err(got, want)
+        assert e < 2e-2, f"rank {rank}: fused MLP call {i} off by {e}"
+    assert ql.lib().ql_gemm_status(None) == 0
+    dist.barrier()
+    if rank == 0:
+        print("PEER OK")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
