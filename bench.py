@@ -440,7 +440,8 @@ class Fp8Mlp(Workload):
         self.mlp = ql.QuantizedMLP(w((il, self.H)), w((il, self.H)), w((self.H, il)), eps=1e-5, group=(dist.group.WORLD if dist is not None else None),
                                     fused_all_reduce=fused)
         self.parallelism = (f"tensor-parallel over {self.world} GPUs: gate/up column-parallel, down row-parallel, " +
-                            ("partial results added into every GPU's output by the GEMM epilogue (multimem.red through NVSwitch), one barrier per step"
+                            ("reduction done by the down-projection epilogue over peer memory (2 GPUs: multimem.red into both outputs; "
+                             "more: red into the owner's rows, then the owners broadcast with multimem.st)"
                              if self.mlp.fused_all_reduce else "NCCL all-reduce"))
         gx = torch.Generator(device="cpu").manual_seed(seed)
         self.x_host = torch.randn((self.T, self.H), generator=gx, dtype=torch.float32).to(torch.bfloat16).pin_memory()
@@ -458,9 +459,13 @@ class Fp8Mlp(Workload):
             def finish():
                 self.mlp.stage_barrier(self.buf)
                 self.mlp._step += 1
-            ps += [("down_gemm_add_all", lambda: self.mlp.stage_down_add_all(self.buf)) + down,
-                   ("clear_next_output", lambda: self.mlp.stage_clear_next(self.buf), 0, 2 * T * H, "hbm"),
-                   ("barrier", finish, 0, 0, "nvlink")]
+            scatter = self.mlp._scatter(self.buf)
+            ps += [("down_gemm_add_owner" if scatter else "down_gemm_add_all", lambda: self.mlp.stage_down_add(self.buf)) + down,
+                   ("clear_next_output", lambda: self.mlp.stage_clear_next(self.buf), 0, 2 * T * H // (self.world if scatter else 1), "hbm")]
+            if scatter:
+                ps += [("barrier_sums", lambda: self.mlp.stage_barrier(self.buf), 0, 0, "nvlink"),
+                       ("broadcast_owned_rows", lambda: self.mlp.stage_broadcast_owned(self.buf), 0, 2 * T * H * (self.world - 1) // self.world, "nvlink")]
+            ps.append(("barrier", finish, 0, 0, "nvlink"))
         else:
             ps.append(("down_gemm", lambda: self.mlp.stage_down(self.buf)) + down)
             if self.world > 1:

@@ -134,20 +134,42 @@ QL_API int ql_gemm_fp8(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor
                        const ql_tensor *sw, ql_tensor *y, void *stream);
 QL_API int ql_gemm_i8(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx,
                       const ql_tensor *sw, ql_tensor *y, void *stream);
-/* The fp8 GEMM with its collective done by the epilogue (tensor-parallel layers over the GPUs of one box).
+/* ---- Tensor-parallel layers over the GPUs of one box: the fp8 GEMM with its collective done by the epilogue.
  * No reference counterpart: the reference has no multi-GPU execution of this path.
- * y->data points at element (0, 0) of this rank's [M, N] slice inside a buffer whose rows are `ldy`
- * elements apart.  With QL_PEER_NONE the buffer is ordinary device memory.  With the other modes it is
- * an address in an NVSwitch replication group (CUDA multicast object) that maps the same buffer on every
- * GPU of the group, and each finished 16 bytes go to all of them in one posted write:
- *   QL_PEER_STORE_ALL  stores the slice in every replica: column-parallel GEMM + all-gather;
- *   QL_PEER_ADD_ALL    adds the slice into every replica (sum in the output type): row-parallel GEMM +
- *                      all-reduce; the replicas must hold zeros (or a bias) before any rank starts.
- * The kernel waits on no peer.  The caller orders it after the buffer is ready on all ranks and puts a
- * cross-rank barrier after it before anyone reads.  Peer modes need N % 32 == 0 and ldy % 8 == 0. */
-typedef enum { QL_PEER_NONE = 0, QL_PEER_STORE_ALL = 1, QL_PEER_ADD_ALL = 2 } ql_peer_mode;
-QL_API int ql_gemm_fp8_peer(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx,
-                            const ql_tensor *sw, ql_tensor *y, int64_t ldy, int peer_mode, void *stream);
+ *
+ * A ql_peer_buffer describes one buffer that exists on every rank ("replica"), one process per GPU:
+ *   replica[r]  the address, in this process, of rank r's copy (peer-mapped device memory; replica[rank] is local);
+ *   all         an address in an NVSwitch replication group (CUDA multicast object) covering all replicas: a
+ *               `multimem` write to it lands in every replica.
+ * The caller allocates and maps the buffer (any symmetric-memory allocator; the Python layer uses torch's).
+ *
+ * ql_gemm_fp8_peer computes this rank's [M, N] result and writes it at element offset `offset` of a row-major
+ * buffer with `ldy` elements per row, in one of three ways:
+ *   QL_PEER_STORE_ALL  stores it in every replica: column-parallel GEMM + all-gather in one kernel;
+ *   QL_PEER_ADD_ALL    adds it into every replica (sum in the output type): row-parallel GEMM + all-reduce in
+ *                      one kernel; every replica receives world x the data, so this suits two ranks;
+ *   QL_PEER_ADD_OWNER  adds each row into the replica of the rank that owns it (rank r owns rows
+ *                      [r * M / world, (r + 1) * M / world), M / world a multiple of 128): row-parallel GEMM +
+ *                      reduce-scatter in one kernel; ql_peer_broadcast of the owned rows completes the all-reduce.
+ * Adds need zeros (or a bias) in the target rows before any rank starts.  The kernels wait on no peer; all their
+ * remote writes are posted.  ql_peer_barrier orders ranks: work queued before it on every rank's stream is
+ * complete and visible before work queued after it starts on any rank.  `flags` is a peer buffer of
+ * (world + 1) uint32, zero-initialised, used by nothing else.  Its wait is bounded (about ten seconds); a rank
+ * that gives up records it for ql_gemm_status.  Peer modes need N % 32 == 0, ldy % 8 == 0, offset % 8 == 0. */
+#define QL_MAX_PEERS 8
+typedef enum { QL_PEER_NONE = 0, QL_PEER_STORE_ALL = 1, QL_PEER_ADD_ALL = 2, QL_PEER_ADD_OWNER = 3 } ql_peer_mode;
+typedef struct {
+  void *replica[QL_MAX_PEERS];
+  void *all;
+  int32_t world;
+  int32_t rank;
+} ql_peer_buffer;
+QL_API int ql_gemm_fp8_peer(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx, const ql_tensor *sw,
+                            const ql_peer_buffer *dest, int32_t y_dtype, int64_t ldy, int64_t offset, int peer_mode,
+                            void *stream);
+QL_API int ql_peer_barrier(const ql_peer_buffer *flags, void *stream);
+/* copies bytes [offset, offset + bytes) of this rank's replica to the same range of every replica (16-byte units) */
+QL_API int ql_peer_broadcast(const ql_peer_buffer *buf, int64_t offset, int64_t bytes, void *stream);
 /* 16-bit GEMM Y = (X . W^T) * sw, X and W both bf16 or both f16 ([M,K], [N,K]); sw may be null. */
 QL_API int ql_gemm_16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *sw, ql_tensor *y,
                       void *stream);

@@ -43,14 +43,17 @@ struct GemmArgs {
   int *status;
   int64_t ldy;     // elements between rows of Y (N, or the full width when Y is a column slice)
   int peer_mode;   // QL_PEER_*: how the epilogue writes Y
+  int rows_per_rank;               // QL_PEER_ADD_OWNER: rows [r * rows_per_rank, ...) belong to rank r
+  void *owner_y[QL_MAX_PEERS];     // QL_PEER_ADD_OWNER: Y as it lies in each rank's replica
 };
 
 // 16 bytes of finished output.  Locally: a streaming store (written once, never re-read here, so it
 // stays out of L2's way).  For the peer modes `p` is an address of an NVSwitch replication group that
 // maps the same buffer on every GPU of the group: one `multimem.st` lands the tile in all of them
 // (an all-gather done by the epilogue), one `multimem.red` adds it into all of them (an all-reduce
-// done by the epilogue, summing in the output type as the collective library does).  Both are posted
-// writes: the kernel waits on no peer, and they are complete when the kernel is.
+// done by the epilogue, summing in the output type as the collective library does), and a plain `red`
+// through a peer mapping adds it into the one replica that owns the row (a reduce-scatter done by the
+// epilogue).  All are posted writes: the kernel waits on no peer, and they are complete when the kernel is.
 template <typename OutT>
 __device__ __forceinline__ void store_out16(OutT *p, const uint4 &o, int peer_mode) {
   if (peer_mode == QL_PEER_NONE) {
@@ -59,12 +62,20 @@ __device__ __forceinline__ void store_out16(OutT *p, const uint4 &o, int peer_mo
     asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(__uint_as_float(o.x)),
                  "f"(__uint_as_float(o.y)), "f"(__uint_as_float(o.z)), "f"(__uint_as_float(o.w))
                  : "memory");
-  } else if constexpr (FloatIO<OutT>::kDtype == QL_F16) {
-    asm volatile("multimem.red.relaxed.sys.global.add.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
-                 : "memory");
-  } else {
-    asm volatile("multimem.red.relaxed.sys.global.add.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
-                 : "memory");
+  } else if (peer_mode == QL_PEER_ADD_ALL) {
+    if constexpr (FloatIO<OutT>::kDtype == QL_F16)
+      asm volatile("multimem.red.relaxed.sys.global.add.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
+                   : "memory");
+    else
+      asm volatile("multimem.red.relaxed.sys.global.add.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
+                   : "memory");
+  } else { // QL_PEER_ADD_OWNER: p already points into the owner's replica
+    if constexpr (FloatIO<OutT>::kDtype == QL_F16)
+      asm volatile("red.relaxed.sys.global.add.noftz.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
+                   : "memory");
+    else
+      asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
+                   : "memory");
   }
 }
 
@@ -91,6 +102,8 @@ constexpr int kPeerStageBytes = 4 * kPeerStageWarp;
 
 template <typename OutT>
 __device__ __forceinline__ void peer_flush(const uint8_t *stage, int lane, OutT *Y, const GemmArgs &args, int m_base, int n_base, int ncols) {
+  // the 32 rows of a warp lie inside one 128-row tile, and owners change at multiples of 128 rows
+  if (args.peer_mode == QL_PEER_ADD_OWNER) Y = static_cast<OutT *>(args.owner_y[min(m_base / args.rows_per_rank, QL_MAX_PEERS - 1)]);
   __syncwarp();
   const int lanes_per_row = ncols / 8, rows_per_instr = 32 / lanes_per_row;
   const int rsub = lane / lanes_per_row, cw = lane % lanes_per_row;
@@ -867,7 +880,7 @@ int check_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_
 
 template <int KIND>
 int run_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_tensor *sa, const ql_tensor *sb, ql_tensor *y,
-             void *stream, int64_t ldy = 0, int peer_mode = QL_PEER_NONE) {
+             void *stream, int64_t ldy = 0, int peer_mode = QL_PEER_NONE, const ql_peer_buffer *dest = nullptr, int64_t offset = 0) {
   const int64_t M = a->shape[0], K = a->shape[1], N = b->shape[0];
   if (M == 0 || N == 0) return QL_OK;
   const int esize = (KIND == KIND_F8 || KIND == KIND_I8) ? 1 : 2;
@@ -894,6 +907,12 @@ int run_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_te
   }
   args.ldy = ldy > 0 ? ldy : N;
   args.peer_mode = peer_mode;
+  args.rows_per_rank = 1;
+  for (int r = 0; r < QL_MAX_PEERS; r++) args.owner_y[r] = nullptr;
+  if (peer_mode == QL_PEER_ADD_OWNER) {
+    args.rows_per_rank = (int)(M / dest->world);
+    for (int r = 0; r < dest->world; r++) args.owner_y[r] = static_cast<char *>(dest->replica[r]) + offset * 2;
+  }
   args.status = device_status_word();
   if (!args.status) return set_error(QL_ERR_CUDA, "%s: could not allocate the device status word", op);
   cudaStream_t st = (cudaStream_t)stream;
@@ -924,19 +943,33 @@ int ql_gemm_fp8(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx, c
   return run_gemm<KIND_F8>("gemm_fp8", xq, wq, sx, sw, y, stream);
 }
 
-int ql_gemm_fp8_peer(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx, const ql_tensor *sw, ql_tensor *y,
-                     int64_t ldy, int peer_mode, void *stream) {
-  int rc = check_gemm("gemm_fp8_peer", xq, wq, sx, sw, y, QL_F8E4M3, QL_F8E4M3);
-  if (rc != QL_OK) return rc;
-  if (peer_mode != QL_PEER_NONE && peer_mode != QL_PEER_STORE_ALL && peer_mode != QL_PEER_ADD_ALL)
+int ql_gemm_fp8_peer(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx, const ql_tensor *sw,
+                     const ql_peer_buffer *dest, int32_t y_dtype, int64_t ldy, int64_t offset, int peer_mode, void *stream) {
+  if (!dest || !xq || !wq) return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_fp8_peer: null argument");
+  if (dest->world < 1 || dest->world > QL_MAX_PEERS || dest->rank < 0 || dest->rank >= dest->world)
+    return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_fp8_peer: bad world / rank (%d / %d)", dest->world, dest->rank);
+  if (peer_mode < QL_PEER_NONE || peer_mode > QL_PEER_ADD_OWNER)
     return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_fp8_peer: unknown peer mode %d", peer_mode);
-  if (ldy < y->shape[1]) return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_fp8_peer: ldy (%lld) is smaller than N (%lld)", (long long)ldy, (long long)y->shape[1]);
+  if (xq->rank != 2 || wq->rank != 2) return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_fp8_peer: operands must be 2-D");
+  const int64_t M = xq->shape[0], N = wq->shape[0];
+  char *base = static_cast<char *>((peer_mode == QL_PEER_STORE_ALL || peer_mode == QL_PEER_ADD_ALL) ? dest->all : dest->replica[dest->rank]);
+  if (!base) return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_fp8_peer: the buffer has no address for this mode");
+  if (offset < 0 || ldy < N) return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_fp8_peer: ldy (%lld) is smaller than N (%lld)", (long long)ldy, (long long)N);
+  ql_tensor y{base + offset * 2, y_dtype, 2, {M, N}};
+  int rc = check_gemm("gemm_fp8_peer", xq, wq, sx, sw, &y, QL_F8E4M3, QL_F8E4M3);
+  if (rc != QL_OK) return rc;
   if (peer_mode != QL_PEER_NONE) {
-    // the peer stores exist as 16-byte vectors only
-    if (y->shape[1] % 32 != 0 || ldy % 8 != 0 || !aligned16(y->data))
-      return set_error(QL_ERR_UNSUPPORTED, "gemm_fp8_peer: peer modes need N %% 32 == 0, ldy %% 8 == 0 and a 16-byte aligned y");
+    // the peer writes exist as 16-byte vectors only
+    if (N % 32 != 0 || ldy % 8 != 0 || offset % 8 != 0 || !aligned16(base))
+      return set_error(QL_ERR_UNSUPPORTED, "gemm_fp8_peer: peer modes need N %% 32 == 0, ldy %% 8 == 0, offset %% 8 == 0 and a 16-byte aligned buffer");
   }
-  return run_gemm<KIND_F8>("gemm_fp8_peer", xq, wq, sx, sw, y, stream, ldy, peer_mode);
+  if (peer_mode == QL_PEER_ADD_OWNER) {
+    if (M % ((int64_t)dest->world * 128) != 0)
+      return set_error(QL_ERR_UNSUPPORTED, "gemm_fp8_peer: add-to-owner needs M (%lld) to be a multiple of 128 x world", (long long)M);
+    for (int r = 0; r < dest->world; r++)
+      if (!dest->replica[r]) return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_fp8_peer: replica %d has no address", r);
+  }
+  return run_gemm<KIND_F8>("gemm_fp8_peer", xq, wq, sx, sw, &y, stream, ldy, peer_mode, dest, offset);
 }
 
 int ql_gemm_i8(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx, const ql_tensor *sw, ql_tensor *y, void *stream) {

@@ -40,7 +40,16 @@ class QlQdqAttrs(ctypes.Structure):
     _fields_ = [("has_axis", ctypes.c_int32), ("axis", ctypes.c_int32), ("fp8_mode", ctypes.c_int32)]
 
 
-PEER_NONE, PEER_STORE_ALL, PEER_ADD_ALL = 0, 1, 2  # ql_peer_mode
+PEER_NONE, PEER_STORE_ALL, PEER_ADD_ALL, PEER_ADD_OWNER = 0, 1, 2, 3  # ql_peer_mode
+QL_MAX_PEERS = 8
+
+
+class QlPeerBuffer(ctypes.Structure):
+    _fields_ = [("replica", ctypes.c_void_p * QL_MAX_PEERS), ("all", ctypes.c_void_p), ("world", ctypes.c_int32),
+                ("rank", ctypes.c_int32)]
+
+
+_P = ctypes.POINTER(QlPeerBuffer)
 
 # every symbol include/qlinear_b200.h declares, with its ctypes signature
 _T = ctypes.POINTER(QlTensor)
@@ -59,7 +68,9 @@ SIGNATURES = {
     "ql_linear_w8a16": ([_T, _T, _T, _T, _S], ctypes.c_int),
     "ql_linear_w4a16": ([_T, _T, _T, _T, _S], ctypes.c_int),
     "ql_gemm_fp8": ([_T, _T, _T, _T, _T, _S], ctypes.c_int),
-    "ql_gemm_fp8_peer": ([_T, _T, _T, _T, _T, ctypes.c_int64, ctypes.c_int, _S], ctypes.c_int),
+    "ql_gemm_fp8_peer": ([_T, _T, _T, _T, _P, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, _S], ctypes.c_int),
+    "ql_peer_barrier": ([_P, _S], ctypes.c_int),
+    "ql_peer_broadcast": ([_P, ctypes.c_int64, ctypes.c_int64, _S], ctypes.c_int),
     "ql_gemm_i8": ([_T, _T, _T, _T, _T, _S], ctypes.c_int),
     "ql_gemm_16": ([_T, _T, _T, _T, _S], ctypes.c_int),
     "ql_rmsnorm_quant_fp8": ([_T, ctypes.c_float, _T, _T, _S], ctypes.c_int),

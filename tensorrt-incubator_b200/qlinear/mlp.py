@@ -65,10 +65,13 @@ class QuantizedMLP:
 
     def __init__(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, eps: float = 1e-5, group=None,
                  fused_all_reduce="auto"):
-        """`fused_all_reduce`: True = the down projection's epilogue adds its partial result into every rank's
-        output through NVSwitch replication (qlinear.peer); False = NCCL all-reduce after the GEMM; "auto" =
-        fused when the box supports it and the group has several ranks."""
+        """`fused_all_reduce`: True = the down projection's epilogue does the reduction over peer memory
+        (qlinear.peer): with two ranks it adds its partial result into both outputs; with more it adds each row
+        into the output of the rank that owns the row, and the owners then broadcast their rows.  False = NCCL
+        all-reduce after the GEMM; "auto" = fused when the box supports it and the group has several ranks;
+        "scatter" = fused, with the owner protocol whatever the group size."""
         self.eps, self.group = eps, group
+        self._force_scatter = fused_all_reduce == "scatter"   # the more-than-two-ranks protocol on any group size
         if fused_all_reduce == "auto":
             fused_all_reduce = group is not None and peer.available(group)
         self.fused_all_reduce = bool(fused_all_reduce) and group is not None
@@ -113,20 +116,36 @@ class QuantizedMLP:
             dist.all_reduce(b["y"], group=self.group)
 
     # the fused form of the last two stages
-    def stage_down_add_all(self, b):
-        peer.gemm_fp8_peer(b["aq"], self.wq_d, b["sa"], self.s_d, b["y_peer"][self._step % 2], peer.ADD_ALL)
+    def _scatter(self, b):
+        """True when rows have owners (reduce-scatter + broadcast); False when every rank adds into every output."""
+        y = b["y_peer"][0]
+        return (y.world > 2 or self._force_scatter) and b["T"] % (128 * y.world) == 0
+
+    def stage_down_add(self, b):
+        mode = peer.ADD_OWNER if self._scatter(b) else peer.ADD_ALL
+        peer.gemm_fp8_peer(b["aq"], self.wq_d, b["sa"], self.s_d, b["y_peer"][self._step % 2], mode)
 
     def stage_clear_next(self, b):
-        b["y_peer"][(self._step + 1) % 2].local.zero_()
+        nxt = b["y_peer"][(self._step + 1) % 2]
+        if self._scatter(b):   # only the rows this rank owns are added into; the rest is overwritten by broadcasts
+            rows = b["T"] // nxt.world
+            nxt.local[nxt.rank * rows:(nxt.rank + 1) * rows].zero_()
+        else:
+            nxt.local.zero_()
 
     def stage_barrier(self, b):
         b["y_peer"][self._step % 2].barrier()
 
+    def stage_broadcast_owned(self, b):
+        y = b["y_peer"][self._step % 2]
+        rows = b["T"] // y.world
+        y.broadcast_rows(y.rank * rows, rows)
+
     def reset_peer_buffers(self):
         """Zero both output buffers on every rank (after anything that added into them out of turn)."""
         for t in self._buf.get("y_peer", []):
+            t.barrier()
             t.local.zero_()
-        for t in self._buf.get("y_peer", [])[:1]:
             t.barrier()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -135,9 +154,12 @@ class QuantizedMLP:
         self.stage_gate_up(b)
         self.stage_swiglu_quant(b)
         if self.fused_all_reduce:
-            self.stage_down_add_all(b)
+            self.stage_down_add(b)
             self.stage_clear_next(b)
-            self.stage_barrier(b)
+            self.stage_barrier(b)           # every rank's partial sums have landed
+            if self._scatter(b):
+                self.stage_broadcast_owned(b)
+                self.stage_barrier(b)       # every rank's rows have landed
             y = b["y_peer"][self._step % 2].local
             self._step += 1
             return y

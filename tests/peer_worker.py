@@ -62,6 +62,18 @@ def main():
             torch.cuda.synchronize()
             e = rel_err(acc.local, full)
             assert e < 2e-2, f"rank {rank}: ADD_ALL off by {e} for {(M, N, K)}"
+        # reduce-scatter into the owners' rows, then the owners broadcast: the same sum again
+        if M % (128 * world) == 0:
+            rs = peer.PeerTensor((M, N), torch.bfloat16)
+            rows = M // world
+            peer.gemm_fp8_peer(xq[:, rank * kl:(rank + 1) * kl].contiguous(), wq[:, rank * kl:(rank + 1) * kl].contiguous(),
+                               sx, sw, rs, peer.ADD_OWNER)
+            rs.barrier()
+            rs.broadcast_rows(rank * rows, rows)
+            rs.barrier()
+            torch.cuda.synchronize()
+            e = rel_err(rs.local, full)
+            assert e < 2e-2, f"rank {rank}: ADD_OWNER + broadcast off by {e} for {(M, N, K)}"
         # every rank holds the same sum, bit for bit
         mine = acc.local.view(torch.int16).to(torch.int32).sum(dtype=torch.int64).reshape(1)
         lo, hi = mine.clone(), mine.clone()
@@ -70,7 +82,7 @@ def main():
         assert int(lo) == int(hi), "replicas differ after ADD_ALL"
 
     # the MLP block: fused all-reduce against the NCCL all-reduce on the same shards
-    T, H, I = 512, 1024, 2048
+    T, H, I = 1024, 1024, 2048
     il = I // world
     g = torch.Generator(device="cpu").manual_seed(100 + rank)
     def w(shape):
@@ -80,11 +92,13 @@ def main():
     fused = ql.QuantizedMLP(wg, wu, wd, group=dist.group.WORLD, fused_all_reduce=True)
     plain = ql.QuantizedMLP(wg, wu, wd, group=dist.group.WORLD, fused_all_reduce=False)
     want = plain(x).clone()
-    for i in range(3):
-        got = fused(x)
-        torch.cuda.synchronize()
-        e = rel_err(got, want)
-        assert e < 2e-2, f"rank {rank}: fused MLP call {i} off by {e}"
+    scattered = ql.QuantizedMLP(wg, wu, wd, group=dist.group.WORLD, fused_all_reduce="scatter")
+    for name, mlp in (("add-all", fused), ("add-owner", scattered)):
+        for i in range(3):
+            got = mlp(x)
+            torch.cuda.synchronize()
+            e = rel_err(got, want)
+            assert e < 2e-2, f"rank {rank}: fused MLP ({name}) call {i} off by {e}"
     assert ql.lib().ql_gemm_status(None) == 0
     dist.barrier()
     if rank == 0:
