@@ -439,14 +439,16 @@ class Fp8Mlp(Workload):
             return (torch.randn(shape, generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
         self.mlp = ql.QuantizedMLP(w((il, self.H)), w((il, self.H)), w((self.H, il)), eps=1e-5, group=(dist.group.WORLD if dist is not None else None),
                                     fused_all_reduce=fused)
-        self.parallelism = (f"tensor-parallel over {self.world} GPUs: gate/up column-parallel, down row-parallel, " +
-                            ("reduction done by the down-projection epilogue over peer memory (2 GPUs: multimem.red into both outputs; "
-                             "more: red into the owner's rows, then the owners broadcast with multimem.st)"
-                             if self.mlp.fused_all_reduce else "NCCL all-reduce"))
         gx = torch.Generator(device="cpu").manual_seed(seed)
         self.x_host = torch.randn((self.T, self.H), generator=gx, dtype=torch.float32).to(torch.bfloat16).pin_memory()
         self.x = self.x_host.to(device)
         self.buf = self.mlp._buffers(self.T, device)
+        proto = self.buf["protocol"]
+        self.parallelism = (f"tensor-parallel over {self.world} GPUs: gate/up column-parallel, down row-parallel, " +
+                            {"add_all": "partial sums added into both GPUs' outputs by the down-projection epilogue (multimem.red), one barrier",
+                             "add_owner": "partial sums added into the owner's rows by the down-projection epilogue (red over peer memory), "
+                                          "barrier, owners broadcast their rows (multimem.st), barrier",
+                             "nccl": "NCCL all-reduce"}[proto])
         self.y_host = torch.empty((self.T, self.H), dtype=torch.bfloat16).pin_memory()
 
     def parts(self):
@@ -455,7 +457,7 @@ class Fp8Mlp(Workload):
               ("gate_up_gemm", lambda: self.mlp.stage_gate_up(self.buf), 2 * T * H * 2 * il, T * H + 2 * il * H + 2 * T * 2 * il, "tensor_fp8"),
               ("swiglu_quant", lambda: self.mlp.stage_swiglu_quant(self.buf), 0, 2 * T * 2 * il + T * il, "hbm")]
         down = (2 * T * il * H, T * il + H * il + 2 * T * H, "tensor_fp8")
-        if self.mlp.fused_all_reduce:
+        if self.buf["protocol"] != "nccl":
             def finish():
                 self.mlp.stage_barrier(self.buf)
                 self.mlp._step += 1

@@ -115,21 +115,42 @@ __device__ __forceinline__ void peer_flush(const uint8_t *stage, int lane, OutT 
   __syncwarp();
 }
 
+// sa * (scale of columns n .. n+31) for one chunk.  Issued before the accumulators are fetched from tensor memory,
+// so that the two latencies overlap; the per-column loads are 16-byte loads every lane shares.
+__device__ __forceinline__ void load_chunk_scales(const GemmArgs &args, int n, float sa, float sb_scalar, float (&s)[32]) {
+  if (!args.sb || args.sb_n == 1) {
+    const float v = sa * sb_scalar;
+#pragma unroll
+    for (int j = 0; j < 32; j++) s[j] = v;
+  } else if (n + 32 <= args.N && (reinterpret_cast<uintptr_t>(args.sb) & 15) == 0) {
+    const float4 *p = reinterpret_cast<const float4 *>(args.sb + n);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const float4 q = __ldg(p + j);
+      s[4 * j] = sa * q.x;
+      s[4 * j + 1] = sa * q.y;
+      s[4 * j + 2] = sa * q.z;
+      s[4 * j + 3] = sa * q.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; j++) s[j] = sa * ((n + j < args.N) ? __ldg(args.sb + n + j) : 0.f);
+  }
+}
+
 // One epilogue warp's 32 rows x 32 columns of accumulators (lane = row m, columns n .. n+31) -> scaled output.
 // `stage` = this warp's staging rows (peer modes only), `c` = index of the chunk within the tile, `last` = no
 // chunk follows in this tile.
 template <int KIND, typename OutT>
-__device__ __forceinline__ void emit_chunk(const GemmArgs &args, OutT *Y, bool vec_ok, const uint32_t (&r)[32], int m, int n, float sa,
-                                           float sb_scalar, uint8_t *stage, int lane, int c, bool last) {
+__device__ __forceinline__ void emit_chunk(const GemmArgs &args, OutT *Y, bool vec_ok, const uint32_t (&r)[32], int m, int n,
+                                           const float (&s)[32], uint8_t *stage, int lane, int c, bool last) {
   const bool peer = args.peer_mode != QL_PEER_NONE; // the same for every thread of the grid
   if (!peer && !(m < args.M && n < args.N)) return;
   float v[32];
 #pragma unroll
   for (int j = 0; j < 32; j++) {
     float acc = (KIND == KIND_I8) ? (float)(int)r[j] : __uint_as_float(r[j]);
-    float s = sa * sb_scalar;
-    if (args.sb && args.sb_n != 1) s = sa * ((n + j < args.N) ? __ldg(args.sb + n + j) : 0.f);
-    v[j] = acc * s;
+    v[j] = acc * s[j];
   }
   if (peer) {
     uint8_t *p = stage + lane * kPeerRowBytes + (c & 1) * 64;
@@ -295,9 +316,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll 1
       for (int c = 0; c < BN / 32; c++) {
         uint32_t r[32];
-        tmem_load_32(taddr + c * 32, r);
+        float sc[32];
         const int n = n0 + c * 32;
-        emit_chunk<KIND, OutT>(args, Y, vec_ok, r, m, n, sa, sb_scalar, stage, lane, c, c == BN / 32 - 1);
+        load_chunk_scales(args, n, sa, sb_scalar, sc);
+        tmem_load_32(taddr + c * 32, r);
+        emit_chunk<KIND, OutT>(args, Y, vec_ok, r, m, n, sc, stage, lane, c, c == BN / 32 - 1);
       }
       tc_fence_before();
       __syncwarp();
@@ -524,9 +547,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll 1
       for (int c = 0; c < BN2 / 32; c++) {
         uint32_t r[32];
-        tmem_load_32(taddr + c * 32, r);
+        float sc[32];
         const int n = n0 + c * 32;
-        emit_chunk<KIND, OutT>(args, Y, vec_ok, r, m, n, sa, sb_scalar, stage, lane, c, c == BN2 / 32 - 1);
+        load_chunk_scales(args, n, sa, sb_scalar, sc);
+        tmem_load_32(taddr + c * 32, r);
+        emit_chunk<KIND, OutT>(args, Y, vec_ok, r, m, n, sc, stage, lane, c, c == BN2 / 32 - 1);
       }
       tc_fence_before();
       __syncwarp();
@@ -704,9 +729,11 @@ gemm_tc2w_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll 1
         for (int c = 0; c < BN2 / 32; c++) {
           uint32_t r[32];
-          tmem_load_32(taddr + c * 32, r);
+          float sc[32];
           const int n = nt * 512 + h * BN2 + c * 32;
-          emit_chunk<KIND, OutT>(args, Y, vec_ok, r, m, n, sa, sb_scalar, nullptr, lane, c, c == BN2 / 32 - 1);
+          load_chunk_scales(args, n, sa, sb_scalar, sc);
+          tmem_load_32(taddr + c * 32, r);
+          emit_chunk<KIND, OutT>(args, Y, vec_ok, r, m, n, sc, nullptr, lane, c, c == BN2 / 32 - 1);
         }
         tc_fence_before();
         __syncwarp();

@@ -91,11 +91,28 @@ class QuantizedMLP:
                          "gu": torch.empty((T, 2 * I), dtype=od, device=device),
                          "aq": torch.empty((T, I), dtype=torch.float8_e4m3fn, device=device), "sa": torch.empty((T,), dtype=torch.float32, device=device),
                          "y": torch.empty((T, H), dtype=od, device=device)}
+            world = 1
             if self.fused_all_reduce:
+                import torch.distributed as dist
+                world = dist.get_world_size(self.group)
+            # Adding into every output is only used with two ranks: with more, the partial sums would reach each
+            # output in a different order and the ranks' results would differ in the last bit.  With owners the
+            # sum of a row is formed once and copied.
+            if world == 2 and not self._force_scatter:
+                self._buf["protocol"] = "add_all"
+            elif world >= 2 and T % (128 * world) == 0:
+                self._buf["protocol"] = "add_owner"
+            else:
+                self._buf["protocol"] = "nccl"
+            if self._buf["protocol"] != "nccl":
                 # two output buffers, used in turn: while the ranks add into one, the other is cleared for
-                # the next call, and one barrier per call separates "all added" from "anyone reads"
+                # the next call, and a barrier separates "all added" from "anyone reads"
                 self._buf["y_peer"] = [peer.PeerTensor((T, H), od, self.group) for _ in range(2)]
         return self._buf
+
+    def protocol(self, T, device) -> str:
+        """How the down projection's partial sums are combined for `T` tokens: add_all, add_owner or nccl."""
+        return self._buffers(T, device)["protocol"]
 
     # the four local stages, separately callable so that a benchmark can time them
     def stage_norm_quant(self, x, b):
@@ -118,8 +135,7 @@ class QuantizedMLP:
     # the fused form of the last two stages
     def _scatter(self, b):
         """True when rows have owners (reduce-scatter + broadcast); False when every rank adds into every output."""
-        y = b["y_peer"][0]
-        return (y.world > 2 or self._force_scatter) and b["T"] % (128 * y.world) == 0
+        return b["protocol"] == "add_owner"
 
     def stage_down_add(self, b):
         mode = peer.ADD_OWNER if self._scatter(b) else peer.ADD_ALL
@@ -153,7 +169,7 @@ class QuantizedMLP:
         self.stage_norm_quant(x, b)
         self.stage_gate_up(b)
         self.stage_swiglu_quant(b)
-        if self.fused_all_reduce:
+        if b["protocol"] != "nccl":
             self.stage_down_add(b)
             self.stage_clear_next(b)
             self.stage_barrier(b)           # every rank's partial sums have landed

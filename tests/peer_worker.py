@@ -24,6 +24,15 @@ def rel_err(got, want):
     return float((got - want).abs().max() / want.abs().max().clamp_min(1e-6))
 
 
+def same_everywhere(t):
+    """True when every rank holds the same bits."""
+    mine = t.view(torch.int16).to(torch.int32).sum(dtype=torch.int64).reshape(1)
+    lo, hi = mine.clone(), mine.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    return int(lo) == int(hi)
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
@@ -74,12 +83,11 @@ def main():
             torch.cuda.synchronize()
             e = rel_err(rs.local, full)
             assert e < 2e-2, f"rank {rank}: ADD_OWNER + broadcast off by {e} for {(M, N, K)}"
-        # every rank holds the same sum, bit for bit
-        mine = acc.local.view(torch.int16).to(torch.int32).sum(dtype=torch.int64).reshape(1)
-        lo, hi = mine.clone(), mine.clone()
-        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
-        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
-        assert int(lo) == int(hi), "replicas differ after ADD_ALL"
+            assert same_everywhere(rs.local), "replicas differ after ADD_OWNER + broadcast"
+        # with two ranks a + b = b + a, so adding into every replica leaves them identical; with more ranks
+        # the order of arrival differs per replica, which is why the MLP then uses owners
+        if world == 2:
+            assert same_everywhere(acc.local), "replicas differ after ADD_ALL"
 
     # the MLP block: fused all-reduce against the NCCL all-reduce on the same shards
     T, H, I = 1024, 1024, 2048
@@ -93,12 +101,14 @@ def main():
     plain = ql.QuantizedMLP(wg, wu, wd, group=dist.group.WORLD, fused_all_reduce=False)
     want = plain(x).clone()
     scattered = ql.QuantizedMLP(wg, wu, wd, group=dist.group.WORLD, fused_all_reduce="scatter")
-    for name, mlp in (("add-all", fused), ("add-owner", scattered)):
+    assert fused.protocol(T, dev) == ("add_all" if world == 2 else "add_owner") and scattered.protocol(T, dev) == "add_owner"
+    for name, mlp in (("auto", fused), ("add-owner", scattered)):
         for i in range(3):
             got = mlp(x)
             torch.cuda.synchronize()
             e = rel_err(got, want)
             assert e < 2e-2, f"rank {rank}: fused MLP ({name}) call {i} off by {e}"
+            assert same_everywhere(got), f"fused MLP ({name}) call {i}: ranks disagree"
     assert ql.lib().ql_gemm_status(None) == 0
     dist.barrier()
     if rank == 0:
