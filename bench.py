@@ -30,7 +30,17 @@ L2_BYTES = 126 * 1024 * 1024
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of each workload's dominant
 # kernel, from the ncu captures summarised under profiles/ (None until a capture exists).
-TRAFFIC = {}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of each part, from the ncu captures summarised under
+# profiles/ (one B200, 1 GPU workloads; parts made of two kernels give the sum of both)
+TRAFFIC = {
+    "config1_int8_qdq_round_trip:fused_qdq": 99_742_976,      # output partly still dirty in L2 when the kernel ends
+    "config2_w8a16_linear:M=1": 45_141_760, "config2_w8a16_linear:M=16": 45_265_152, "config2_w8a16_linear:M=128": 46_203_648,
+    "config2_w8a16_linear:M=2048": 210_927_104,               # widen 78.6 MB + GEMM 132.3 MB
+    "config3_w4a16_linear:M=1": 8_668_416, "config3_w4a16_linear:M=8": 8_726_016, "config3_w4a16_linear:M=32": 8_924_160,
+    "config4_fp8_w8a8_gemm:fp8_gemm": 1_593_066_736,
+    "config5_fp8_mlp_block:rmsnorm_quant": 72_779_008, "config5_fp8_mlp_block:gate_up_gemm": 1_503_679_224,
+    "config5_fp8_mlp_block:swiglu_quant": 557_469_696, "config5_fp8_mlp_block:down_gemm": 1_941_525_872,
+}
 
 
 def measured_peaks():
