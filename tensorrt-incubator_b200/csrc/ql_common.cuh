@@ -76,10 +76,12 @@ __device__ __forceinline__ IdxT scale_idx(const ScaleGeom &g, IdxT i) {
   return ((i / (IdxT)g.a) % (IdxT)g.b) * (IdxT)g.c + (i % (IdxT)g.d) / (IdxT)g.e;
 }
 
+// Plain loads on purpose: the 16-bit overloads of __ldg are non-volatile inline assembly, which the compiler may
+// hoist above a null check of `p` (it did, in a GEMM epilogue called without scales: an illegal address).
 __device__ __forceinline__ float load_scale(const void *p, int dtype, int64_t i) {
-  if (dtype == QL_F32) return __ldg(reinterpret_cast<const float *>(p) + i);
-  if (dtype == QL_F16) return __half2float(__ldg(reinterpret_cast<const __half *>(p) + i));
-  return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16 *>(p) + i));
+  if (dtype == QL_F32) return reinterpret_cast<const float *>(p)[i];
+  if (dtype == QL_F16) return __half2float(reinterpret_cast<const __half *>(p)[i]);
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p)[i]);
 }
 
 template <typename T> struct FloatIO;

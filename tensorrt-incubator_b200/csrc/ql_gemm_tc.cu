@@ -33,7 +33,8 @@ constexpr int kGemmThreads = 192;
 struct GemmArgs {
   void *Y;
   const float *sa; // null = 1, else one value (sa_n == 1) or one per row of A
-  const float *sb; // null = 1, else one value (sb_n == 1) or one per row of B
+  const void *sb;  // null = 1, else one value (sb_n == 1) or one per row of B, of type sb_dtype
+  int sb_dtype;
   int sa_n, sb_n;
   int M, N;
   int num_kb;      // K blocks of 128 bytes (the last may be partial: TMA fills zeros)
@@ -122,8 +123,8 @@ __device__ __forceinline__ void load_chunk_scales(const GemmArgs &args, int n, f
     const float v = sa * sb_scalar;
 #pragma unroll
     for (int j = 0; j < 32; j++) s[j] = v;
-  } else if (n + 32 <= args.N && (reinterpret_cast<uintptr_t>(args.sb) & 15) == 0) {
-    const float4 *p = reinterpret_cast<const float4 *>(args.sb + n);
+  } else if (n + 32 <= args.N && (reinterpret_cast<uintptr_t>(args.sb) & 15) == 0 && args.sb_dtype == QL_F32) {
+    const float4 *p = reinterpret_cast<const float4 *>(static_cast<const float *>(args.sb) + n);
 #pragma unroll
     for (int j = 0; j < 8; j++) {
       const float4 q = __ldg(p + j);
@@ -132,9 +133,30 @@ __device__ __forceinline__ void load_chunk_scales(const GemmArgs &args, int n, f
       s[4 * j + 2] = sa * q.z;
       s[4 * j + 3] = sa * q.w;
     }
+  } else if (n + 32 <= args.N && (reinterpret_cast<uintptr_t>(args.sb) & 15) == 0) { // 16-bit scales: 32 values in 64 bytes
+    const uint4 *p = reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(args.sb) + n);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const uint4 q = __ldg(p + j);
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        float lo, hi;
+        if (args.sb_dtype == QL_F16) {
+          const __half2 h = *reinterpret_cast<const __half2 *>(&w[i]);
+          lo = __low2float(h);
+          hi = __high2float(h);
+        } else {
+          lo = __uint_as_float(w[i] << 16);
+          hi = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+        s[8 * j + 2 * i] = sa * lo;
+        s[8 * j + 2 * i + 1] = sa * hi;
+      }
+    }
   } else {
 #pragma unroll
-    for (int j = 0; j < 32; j++) s[j] = sa * ((n + j < args.N) ? __ldg(args.sb + n + j) : 0.f);
+    for (int j = 0; j < 32; j++) s[j] = sa * ((n + j < args.N) ? load_scale(args.sb, args.sb_dtype, n + j) : 0.f);
   }
 }
 
@@ -311,7 +333,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int m = m0 + quad * 32 + lane;
       float sa = 1.f;
       if (args.sa) sa = (args.sa_n == 1) ? __ldg(args.sa) : (m < args.M ? __ldg(args.sa + m) : 0.f);
-      const float sb_scalar = (args.sb && args.sb_n == 1) ? __ldg(args.sb) : 1.f;
+      const float sb_scalar = (args.sb && args.sb_n == 1) ? load_scale(args.sb, args.sb_dtype, 0) : 1.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; c++) {
@@ -416,10 +438,58 @@ __device__ __forceinline__ uint32_t make_instr_desc_pair() {
   return d;
 }
 
+// W8A16 inside the pair kernel.  The B operand's tensor map points at a 16-bit scratch copy of the int8 weights
+// that eight extra warps per CTA produce while the GEMM runs: the weights are cut into chunks of 8 rows, CTA i
+// widens chunks i, i + grid, ... in order and bumps the counter of the chunk's tile; a TMA producer waits until the 32 chunks
+// of a 256-row tile are there before its first load of that tile.  Tiles are walked in rising column order, so
+// only the first wave waits noticeably (one chunk per CTA), and the rest of the conversion's HBM traffic hides
+// under the MMAs.  The launch is cooperative (all CTAs resident), so a waiting producer cannot starve the CTA
+// that owes it a chunk; waits are bounded all the same.  The last CTA to finish clears the counters.
+constexpr int kWidenThreads = 256;
+constexpr int kWidenChunkRows = 8;
+struct WidenArgs {
+  const uint8_t *raw; // int8 [N, K]
+  void *wide;         // XT [N, K] scratch
+  int *ready;         // one counter per 256-row tile of W, then the exit counter
+  int N, K;
+};
+
+template <typename XT, int I>
+__device__ __forceinline__ uint32_t widen_i8_pair(uint32_t w) {
+  if constexpr (FloatIO<XT>::kDtype == QL_F16) {
+    uint32_t v = __byte_perm(w ^ 0x80808080u, 0x64646464u, 0x4040 | I | ((I + 1) << 8));
+    __half2 h = __hsub2(*reinterpret_cast<__half2 *>(&v), __half2half2(__ushort_as_half(0x6480)));
+    return *reinterpret_cast<uint32_t *>(&h);
+  } else {
+    const uint32_t w16 = __byte_perm(w, 0u, 0x4140 + I * 0x0101);
+    uint32_t y = (w16 & 0x007F007Fu) | 0x43004300u; // 128 + low seven bits
+    uint32_t c = (w16 & 0x00800080u) | 0x43004300u; // 128, or 256 when the sign bit is set
+    __nv_bfloat162 d = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&y), *reinterpret_cast<__nv_bfloat162 *>(&c));
+    return *reinterpret_cast<uint32_t *>(&d);
+  }
+}
+
+__device__ __forceinline__ bool wait_counter(const int *ctr, int need, volatile int *abort_flag, int *status, int code) {
+  const long long t0 = clock64();
+  for (;;) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+    if (v >= need) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitLimitCycles) {
+      *abort_flag = 1;
+      atomicCAS(status, 0, code);
+      return false;
+    }
+    __nanosleep(200);
+  }
+}
+
 // args.tiles_m counts 256-row tiles here; args.tiles_n counts 256-column tiles.
-template <int KIND, typename OutT, bool PEER>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
-gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs args) {
+template <int KIND, typename OutT, bool PEER, bool WIDEN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(WIDEN ? kGemmThreads + kWidenThreads : kGemmThreads, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs args,
+                const WidenArgs wargs) {
   using L = Smem2<PEER>;
   constexpr int STAGES2 = L::kStages;
   constexpr uint32_t kTmemCols = 512; // two 256-column accumulators
@@ -474,6 +544,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         int mt, nt;
         tile_coords(args, tile, &mt, &nt);
         const int m0 = mt * 256 + (int)rank * BM, n0 = nt * BN2 + (int)rank * (BN2 / 2);
+        if constexpr (WIDEN) {
+          const int chunks = (wargs.N + kWidenChunkRows - 1) / kWidenChunkRows, per_tile = BN2 / kWidenChunkRows;
+          const int need = min(per_tile, chunks - nt * per_tile);
+          if (!wait_counter(wargs.ready + nt, need, abort_flag, args.status, ST_TIMEOUT_READY)) { ok = false; break; }
+          asm volatile("fence.proxy.async;" ::: "memory"); // the chunks were written with ordinary stores
+        }
         for (int kb = 0; kb < args.num_kb; kb++) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           const uint32_t a_dst = smem_base + stage * STAGE2_BYTES, b_dst = a_dst + A_STAGE_BYTES;
@@ -524,6 +600,26 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (clock64() - t0 > kWaitLimitCycles) { atomicCAS(args.status, 0, ST_TIMEOUT_DRAIN); break; }
       }
     }
+  } else if (WIDEN && warp >= 6) {
+    // ------------------------------------------------------------------ weight wideners (warps 6 and up, both CTAs)
+    const int ct = threadIdx.x - kGemmThreads;
+    const int chunks = (wargs.N + kWidenChunkRows - 1) / kWidenChunkRows;
+    for (int c = blockIdx.x; c < chunks; c += gridDim.x) {
+      const int r0 = c * kWidenChunkRows, rows = min(kWidenChunkRows, wargs.N - r0);
+      const uint4 *src = reinterpret_cast<const uint4 *>(wargs.raw + (size_t)r0 * wargs.K);
+      uint4 *dst = reinterpret_cast<uint4 *>(static_cast<OutT *>(wargs.wide) + (size_t)r0 * wargs.K);
+      const int n16 = rows * (wargs.K / 16);
+#pragma unroll 8
+      for (int i = ct; i < n16; i += kWidenThreads) {
+        const uint4 w = __ldcs(src + i);
+        dst[2 * i] = make_uint4(widen_i8_pair<OutT, 0>(w.x), widen_i8_pair<OutT, 2>(w.x), widen_i8_pair<OutT, 0>(w.y), widen_i8_pair<OutT, 2>(w.y));
+        dst[2 * i + 1] = make_uint4(widen_i8_pair<OutT, 0>(w.z), widen_i8_pair<OutT, 2>(w.z), widen_i8_pair<OutT, 0>(w.w), widen_i8_pair<OutT, 2>(w.w));
+      }
+      __threadfence();
+      asm volatile("fence.proxy.async;" ::: "memory");            // TMA (async proxy) will read what was just stored
+      asm volatile("bar.sync 1, %0;" ::"n"(kWidenThreads) : "memory"); // the whole chunk is out before it is announced
+      if (ct == 0) asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(wargs.ready + c / (BN2 / kWidenChunkRows)) : "memory");
+    }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
     const int quad = warp & 3;
@@ -542,7 +638,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const int m = m0 + quad * 32 + lane;
       float sa = 1.f;
       if (args.sa) sa = (args.sa_n == 1) ? __ldg(args.sa) : (m < args.M ? __ldg(args.sa + m) : 0.f);
-      const float sb_scalar = (args.sb && args.sb_n == 1) ? __ldg(args.sb) : 1.f;
+      const float sb_scalar = (args.sb && args.sb_n == 1) ? load_scale(args.sb, args.sb_dtype, 0) : 1.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN2);
 #pragma unroll 1
       for (int c = 0; c < BN2 / 32; c++) {
@@ -566,202 +662,27 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
-}
-
-// ----------------------------------------------------------------------------------------------
-// Wide two-CTA variant: the pair computes a 256 x 512 tile as two 256-column halves that share the
-// A tile.  The one-tile-per-pair kernel above is bound by L2 -> shared-memory bandwidth (about 10 TB/s
-// measured on B200: 64 KiB per 2*256*256*128 MACs); doubling the tile's width moves 96 KiB per twice
-// the work, a quarter less per flop.  Tensor memory then holds exactly one accumulator (512 columns),
-// so instead of two buffers the two halves are handed over separately: the epilogue frees half 0 while
-// it still drains half 1, and the next tile's MMAs into half 0 may start.
-// ----------------------------------------------------------------------------------------------
-constexpr int STAGESW = 4;
-constexpr int STAGEW_BYTES = A_STAGE_BYTES + 2 * B2_STAGE_BYTES; // A + both halves' share of B = 48 KiB
-
-struct SmemW {
-  static constexpr int kTiles = STAGESW * STAGEW_BYTES;
-  static constexpr int kBarriers = kTiles;                   // full[S], empty[S], tfull[2], tempty[2], drain
-  static constexpr int kTmemPtr = kBarriers + (2 * STAGESW + 5) * 8;
-  static constexpr int kAbort = kTmemPtr + 4;
-  static constexpr int kTotal = kAbort + 4;
-  static constexpr int kDynamic = kTotal + 1024;
-};
-
-// args.tiles_m counts 256-row tiles, args.tiles_n 512-column tiles.
-template <int KIND, typename OutT>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
-gemm_tc2w_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs args) {
-  using L = SmemW;
-  constexpr uint32_t kTmemCols = 512;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const uint32_t smem_base = smem_u32(smem);
-  const uint32_t bar_base = smem_base + L::kBarriers;
-  auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGESW + s); };
-  auto tfull_bar = [&](int h) { return bar_base + 8u * (2 * STAGESW + h); };
-  auto tempty_bar = [&](int h) { return bar_base + 8u * (2 * STAGESW + 2 + h); };
-  const uint32_t drain_bar = bar_base + 8u * (2 * STAGESW + 4);
-  volatile uint32_t *tmem_ptr_smem = reinterpret_cast<volatile uint32_t *>(smem + L::kTmemPtr);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_ctarank();
-  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
-  const int num_tiles = args.tiles_m * args.tiles_n;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGESW; s++) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
-    }
-    for (int h = 0; h < 2; h++) {
-      mbar_init(tfull_bar(h), 1);
-      mbar_init(tempty_bar(h), 8);
-    }
-    mbar_init(drain_bar, 1);
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_ptr_smem)), "r"(kTmemCols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  cluster_sync_all();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_ptr_smem;
-
-  // a tile whose second half lies entirely beyond N uses one half only
-  auto halves_of = [&](int nt) { return (nt * 512 + 256 < args.N) ? 2 : 1; };
-
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer (both CTAs)
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        int mt, nt;
-        tile_coords(args, tile, &mt, &nt);
-        const int halves = halves_of(nt);
-        const int m0 = mt * 256 + (int)rank * BM, n0 = nt * 512 + (int)rank * (BN2 / 2);
-        for (int kb = 0; kb < args.num_kb; kb++) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
-          const uint32_t a_dst = smem_base + stage * STAGEW_BYTES, b_dst = a_dst + A_STAGE_BYTES;
-          const uint32_t leader_full = map_to_cta(full_bar(stage), 0);
-          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * (A_STAGE_BYTES + halves * B2_STAGE_BYTES));
-          const int x = kb * args.k_elems_per_block;
-          tma_load_2d_pair(a_dst, &map_a, leader_full, x, m0);
-          tma_load_2d_pair(b_dst, &map_b, leader_full, x, n0);
-          if (halves == 2) tma_load_2d_pair(b_dst + B2_STAGE_BYTES, &map_b, leader_full, x, n0 + 256);
-          if (++stage == STAGESW) { stage = 0; phase ^= 1; }
-        }
+  if constexpr (WIDEN) {
+    // the last CTA out leaves the counters at zero for the next launch
+    if (threadIdx.x == 0) {
+      const int tiles_w = (wargs.N + BN2 - 1) / BN2;
+      __threadfence();
+      if (atomicAdd(wargs.ready + tiles_w, 1) == (int)gridDim.x - 1) {
+        for (int i = 0; i <= tiles_w; i++) wargs.ready[i] = 0;
+        __threadfence();
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer (leader only)
-    if (lane == 0 && rank == 0) {
-      const uint32_t idesc = make_instr_desc_pair<KIND>();
-      int stage = 0;
-      uint32_t phase = 0;
-      int use[2] = {0, 0}; // how often each accumulator half has been used so far
-      bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        int mt, nt;
-        tile_coords(args, tile, &mt, &nt);
-        const int halves = halves_of(nt);
-        for (int kb = 0; kb < args.num_kb && ok; kb++) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, ST_TIMEOUT_FULL)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t a_addr = smem_base + stage * STAGEW_BYTES;
-          const uint64_t adesc = make_smem_desc(a_addr);
-          for (int h = 0; h < halves; h++) {
-            if (kb == 0) { // the epilogue must have drained this half of the previous tile
-              if (!mbar_wait(tempty_bar(h), (use[h] & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
-              tc_fence_after();
-            }
-            const uint64_t bdesc = make_smem_desc(a_addr + A_STAGE_BYTES + h * B2_STAGE_BYTES);
-#pragma unroll
-            for (int k = 0; k < BK_BYTES / 32; k++)
-              tc_mma_pair<KIND>(tmem_base + (uint32_t)(h * BN2), adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-          }
-          if (!ok) break;
-          tc_commit_pair(map_to_cta(empty_bar(stage), 0));
-          tc_commit_pair(map_to_cta(empty_bar(stage), 1));
-          if (++stage == STAGESW) { stage = 0; phase ^= 1; }
-        }
-        if (ok) {
-          for (int h = 0; h < halves; h++) {
-            tc_commit_pair(map_to_cta(tfull_bar(h), 0));
-            tc_commit_pair(map_to_cta(tfull_bar(h), 1));
-            use[h]++;
-          }
-        }
-      }
-      tc_commit_pair(map_to_cta(drain_bar, 0));
-      const long long t0 = clock64();
-      while (!mbar_try_wait(drain_bar, 0)) {
-        if (clock64() - t0 > kWaitLimitCycles) { atomicCAS(args.status, 0, ST_TIMEOUT_DRAIN); break; }
-      }
-    }
-  } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
-    const int quad = warp & 3;
-    OutT *Y = static_cast<OutT *>(args.Y);
-    const bool vec_ok = (args.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
-    int use[2] = {0, 0};
-    bool ok = true;
-    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-      int mt, nt;
-      tile_coords(args, tile, &mt, &nt);
-      const int halves = halves_of(nt);
-      const int m = mt * 256 + (int)rank * BM + quad * 32 + lane;
-      float sa = 1.f;
-      if (args.sa) sa = (args.sa_n == 1) ? __ldg(args.sa) : (m < args.M ? __ldg(args.sa + m) : 0.f);
-      const float sb_scalar = (args.sb && args.sb_n == 1) ? __ldg(args.sb) : 1.f;
-      for (int h = 0; h < halves && ok; h++) {
-        if (!mbar_wait(tfull_bar(h), use[h] & 1, abort_flag, args.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(h * BN2);
-#pragma unroll 1
-        for (int c = 0; c < BN2 / 32; c++) {
-          uint32_t r[32];
-          float sc[32];
-          const int n = nt * 512 + h * BN2 + c * 32;
-          load_chunk_scales(args, n, sa, sb_scalar, sc);
-          tmem_load_32(taddr + c * 32, r);
-          emit_chunk<KIND, OutT>(args, Y, vec_ok, r, m, n, sc, nullptr, lane, c, c == BN2 / 32 - 1);
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(h), 0));
-        use[h]++;
-      }
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  cluster_sync_all();
-  if (warp == 1) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
-// The CTA-pair kernels: 0 = 256 x 256 tiles, 1 = 256 x 512 tiles, 2 = 256 x 256 tiles with the peer-mode epilogue.
-enum { PAIR_PLAIN = 0, PAIR_WIDE = 1, PAIR_PEER = 2 };
+// The CTA-pair kernel's variants: plain, with the peer-mode epilogue, with the int8 weights widened inside.
+enum { PAIR_PLAIN = 0, PAIR_PEER = 2, PAIR_WIDEN = 3 };
 template <int KIND, typename OutT, int V>
 auto pair_kernel() {
-  if constexpr (V == PAIR_WIDE) return gemm_tc2w_kernel<KIND, OutT>;
-  else return gemm_tc2_kernel<KIND, OutT, V == PAIR_PEER>;
+  return gemm_tc2_kernel<KIND, OutT, V == PAIR_PEER, V == PAIR_WIDEN>;
 }
-template <int V> constexpr int pair_smem() {
-  return V == PAIR_WIDE ? SmemW::kDynamic : V == PAIR_PEER ? Smem2<true>::kDynamic : Smem2<false>::kDynamic;
-}
+template <int V> constexpr int pair_smem() { return V == PAIR_PEER ? Smem2<true>::kDynamic : Smem2<false>::kDynamic; }
+template <int V> constexpr int pair_threads() { return V == PAIR_WIDEN ? kGemmThreads + kWidenThreads : kGemmThreads; }
 
 // Largest number of CTA pairs that can be resident at once on this device (0 = pairs unavailable).
 template <int KIND, typename OutT, int V>
@@ -777,7 +698,7 @@ int max_resident_pairs() {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) == cudaSuccess) {
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(2 * sm_count(), 1, 1);
-      cfg.blockDim = dim3(kGemmThreads, 1, 1);
+      cfg.blockDim = dim3(pair_threads<V>(), 1, 1);
       cfg.dynamicSmemBytes = smem_bytes;
       cudaLaunchAttribute attr;
       attr.id = cudaLaunchAttributeClusterDimension;
@@ -796,12 +717,12 @@ int max_resident_pairs() {
 }
 
 template <int KIND, typename OutT, int V>
-int launch_gemm_pair(const void *A, const void *B, GemmArgs args, int64_t K, int pairs, cudaStream_t st) {
+int launch_gemm_pair(const void *A, const void *B, GemmArgs args, int64_t K, int pairs, cudaStream_t st, WidenArgs wargs = WidenArgs{}) {
   CUtensorMap ma, mb;
   int rc;
   if ((rc = make_map(&ma, KIND, A, args.M, K, BM)) != QL_OK) return rc;
   if ((rc = make_map(&mb, KIND, B, args.N, K, BN2 / 2)) != QL_OK) return rc;
-  constexpr int kTileN = V == PAIR_WIDE ? 512 : BN2;
+  constexpr int kTileN = BN2;
   args.tiles_m = (args.M + 255) / 256;
   args.tiles_n = (args.N + kTileN - 1) / kTileN;
   args.group_m = (args.group_m + 1) / 2; // bands were sized in 128-row tiles
@@ -809,7 +730,27 @@ int launch_gemm_pair(const void *A, const void *B, GemmArgs args, int64_t K, int
   if (args.group_m > args.tiles_m) args.group_m = args.tiles_m;
   const int tiles = args.tiles_m * args.tiles_n;
   const int clusters = tiles < pairs ? tiles : pairs;
-  pair_kernel<KIND, OutT, V>()<<<2 * clusters, kGemmThreads, pair_smem<V>(), st>>>(ma, mb, args);
+  if constexpr (V == PAIR_WIDEN) {
+    // column-major walk over the whole M: the weight tiles are needed in the order they are widened
+    args.group_m = args.tiles_m;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * clusters, 1, 1);
+    cfg.blockDim = dim3(pair_threads<V>(), 1, 1);
+    cfg.dynamicSmemBytes = pair_smem<V>();
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeCooperative; // every CTA resident: producers wait on chunks other CTAs widen
+    attr.val.cooperative = getenv("QL_W8_NOT_COOPERATIVE") ? 0 : 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, pair_kernel<KIND, OutT, V>(), ma, mb, args, wargs);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return QL_ERR_UNSUPPORTED; // the caller falls back to the two-kernel route
+    }
+  } else {
+    pair_kernel<KIND, OutT, V>()<<<2 * clusters, pair_threads<V>(), pair_smem<V>(), st>>>(ma, mb, args, wargs);
+  }
   count_launches(1);
   QL_CUDA_TRY(cudaGetLastError());
   return QL_OK;
@@ -839,14 +780,8 @@ template <int KIND, typename OutT>
 int launch_gemm_kind(const void *A, const void *B, GemmArgs args, int64_t K, cudaStream_t st) {
   const int sms = sm_count();
   if (args.M > 256 && args.N >= 512 && !getenv("QL_GEMM_ONE_CTA")) {
-    // Wide (256 x 512) tiles are opt-in: they cut L2 traffic per flop by a quarter, but with a single
-    // accumulator the hand-over between tiles is exposed, and on B200 that cost more than the traffic
-    // saved (1.51 ms against 1.44 ms for 8192 x 28672 x 8192 fp8).
-    if (getenv("QL_GEMM_WIDE_PAIR") && args.peer_mode == QL_PEER_NONE) {
-      const long long tiles_w = (long long)((args.M + 255) / 256) * ((args.N + 511) / 512);
-      const int pairs_w = max_resident_pairs<KIND, OutT, PAIR_WIDE>();
-      if (pairs_w > 0 && tiles_w >= 4ll * pairs_w) return launch_gemm_pair<KIND, OutT, PAIR_WIDE>(A, B, args, K, pairs_w, st);
-    }
+    // (256 x 512 tiles per pair were built and measured: a quarter less L2 traffic per flop, but with a single
+    // accumulator the hand-over between tiles is exposed; 1.51 ms against 1.44 ms for 8192 x 28672 x 8192 fp8.)
     const long long tiles2 = (long long)((args.M + 255) / 256) * ((args.N + BN2 - 1) / BN2);
     if constexpr (KIND == KIND_F8) {
       if (args.peer_mode != QL_PEER_NONE) {
@@ -916,7 +851,8 @@ int run_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_te
   GemmArgs args;
   args.Y = y->data;
   args.sa = sa ? static_cast<const float *>(sa->data) : nullptr;
-  args.sb = sb ? static_cast<const float *>(sb->data) : nullptr;
+  args.sb = sb ? sb->data : nullptr;
+  args.sb_dtype = sb ? sb->dtype : QL_F32;
   args.sa_n = sa ? (int)numel(sa) : 1;
   args.sb_n = sb ? (int)numel(sb) : 1;
   args.M = (int)M;
@@ -926,8 +862,13 @@ int run_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_te
   args.tiles_m = (int)((M + BM - 1) / BM);
   args.tiles_n = 0;
   {
-    // a band of A of about 16 MiB stays L2-resident while B streams through
-    const int64_t band = (16ll << 20) / ((int64_t)BM * K * esize);
+    // A band of row tiles of A stays L2-resident while B streams through once per band.  Measured on B200: about
+    // 16 MiB of A, but never fewer than 16 row tiles (2048 rows) while those stay under 64 MiB: with long rows
+    // (K = 28672) 4 tiles per band re-streamed B eight times and cost 7 % against 16 tiles per band.
+    const int64_t tile_bytes = (int64_t)BM * K * esize;
+    int64_t band = (16ll << 20) / tile_bytes;
+    const int64_t wide = (64ll << 20) / tile_bytes;
+    if (band < 16) band = wide < 16 ? wide : 16;
     args.group_m = (int)(band < 4 ? 4 : band);
     if (const char *e = getenv("QL_GEMM_GROUP_M")) args.group_m = atoi(e) > 0 ? atoi(e) : args.group_m; // tuning aid
     if (args.group_m > args.tiles_m) args.group_m = args.tiles_m;
@@ -956,6 +897,55 @@ int gemm16_device(int dtype, const void *X, const void *W, const float *sb, int 
   ql_tensor s{const_cast<float *>(sb), QL_F32, 1, {sb_n}};
   if (dtype == QL_BF16) return run_gemm<KIND_BF16>("gemm_16", &x, &w, nullptr, sb ? &s : nullptr, &y, st);
   return run_gemm<KIND_F16>("gemm_16", &x, &w, nullptr, sb ? &s : nullptr, &y, st);
+}
+
+// Y[M,N] = (X[M,K] . widen(Wq[N,K])^T) * scale[n] in one launch: the pair kernel with the int8 -> 16-bit conversion
+// running ahead of the tiles (see WidenArgs).  `wide` = [N,K] scratch of X's type, `counters` = ceil(N/256) + 1
+// zeroed ints.  Returns QL_ERR_UNSUPPORTED (without touching the error text) when the shape or the device does not
+// suit it; the caller then widens in a kernel of its own.
+template <int KIND, typename XT>
+int gemm16_widen_t(const void *X, const void *Wraw, void *wide, int *counters, const void *scale, int sdt, void *Y, int M, int N, int K,
+                   cudaStream_t st) {
+  const int pairs = max_resident_pairs<KIND, XT, PAIR_WIDEN>();
+  const long long tiles2 = (long long)((M + 255) / 256) * ((N + BN2 - 1) / BN2);
+  // Worth it from about four waves of tiles on: the wideners are slower than a kernel of their own (they share the
+  // SMs with the GEMM), and with few waves the first one waits for most of the weights.
+  if (pairs <= 0 || tiles2 < 4ll * pairs) return QL_ERR_UNSUPPORTED;
+  GemmArgs args;
+  args.Y = Y;
+  args.sa = nullptr;
+  args.sb = scale;
+  args.sb_dtype = sdt;
+  args.sa_n = 1;
+  args.sb_n = N;
+  args.M = M;
+  args.N = N;
+  args.k_elems_per_block = BK_BYTES / 2;
+  args.num_kb = (int)(((int64_t)K * 2 + BK_BYTES - 1) / BK_BYTES);
+  args.tiles_m = (M + BM - 1) / BM;
+  args.tiles_n = 0;
+  args.group_m = args.tiles_m;
+  args.ldy = N;
+  args.peer_mode = QL_PEER_NONE;
+  args.rows_per_rank = 1;
+  for (int r = 0; r < QL_MAX_PEERS; r++) args.owner_y[r] = nullptr;
+  args.status = device_status_word();
+  if (!args.status) return set_error(QL_ERR_CUDA, "linear_w8a16: could not allocate the device status word");
+  WidenArgs w;
+  w.raw = static_cast<const uint8_t *>(Wraw);
+  w.wide = wide;
+  w.ready = counters;
+  w.N = N;
+  w.K = K;
+  return launch_gemm_pair<KIND, XT, PAIR_WIDEN>(X, wide, args, K, pairs, st, w);
+}
+
+int gemm16_widen_device(int dtype, const void *X, const void *Wraw, void *wide, int *counters, const void *scale, int sdt, void *Y,
+                        int M, int N, int K, cudaStream_t st) {
+  if (M <= 256 || N < 512 || K % 16 != 0 || !aligned16(Wraw) || !aligned16(wide) || !aligned16(X) || getenv("QL_W8_TWO_KERNELS"))
+    return QL_ERR_UNSUPPORTED;
+  if (dtype == QL_BF16) return gemm16_widen_t<KIND_BF16, __nv_bfloat16>(X, Wraw, wide, counters, scale, sdt, Y, M, N, K, st);
+  return gemm16_widen_t<KIND_F16, __half>(X, Wraw, wide, counters, scale, sdt, Y, M, N, K, st);
 }
 
 } // namespace ql

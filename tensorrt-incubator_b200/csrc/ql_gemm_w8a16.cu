@@ -382,7 +382,8 @@ __global__ void __launch_bounds__(256) scale_to_f32_kernel(const void *__restric
 
 // Grow-only scratch buffer per device for the widened weights (allocated with cudaMalloc on first
 // use or growth, so the first call of a given size must not happen inside a stream capture; calls
-// on different streams that may overlap would share it and must be ordered by the caller).
+// on different streams that may overlap would share it, and the tile counters below, and must be
+// ordered by the caller).
 int widen_workspace(size_t bytes, uint8_t **out) {
   static uint8_t *buf[64] = {nullptr};
   static size_t cap[64] = {0};
@@ -400,14 +401,34 @@ int widen_workspace(size_t bytes, uint8_t **out) {
   return QL_OK;
 }
 
+// Tile counters of the single-launch route: allocated and zeroed once per device; the kernel leaves them at zero.
+constexpr int kWidenCounters = 1024;
+int widen_counters(int **out) {
+  static int *ctr[64] = {nullptr};
+  int dev = 0;
+  QL_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return set_error(QL_ERR_UNSUPPORTED, "linear_w8a16: device index %d out of range", dev);
+  if (!ctr[dev]) {
+    int *p = nullptr;
+    QL_CUDA_TRY(cudaMalloc(&p, kWidenCounters * sizeof(int)));
+    QL_CUDA_TRY(cudaMemset(p, 0, kWidenCounters * sizeof(int)));
+    ctr[dev] = p;
+  }
+  *out = ctr[dev];
+  return QL_OK;
+}
+
 } // namespace
 
 int gemm16_device(int dtype, const void *X, const void *W, const float *sb, int sb_n, void *Y, int M, int N, int K,
                   cudaStream_t st);
+int gemm16_widen_device(int dtype, const void *X, const void *Wraw, void *wide, int *counters, const void *scale, int sdt, void *Y,
+                        int M, int N, int K, cudaStream_t st);
 
-// Compute-bound batches: widen the weights once per call into scratch (exact) and run the plain 16-bit
-// tcgen05 GEMM with the per-channel scales in its epilogue.  The in-kernel conversion above is bound by
-// its converter warps once the MMA work per weight grows, so it serves the memory-bound range only.
+// Compute-bound batches: the weights are widened once per call into scratch (exact) and the 16-bit tcgen05 GEMM
+// runs on the scratch with the per-channel scales in its epilogue.  (The per-tile conversion of the kernel above
+// repeats the widening for every row tile and is bound by its converter warps once M grows.)  Where the CTA-pair
+// kernel applies, the widening runs inside it, ahead of the tiles that need it; otherwise in a kernel of its own.
 int launch_w8a16_widen(int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M, int N, int K,
                        cudaStream_t st) {
   const int64_t n = (int64_t)N * K;
@@ -416,6 +437,12 @@ int launch_w8a16_widen(int xdt, const void *X, const void *W, const void *scale,
   int rc = widen_workspace(scale_off + (size_t)N * sizeof(float), &scratch);
   if (rc != QL_OK) return rc;
   float *sf = reinterpret_cast<float *>(scratch + scale_off);
+  if ((N + 255) / 256 + 1 <= kWidenCounters) {
+    int *counters = nullptr;
+    if ((rc = widen_counters(&counters)) != QL_OK) return rc;
+    rc = gemm16_widen_device(xdt, X, W, scratch, counters, scale, sdt, Y, M, N, K, st);
+    if (rc != QL_ERR_UNSUPPORTED) return rc;
+  }
   const int64_t n16 = n / 16; // K % 64 == 0
   if (xdt == QL_F16) widen_i8_kernel<__half><<<(unsigned)((n16 + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t *>(W), reinterpret_cast<__half *>(scratch), n16);
   else widen_i8_kernel<__nv_bfloat16><<<(unsigned)((n16 + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t *>(W), reinterpret_cast<__nv_bfloat16 *>(scratch), n16);

@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 def _status_ok():
     code = ctypes.c_int32(0)
     rc = ql.lib().ql_gemm_status(ctypes.byref(code))
-    assert rc == 0 and code.value == 0, f"a GEMM kernel gave up waiting: code {code.value}"
+    assert rc == 0 and code.value == 0, f"status {rc}, code {code.value}: {ql.lib().ql_last_error().decode()}"
 
 
 def _fp8(shape, seed, std=1.0):

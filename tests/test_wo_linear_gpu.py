@@ -90,6 +90,34 @@ def test_config2_shapes(M):
     assert torch.equal(y2, y * 2)
 
 
+@pytest.mark.parametrize("xdtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K", [(2048, 11008, 4096), (2200, 9000, 320), (1025, 19000, 64)])
+def test_w8a16_compute_bound_single_launch_path(xdtype, M, N, K, monkeypatch):
+    """M > 256 with enough tiles: the CTA-pair GEMM that widens the weights ahead of its own tiles, against the
+    oracle on slices of rows and channels (first, ragged last chunk, middle) and, bit for bit, against the route that
+    widens in a kernel of its own."""
+    import ctypes
+    x, q, s = _w8_case(M, N, K, xdtype, 1200 + M)
+    c0 = ql.lib().ql_launch_count()
+    y = ql.linear_w8a16(x, q, s)
+    assert ql.lib().ql_launch_count() - c0 == 1
+    for _ in range(2):   # the kernel must leave its tile counters ready for the next launch
+        y_again = ql.linear_w8a16(x, q, s)
+    assert torch.equal(y, y_again)
+    code = ctypes.c_int32(0)
+    assert ql.lib().ql_gemm_status(ctypes.byref(code)) == 0 and code.value == 0
+    ulp = 2.0 ** -8 if xdtype == torch.bfloat16 else 2.0 ** -10
+    rows = slice(M - 40, M)
+    for sl in (slice(0, 48), slice(N - 40, N), slice(N // 2 - 7, N // 2 + 25)):
+        want = orc.linear_w8(to_np(x[rows]), code_of(x), to_np(q[sl]), to_np(s[sl]), code_of(s), orc.F32, acc64=True)
+        assert_close_rel(float_values(y[rows, sl]), want, ulp, f"single-launch w8a16 {M}x{N}x{K} channels {sl}")
+    monkeypatch.setenv("QL_W8_TWO_KERNELS", "1")
+    c0 = ql.lib().ql_launch_count()
+    y_two = ql.linear_w8a16(x, q, s)
+    assert ql.lib().ql_launch_count() - c0 == 3
+    assert torch.equal(y, y_two)
+
+
 @pytest.mark.parametrize("M", [1, 8, 32])
 def test_config3_shapes(M):
     w = randn((4096, 4096), torch.float16, 1003, std=0.02)
