@@ -224,10 +224,18 @@ int launch_wo_t(const void *X, const void *W, const void *scale, int sdt, void *
     // (k-steps in flight per warp, minimum resident blocks) per batch width, from timing on B200: many
     // resident blocks with one step in flight each beat fewer blocks with deeper unrolling
 #define QL_WO_LAUNCH(NT_, U_, MB_) wo_linear_kernel<XT, WBITS, NT_, U_, MB_><<<grid, kThreadsWo, 0, st>>>(xp, wp, scale, sdt, yp, mc, N, K, block)
+    // (int4 keeps four X words per row and step alive instead of two: the int8 settings would spill.)  When the
+    // grid cannot fill the SMs several times over, occupancy is not what limits the bytes in flight, so each warp
+    // issues all of its few steps at once instead.
+    const bool few_blocks = grid < 3u * (unsigned)sm_count();
     if (mc <= 8) {
-      QL_WO_LAUNCH(1, 1, 6);
+      if (few_blocks) QL_WO_LAUNCH(1, 4, 2);
+      else if constexpr (WBITS == 8) QL_WO_LAUNCH(1, 1, 6);
+      else QL_WO_LAUNCH(1, 1, 4);
     } else if (mc <= 16) {
-      QL_WO_LAUNCH(2, 2, 3);
+      if (few_blocks) QL_WO_LAUNCH(2, 2, 2);
+      else if constexpr (WBITS == 8) QL_WO_LAUNCH(2, 2, 3);
+      else QL_WO_LAUNCH(2, 1, 3);
     } else {
       QL_WO_LAUNCH(4, 1, 2);
     }
