@@ -447,7 +447,7 @@ class Fp8Mlp(Workload):
         self.torch, self.ql, self.device, self.dist = torch, ql, device, dist
         self.world = dist.get_world_size() if dist is not None else 1
         self.rank = dist.get_rank() if dist is not None else 0
-        fused = "auto" if not os.environ.get("QL_BENCH_NCCL") else False
+        fused = os.environ.get("QL_BENCH_MLP_PROTOCOL", "auto") if not os.environ.get("QL_BENCH_NCCL") else False
         il = self.I // self.world
         self.il = il
         g = torch.Generator(device=device).manual_seed(seed * 100 + self.rank)   # this rank's shard of the random weights
@@ -464,6 +464,8 @@ class Fp8Mlp(Workload):
                             {"add_all": "partial sums added into both GPUs' outputs by the down-projection epilogue (multimem.red), one barrier",
                              "add_owner": "partial sums added into the owner's rows by the down-projection epilogue (red over peer memory), "
                                           "barrier, owners broadcast their rows (multimem.st), barrier",
+                             "switch_reduce": "down projection into the local copy, barrier, in-switch sum of each GPU's own rows written to all "
+                                              "GPUs (multimem.ld_reduce + multimem.st), barrier",
                              "nccl": "NCCL all-reduce"}[proto])
         self.y_host = torch.empty((self.T, self.H), dtype=torch.bfloat16).pin_memory()
 
@@ -473,16 +475,22 @@ class Fp8Mlp(Workload):
               ("gate_up_gemm", lambda: self.mlp.stage_gate_up(self.buf), 2 * T * H * 2 * il, T * H + 2 * il * H + 2 * T * 2 * il, "tensor_fp8"),
               ("swiglu_quant", lambda: self.mlp.stage_swiglu_quant(self.buf), 0, 2 * T * 2 * il + T * il, "hbm")]
         down = (2 * T * il * H, T * il + H * il + 2 * T * H, "tensor_fp8")
-        if self.buf["protocol"] != "nccl":
+        proto = self.buf["protocol"]
+        if proto != "nccl":
             def finish():
                 self.mlp.stage_barrier(self.buf)
                 self.mlp._step += 1
-            scatter = self.mlp._scatter(self.buf)
-            ps += [("down_gemm_add_owner" if scatter else "down_gemm_add_all", lambda: self.mlp.stage_down_add(self.buf)) + down,
-                   ("clear_next_output", lambda: self.mlp.stage_clear_next(self.buf), 0, 2 * T * H // (self.world if scatter else 1), "hbm")]
-            if scatter:
-                ps += [("barrier_sums", lambda: self.mlp.stage_barrier(self.buf), 0, 0, "nvlink"),
-                       ("broadcast_owned_rows", lambda: self.mlp.stage_broadcast_owned(self.buf), 0, 2 * T * H * (self.world - 1) // self.world, "nvlink")]
+            if proto == "switch_reduce":
+                ps += [("down_gemm", lambda: self.mlp.stage_down_local(self.buf)) + down,
+                       ("barrier_partials", lambda: self.mlp.stage_barrier(self.buf), 0, 0, "nvlink"),
+                       ("switch_reduce_owned_rows", lambda: self.mlp.stage_switch_reduce_owned(self.buf), 0, 2 * T * H, "nvlink")]
+            else:
+                scatter = proto == "add_owner"
+                ps += [("down_gemm_add_owner" if scatter else "down_gemm_add_all", lambda: self.mlp.stage_down_add(self.buf)) + down,
+                       ("clear_next_output", lambda: self.mlp.stage_clear_next(self.buf), 0, 2 * T * H // (self.world if scatter else 1), "hbm")]
+                if scatter:
+                    ps += [("barrier_sums", lambda: self.mlp.stage_barrier(self.buf), 0, 0, "nvlink"),
+                           ("broadcast_owned_rows", lambda: self.mlp.stage_broadcast_owned(self.buf), 0, 2 * T * H * (self.world - 1) // self.world, "nvlink")]
             ps.append(("barrier", finish, 0, 0, "nvlink"))
         else:
             ps.append(("down_gemm", lambda: self.mlp.stage_down(self.buf)) + down)

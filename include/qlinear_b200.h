@@ -168,6 +168,11 @@ QL_API int ql_gemm_fp8_peer(const ql_tensor *xq, const ql_tensor *wq, const ql_t
                             const ql_peer_buffer *dest, int32_t y_dtype, int64_t ldy, int64_t offset, int peer_mode,
                             void *stream);
 QL_API int ql_peer_barrier(const ql_peer_buffer *flags, void *stream);
+/* In-switch all-reduce of bytes [offset, offset + bytes) (bf16 or f16 elements, 16-byte units): the NVSwitch adds
+ * that range of all replicas in f32 and the sum replaces it in every replica.  Ranks call it on disjoint ranges
+ * between two ql_peer_barrier calls; with a GEMM that wrote its partial result into the local replica this is a
+ * row-parallel all-reduce in which every sum is rounded once. */
+QL_API int ql_peer_reduce(const ql_peer_buffer *buf, int32_t dtype, int64_t offset, int64_t bytes, void *stream);
 /* copies bytes [offset, offset + bytes) of this rank's replica to the same range of every replica (16-byte units) */
 QL_API int ql_peer_broadcast(const ql_peer_buffer *buf, int64_t offset, int64_t bytes, void *stream);
 /* 16-bit GEMM Y = (X . W^T) * sw, X and W both bf16 or both f16 ([M,K], [N,K]); sw may be null. */

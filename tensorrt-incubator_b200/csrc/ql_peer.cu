@@ -55,6 +55,26 @@ __global__ void peer_broadcast_kernel(const uint4 *__restrict__ src, uint4 *dst_
   }
 }
 
+// In-switch all-reduce of one rank's share of a buffer: `multimem.ld_reduce` makes the NVSwitch fetch the same 16
+// bytes from every replica and add them (f32 accumulation, one rounding), `multimem.st` writes the sum back into
+// every replica.  Every rank runs this on a disjoint range, between two barriers.
+template <bool kHalf>
+__global__ void peer_reduce_kernel(uint4 *all, int64_t n16) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
+    uint32_t a, b, c, d;
+    if (kHalf)
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "l"(all + i) : "memory");
+    else
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "l"(all + i) : "memory");
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(all + i), "f"(__uint_as_float(a)),
+                 "f"(__uint_as_float(b)), "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
+                 : "memory");
+  }
+}
+
 int check_peer(const char *op, const ql_peer_buffer *b) {
   if (!b) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: null buffer", op);
   if (b->world < 1 || b->world > QL_MAX_PEERS || b->rank < 0 || b->rank >= b->world)
@@ -79,6 +99,26 @@ int ql_peer_barrier(const ql_peer_buffer *flags, void *stream) {
   FlagPtrs p;
   for (int r = 0; r < QL_MAX_PEERS; r++) p.flags[r] = r < flags->world ? static_cast<uint32_t *>(flags->replica[r]) : nullptr;
   peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(p, flags->world, flags->rank, status);
+  count_launches(1);
+  QL_CUDA_TRY(cudaGetLastError());
+  return QL_OK;
+}
+
+int ql_peer_reduce(const ql_peer_buffer *buf, int32_t dtype, int64_t offset, int64_t bytes, void *stream) {
+  int rc = check_peer("peer_reduce", buf);
+  if (rc != QL_OK) return rc;
+  if (!buf->all) return set_error(QL_ERR_INVALID_ARGUMENT, "peer_reduce: the buffer has no replication address");
+  if (dtype != QL_BF16 && dtype != QL_F16) return set_error(QL_ERR_INVALID_ARGUMENT, "peer_reduce: elements must be bf16 or f16");
+  if (offset < 0 || bytes < 0 || offset % 16 != 0 || bytes % 16 != 0)
+    return set_error(QL_ERR_INVALID_ARGUMENT, "peer_reduce: offset and size must be multiples of 16 bytes");
+  if (bytes == 0) return QL_OK;
+  const int64_t n16 = bytes / 16;
+  uint4 *all = reinterpret_cast<uint4 *>(static_cast<char *>(buf->all) + offset);
+  int64_t blocks = (n16 + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  if (dtype == QL_F16) peer_reduce_kernel<true><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(all, n16);
+  else peer_reduce_kernel<false><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(all, n16);
   count_launches(1);
   QL_CUDA_TRY(cudaGetLastError());
   return QL_OK;

@@ -70,6 +70,7 @@ SIGNATURES = {
     "ql_gemm_fp8": ([_T, _T, _T, _T, _T, _S], ctypes.c_int),
     "ql_gemm_fp8_peer": ([_T, _T, _T, _T, _P, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, _S], ctypes.c_int),
     "ql_peer_barrier": ([_P, _S], ctypes.c_int),
+    "ql_peer_reduce": ([_P, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, _S], ctypes.c_int),
     "ql_peer_broadcast": ([_P, ctypes.c_int64, ctypes.c_int64, _S], ctypes.c_int),
     "ql_gemm_i8": ([_T, _T, _T, _T, _T, _S], ctypes.c_int),
     "ql_gemm_16": ([_T, _T, _T, _T, _S], ctypes.c_int),

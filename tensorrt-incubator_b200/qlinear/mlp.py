@@ -66,12 +66,12 @@ class QuantizedMLP:
     def __init__(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, eps: float = 1e-5, group=None,
                  fused_all_reduce="auto"):
         """`fused_all_reduce`: True = the down projection's epilogue does the reduction over peer memory
-        (qlinear.peer): with two ranks it adds its partial result into both outputs; with more it adds each row
-        into the output of the rank that owns the row, and the owners then broadcast their rows.  False = NCCL
-        all-reduce after the GEMM; "auto" = fused when the box supports it and the group has several ranks;
-        "scatter" = fused, with the owner protocol whatever the group size."""
+        (qlinear.peer): with two ranks the epilogue adds its partial result into both outputs; with more it adds
+        each row into the output of the rank that owns the row, and the owners broadcast.  False = NCCL all-reduce after the GEMM;
+        "auto" = over peer memory when the box supports it and the group has several ranks; "scatter" / "switch"
+        = a given protocol whatever the group size (see _buffers)."""
         self.eps, self.group = eps, group
-        self._force_scatter = fused_all_reduce == "scatter"   # the more-than-two-ranks protocol on any group size
+        self._force = fused_all_reduce if fused_all_reduce in ("scatter", "switch") else None   # a protocol on any group size
         if fused_all_reduce == "auto":
             fused_all_reduce = group is not None and peer.available(group)
         self.fused_all_reduce = bool(fused_all_reduce) and group is not None
@@ -96,12 +96,24 @@ class QuantizedMLP:
                 import torch.distributed as dist
                 world = dist.get_world_size(self.group)
             # Adding into every output is only used with two ranks: with more, the partial sums would reach each
-            # output in a different order and the ranks' results would differ in the last bit.  With owners the
-            # sum of a row is formed once and copied.
-            if world == 2 and not self._force_scatter:
-                self._buf["protocol"] = "add_all"
-            elif world >= 2 and T % (128 * world) == 0:
+            # output in a different order and the ranks' results would differ in the last bit (and every GPU would
+            # receive world x the data).  Beyond two ranks rows have owners: the epilogue adds each row into its
+            # owner's output (the reduce-scatter hides under the GEMM) and the owners broadcast their rows.
+            # "switch_reduce" (GEMM into the local replica, then the NVSwitch sums each rank's own rows in f32 and
+            # writes them to everyone) rounds every sum once; on two GPUs it was the slowest of the three
+            # (1.37 ms per step against 1.23 add_all and 1.31 add_owner), so it serves where rows do not split
+            # into owner blocks of 128, or on request.
+            owner_ok, switch_ok = world >= 2 and T % (128 * world) == 0, world >= 2 and T % world == 0
+            if self._force == "scatter" and owner_ok:
                 self._buf["protocol"] = "add_owner"
+            elif self._force == "switch" and switch_ok:
+                self._buf["protocol"] = "switch_reduce"
+            elif world == 2:
+                self._buf["protocol"] = "add_all"
+            elif owner_ok:
+                self._buf["protocol"] = "add_owner"
+            elif switch_ok:
+                self._buf["protocol"] = "switch_reduce"
             else:
                 self._buf["protocol"] = "nccl"
             if self._buf["protocol"] != "nccl":
@@ -111,7 +123,7 @@ class QuantizedMLP:
         return self._buf
 
     def protocol(self, T, device) -> str:
-        """How the down projection's partial sums are combined for `T` tokens: add_all, add_owner or nccl."""
+        """How the down projection's partial sums are combined for `T` tokens: add_all, add_owner, switch_reduce or nccl."""
         return self._buffers(T, device)["protocol"]
 
     # the four local stages, separately callable so that a benchmark can time them
@@ -157,6 +169,15 @@ class QuantizedMLP:
         rows = b["T"] // y.world
         y.broadcast_rows(y.rank * rows, rows)
 
+    # the switch protocol: plain GEMM into the local replica, then the in-switch sum of the owned rows
+    def stage_down_local(self, b):
+        gemm_fp8(b["aq"], self.wq_d, b["sa"], self.s_d, out_dtype=self.out_dtype, out=b["y_peer"][self._step % 2].local)
+
+    def stage_switch_reduce_owned(self, b):
+        y = b["y_peer"][self._step % 2]
+        rows = b["T"] // y.world
+        y.reduce_rows(y.rank * rows, rows)
+
     def reset_peer_buffers(self):
         """Zero both output buffers on every rank (after anything that added into them out of turn)."""
         for t in self._buf.get("y_peer", []):
@@ -169,6 +190,14 @@ class QuantizedMLP:
         self.stage_norm_quant(x, b)
         self.stage_gate_up(b)
         self.stage_swiglu_quant(b)
+        if b["protocol"] == "switch_reduce":
+            self.stage_down_local(b)
+            self.stage_barrier(b)           # every rank's partial result is in its own replica
+            self.stage_switch_reduce_owned(b)
+            self.stage_barrier(b)           # every rank's rows have been summed and written everywhere
+            y = b["y_peer"][self._step % 2].local
+            self._step += 1
+            return y
         if b["protocol"] != "nccl":
             self.stage_down_add(b)
             self.stage_clear_next(b)

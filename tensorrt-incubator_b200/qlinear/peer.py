@@ -70,6 +70,13 @@ class PeerTensor:
         flags = self._flags if self._flags is not None else self
         _lib.check(_lib.lib().ql_peer_barrier(flags.desc, current_stream(self.local.device)))
 
+    def reduce_rows(self, row0: int, rows: int) -> None:
+        """Replaces rows [row0, row0 + rows) of every replica by their sum over the replicas (formed in the switch,
+        f32 accumulation).  Ranks call it on disjoint row ranges, between two barriers."""
+        row_bytes = self.local.shape[1] * self.local.element_size()
+        _lib.check(_lib.lib().ql_peer_reduce(self.desc, dt.from_torch(self.local.dtype).code, row0 * row_bytes, rows * row_bytes,
+                                             current_stream(self.local.device)))
+
     def broadcast_rows(self, row0: int, rows: int) -> None:
         """Copies rows [row0, row0 + rows) of this rank's replica into every replica."""
         row_bytes = self.local.shape[1] * self.local.element_size()

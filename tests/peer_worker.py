@@ -84,6 +84,18 @@ def main():
             e = rel_err(rs.local, full)
             assert e < 2e-2, f"rank {rank}: ADD_OWNER + broadcast off by {e} for {(M, N, K)}"
             assert same_everywhere(rs.local), "replicas differ after ADD_OWNER + broadcast"
+        # local partial results summed by the switch: one rounding, so at least as close as the bf16 adds above
+        sw_buf = peer.PeerTensor((M, N), torch.bfloat16)
+        if M % world == 0:
+            rows = M // world
+            ql.gemm_fp8(xq[:, rank * kl:(rank + 1) * kl].contiguous(), wq[:, rank * kl:(rank + 1) * kl].contiguous(), sx, sw, out=sw_buf.local)
+            sw_buf.barrier()
+            sw_buf.reduce_rows(rank * rows, rows)
+            sw_buf.barrier()
+            torch.cuda.synchronize()
+            e = rel_err(sw_buf.local, full)
+            assert e < 2e-2, f"rank {rank}: in-switch reduce off by {e} for {(M, N, K)}"
+            assert same_everywhere(sw_buf.local), "replicas differ after the in-switch reduce"
         # with two ranks a + b = b + a, so adding into every replica leaves them identical; with more ranks
         # the order of arrival differs per replica, which is why the MLP then uses owners
         if world == 2:
@@ -101,8 +113,10 @@ def main():
     plain = ql.QuantizedMLP(wg, wu, wd, group=dist.group.WORLD, fused_all_reduce=False)
     want = plain(x).clone()
     scattered = ql.QuantizedMLP(wg, wu, wd, group=dist.group.WORLD, fused_all_reduce="scatter")
-    assert fused.protocol(T, dev) == ("add_all" if world == 2 else "add_owner") and scattered.protocol(T, dev) == "add_owner"
-    for name, mlp in (("auto", fused), ("add-owner", scattered)):
+    switched = ql.QuantizedMLP(wg, wu, wd, group=dist.group.WORLD, fused_all_reduce="switch")
+    assert fused.protocol(T, dev) == ("add_all" if world == 2 else "add_owner")
+    assert scattered.protocol(T, dev) == "add_owner" and switched.protocol(T, dev) == "switch_reduce"
+    for name, mlp in (("auto", fused), ("add-owner", scattered), ("switch", switched)):
         for i in range(3):
             got = mlp(x)
             torch.cuda.synchronize()
