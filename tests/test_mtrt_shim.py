@@ -92,6 +92,56 @@ def test_jit_kernel_from_caller_ptx_with_memref_and_scalar_args(rt):
 
 
 @pytest.mark.gpu
+def test_prebuilt_cubin_artifact_loads_like_ptx(rt, tmp_path):
+    """The module data of a compiled program may be a cubin instead of PTX (cuda.compiled_module, kind and data as in
+    compiler/include/mlir-tensorrt/Dialect/CUDA/IR/CUDAOps.td:157-215): the same entry points take it."""
+    import shutil
+    import subprocess
+    ptxas = shutil.which("ptxas") or "/usr/local/cuda/bin/ptxas"
+    if not os.path.exists(ptxas):
+        pytest.skip("no ptxas on this machine to make a cubin from the test artifact")
+    cubin = tmp_path / "add_scalar.cubin"
+    subprocess.run([ptxas, "-arch=sm_100a", "-o", str(cubin), PTX], check=True)
+    path = str(cubin).encode()
+    mod = rt.mtrt_cuda_module_load_from_ptx_file(path, len(path))
+    assert mod, rt.mtrt_cuda_last_error()
+    fn = rt.mtrt_cuda_module_get_function(mod, b"add_scalar", 10)
+    assert fn, rt.mtrt_cuda_last_error()
+    n = 777
+    x = torch.arange(n, dtype=torch.float32, device="cuda")
+    arr, keep = _args(ctypes.c_void_p(x.data_ptr()), ctypes.c_int32(n), ctypes.c_float(-1.5))
+    rt.mtrt_cuda_launch_kernel(fn, (n + 63) // 64, 1, 1, 64, 1, 1, 0, torch.cuda.current_stream().cuda_stream, arr)
+    torch.cuda.synchronize()
+    assert torch.equal(x.cpu(), torch.arange(n, dtype=torch.float32) - 1.5)
+    rt.mtrt_cuda_module_unload(mod)
+
+
+def test_manifest_file_maps_compiler_names_to_library_kernels(tmp_path):
+    """QL_MTRT_MANIFEST: lines `name = ql:...` bind the names a compiler already emits (read once per process, so the
+    check runs in a child process; resolving a library kernel needs no GPU)."""
+    import subprocess
+    import sys
+    manifest = tmp_path / "kernels.manifest"
+    manifest.write_text("# kernels of program main\n"
+                        "main_quantize_kernel_0 = ql:quantize;in=f32;out=i8;scale=f32;shape=4096x4096\n"
+                        "main_linear_kernel_3 = ql:linear_w8a16;x=bf16;scale=f16;M=16;N=11008;K=4096\n")
+    code = f"""
+import ctypes
+L = ctypes.CDLL({_lib.LIB_PATH!r})
+L.mtrt_cuda_module_load_from_ptx.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
+L.mtrt_cuda_module_load_from_ptx.restype = ctypes.c_void_p
+L.mtrt_cuda_module_get_function.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int64]
+L.mtrt_cuda_module_get_function.restype = ctypes.c_void_p
+mod = L.mtrt_cuda_module_load_from_ptx(b"", 0)
+assert L.mtrt_cuda_module_get_function(mod, b"main_quantize_kernel_0", 22)
+assert L.mtrt_cuda_module_get_function(mod, b"main_linear_kernel_3", 20)
+print("MANIFEST OK")
+"""
+    r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, QL_MTRT_MANIFEST=str(manifest)), capture_output=True, text=True)
+    assert r.returncode == 0 and "MANIFEST OK" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.gpu
 def test_library_kernels_through_the_launch_abi(rt):
     """Kernel names bound to library kernels: same host-side calls, hand-written sm_100a code."""
     mod = rt.mtrt_cuda_module_load_from_ptx(b"", 0)
