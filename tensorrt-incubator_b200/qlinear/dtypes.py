@@ -26,11 +26,16 @@ int8 = dtype("int8", _lib.I8, torch.int8, 8)
 int4 = dtype("int4", _lib.I4, None, 4)
 float8 = dtype("float8", _lib.F8E4M3, torch.float8_e4m3fn, 8)
 
+# plain types `cast` converts between (no kernel of this library involved)
+int32 = dtype("int32", -1, torch.int32, 32)
+int64 = dtype("int64", -1, torch.int64, 64)
+bool = dtype("bool", -1, torch.bool, 8)  # noqa: A001  (Tripy's name)
+
 QUANTIZABLE_DTYPES = (float32, float16, bfloat16)
 QUANTIZED_DTYPES = (int8, int4, float8)
 MAXBOUND = {int8: 127.0, int4: 7.0, float8: 448.0}
 
-_BY_TORCH = {d.torch: d for d in (float32, float16, bfloat16, int8, float8)}
+_BY_TORCH = {d.torch: d for d in (float32, float16, bfloat16, int8, float8, int32, int64, bool)}
 
 
 def from_torch(t) -> dtype:

@@ -153,3 +153,24 @@ def amax_scale(input: torch.Tensor, dtype: dt.dtype, dim=None, block=None, *, sc
     tx, ts = ql_view(x), ql_view(s)
     _lib.check(_lib.lib().ql_amax_scale(tx, ts, attrs, dt.MAXBOUND[dtype], current_stream(x.device)))
     return s
+
+
+def cast(input, dtype: dt.dtype):
+    """Tripy's `cast` (tripy/nvtripy/frontend/ops/cast.py:40-118): into int4 / float8 it is a per-tensor quantize
+    with scale 1.0 (from float32), out of int4 / float8 a per-tensor dequantize with scale 1.0 to float32, followed
+    by an ordinary conversion where the target is something else; int8 converts like any integer type.  The same
+    combinations are refused: float8 -> int4 / int8, int8 -> float8, int4 -> float8 / int8 / int64."""
+    src = dtype_of(input)
+    if src is dtype:
+        return input
+    refused = {dt.float8: (dt.int4, dt.int8), dt.int8: (dt.float8,), dt.int4: (dt.float8, dt.int8, dt.int64)}
+    if dtype in refused.get(src, ()):
+        raise QuantizeError(f"Unsupported cast from {src} to {dtype}.")
+    if src in (dt.int4, dt.float8) or (src is dt.int8 and dtype is dt.bool):
+        input = dequantize(input, 1.0, dt.float32)
+        if dtype is dt.float32:
+            return input
+    if dtype in (dt.int4, dt.float8):
+        x = input if input.dtype == torch.float32 else input.to(torch.float32)
+        return quantize(x, 1.0, dtype)
+    return input.to(dtype.torch)

@@ -68,3 +68,21 @@ def test_linear_rejects_input_scale_with_weight_quant_dim_1():
     lin.input_scale = torch.tensor(1.0)
     with pytest.raises(ql.QuantizeError, match="Unsupported quantization parameters for Linear module."):
         lin(torch.ones(1, 4))
+
+
+def test_cast_refuses_what_tripy_refuses():
+    """tripy/nvtripy/frontend/ops/cast.py:32-38."""
+    q8 = torch.ones(4, dtype=torch.int8)
+    f8 = torch.ones(4).to(torch.float8_e4m3fn)
+    i4 = ql.Int4Tensor.pack(torch.ones(4, dtype=torch.int8))
+    for x, target in [(f8, ql.int4), (f8, ql.int8), (q8, ql.float8), (i4, ql.float8), (i4, ql.int8), (i4, ql.int64)]:
+        with pytest.raises(ql.QuantizeError, match="Unsupported cast"):
+            ql.cast(x, target)
+
+
+def test_cast_between_plain_types_is_an_ordinary_conversion():
+    x = torch.tensor([1.0, -2.0, 3.5])
+    assert ql.cast(x, ql.float32) is x
+    assert ql.cast(x, ql.int32).tolist() == [1, -2, 3]
+    assert ql.cast(torch.tensor([0, 5], dtype=torch.int8), ql.float32).tolist() == [0.0, 5.0]
+    assert ql.cast(torch.tensor([False, True]), ql.int8).tolist() == [0, 1]

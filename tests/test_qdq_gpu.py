@@ -238,3 +238,17 @@ def test_config2_and_3_weight_quantization_full_size():
     assert np.array_equal(to_np(q3), want3)
     v = q3.unpack()
     assert int(v.max()) == 7 and int(v.min()) >= -8
+
+
+@pytest.mark.parametrize("qdt", [ql.float8, ql.int4])
+def test_cast_into_and_out_of_quantized_types(qdt):
+    """Tripy's cast: quantize / dequantize per tensor with scale 1.0
+    (tripy/nvtripy/frontend/ops/cast.py:48-52, tests/integration/test_cast.py:64-74)."""
+    x = torch.tensor([-1.0, 0.0, 0.0, 1.0, 2.5, -3.5, 6.0, 100.0], device="cuda")
+    q = ql.cast(x, qdt)
+    want = ql.quantize(x, 1.0, qdt)
+    assert np.array_equal(to_np(q), to_np(want))
+    back = ql.cast(q, ql.float32)
+    assert torch.equal(back, ql.dequantize(q, 1.0, ql.float32))
+    assert ql.cast(q, ql.bool).tolist() == [True, False, False, True, True, True, True, True]
+    assert ql.cast(x.to(torch.float16), qdt).shape == q.shape   # 16-bit inputs go through float32, as in Tripy
