@@ -31,7 +31,8 @@ typedef enum {
   QL_BF16 = 2,
   QL_I8 = 3,
   QL_I4 = 4,     /* two values per byte, first element in the low nibble */
-  QL_F8E4M3 = 5  /* e4m3fn: no infinities, 0x7F/0xFF are NaN, largest finite 448 */
+  QL_F8E4M3 = 5, /* e4m3fn: no infinities, 0x7F/0xFF are NaN, largest finite 448 */
+  QL_F4E2M1 = 6  /* e2m1fn (0, 0.5, 1, 1.5, 2, 3, 4, 6 and negatives): two per byte, first element in the low nibble */
 } ql_dtype;
 
 typedef enum {
@@ -116,6 +117,17 @@ QL_API int ql_amax_scale(const ql_tensor *input, ql_tensor *scale, const ql_qdq_
 #define QL_NOALLOC_MAX_SCALES 65536
 QL_API int ql_amax_scale_noalloc(const ql_tensor *input, ql_tensor *scale, const ql_qdq_attrs *attrs,
                                  float maxbound, void *stream);
+
+/* NVFP4.  ql_dynamic_quantize is tensorrt.dynamic_quantize (TensorRTOps.td:3279-3358; checks and wording of
+ * Verification.cpp:1270-1290): blocks of 16 along `axis` (the last axis; the second last is legal for the operator
+ * but not built), scales [..., K/16] = e4m3((max|block| / 6) / double_quant_scale), result = e2m1(x / (scale *
+ * double_quant_scale)).  ql_dequantize_nvfp4 is the operator's documented inverse, the two tensorrt.dequantize
+ * steps in one pass: output = e2m1 value * (e4m3 scale * double_quant_scale).  double_quant_scale is a rank-0
+ * device tensor.  Data tensors of type QL_F4E2M1 carry their logical shape; the buffer holds numel / 2 bytes. */
+QL_API int ql_dynamic_quantize(const ql_tensor *input, const ql_tensor *double_quant_scale, int32_t axis,
+                               int32_t block_size, ql_tensor *result, ql_tensor *scales, void *stream);
+QL_API int ql_dequantize_nvfp4(const ql_tensor *data, const ql_tensor *scales, const ql_tensor *double_quant_scale,
+                               ql_tensor *output, void *stream);
 
 /* Weight-only linear layers, Y[M,N] = X[M,K] . dequantize(W)[N,K]^T with f32 accumulation
  * (linear.py:140-151 with quant_dtype set and no input scale).

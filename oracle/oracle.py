@@ -68,6 +68,12 @@ def lib():
         L.orc_silu_mul.argtypes = [f, f]
         L.orc_silu_mul.restype = f
         L.orc_num_threads.restype = ci
+        L.orc_dynamic_quantize_nvfp4.argtypes = [vp, ci, i64, i64, f, vp, vp]
+        L.orc_dequantize_nvfp4.argtypes = [vp, vp, f, i64, i64, vp, ci]
+        L.orc_f32_to_f4e2m1.argtypes = [f]
+        L.orc_f32_to_f4e2m1.restype = ctypes.c_uint8
+        L.orc_f4e2m1_to_f32.argtypes = [ctypes.c_uint8]
+        L.orc_f4e2m1_to_f32.restype = f
         _lib = L
     return _lib
 
@@ -252,6 +258,29 @@ def swiglu_quant_fp8(GU, x_code):
     s = np.zeros(M, dtype=np.float32)
     lib().orc_swiglu_quant_fp8(_ptr(np.ascontiguousarray(GU)), x_code, M, I2 // 2, _ptr(Q), _ptr(s))
     return Q, s
+
+
+def dynamic_quantize_nvfp4(x, x_code, double_quant_scale=1.0):
+    """tensorrt.dynamic_quantize over the last axis: (packed e2m1 bytes [..., K/2], e4m3 block scales [..., K/16])."""
+    K = x.shape[-1]
+    rows = x.size // K
+    q = np.empty(x.shape[:-1] + (K // 2,), dtype=np.uint8)
+    s = np.empty(x.shape[:-1] + (K // 16,), dtype=np.uint8)
+    xc = np.ascontiguousarray(x)
+    rc = lib().orc_dynamic_quantize_nvfp4(_ptr(xc), x_code, rows, K, float(double_quant_scale), _ptr(q), _ptr(s))
+    assert rc == 0
+    return q, s
+
+
+def dequantize_nvfp4(q, scales, double_quant_scale, y_code):
+    """e2m1 data * (e4m3 block scale * double_quant_scale) -> array of y_code, shape [..., K]."""
+    K = q.shape[-1] * 2
+    rows = q.size * 2 // K
+    y = np.empty(q.shape[:-1] + (K,), dtype={F32: np.float32, F16: np.float16, BF16: np.uint16}[y_code])
+    qc, sc = np.ascontiguousarray(q), np.ascontiguousarray(scales)
+    rc = lib().orc_dequantize_nvfp4(_ptr(qc), _ptr(sc), float(double_quant_scale), rows, K, _ptr(y), y_code)
+    assert rc == 0
+    return y
 
 
 def f8_to_f32(bits: np.ndarray) -> np.ndarray:

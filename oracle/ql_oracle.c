@@ -419,6 +419,77 @@ int orc_swiglu_quant_fp8(const void *GU, int x_dtype, int64_t M, int64_t I, uint
   return 0;
 }
 
+/* ---- NVFP4 (tensorrt.dynamic_quantize, tensorrt/include/mlir-tensorrt-dialect/TensorRT/IR/TensorRTOps.td:3279-3358):
+ * blocks of 16 along the last axis; block scale = max|x| / 6 divided by the per-tensor "double quantization" scale
+ * and rounded to e4m3; data = x / (e4m3 scale * double_quant_scale) rounded to e2m1 (values 0, 0.5, 1, 1.5, 2, 3, 4, 6
+ * and their negatives; round to nearest even, saturating, as PTX cvt.rn.satfinite.e2m1x2.f32 which the reference's
+ * kernel backend uses, kernel/lib/Kernel/Transforms/LowerToNVVM.cpp:339-392).  Pinned by the known answer of
+ * compiler/test/python/IntegrationTests/test_tensorrt_fp4.py.  A block whose scale rounds to zero quantizes to
+ * zeros (this implementation's choice; the reference has no test there). */
+static const float kE2M1[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+
+float orc_f4e2m1_to_f32(uint8_t nibble) {
+  float v = kE2M1[nibble & 7];
+  return (nibble & 8) ? -v : v;
+}
+
+uint8_t orc_f32_to_f4e2m1(float f) {
+  if (f != f) return 0x7; /* satfinite: NaN becomes the largest positive value */
+  uint8_t sign = (f < 0.0f || (f == 0.0f && 1.0f / f < 0.0f)) ? 8 : 0;
+  float a = fabsf(f);
+  if (a >= 6.0f) return sign | 7;
+  /* nearest representable value; a tie goes to the one with an even mantissa bit (even index here, because
+   * the codes alternate mantissa 0 / 1) */
+  int best = 0;
+  for (int i = 1; i < 8; i++) {
+    float dlo = fabsf(a - kE2M1[best]), dhi = fabsf(kE2M1[i] - a);
+    if (dhi < dlo || (dhi == dlo && (i & 1) == 0)) best = i;
+  }
+  return sign | (uint8_t)best;
+}
+
+/* x: [rows, K] (K % 16 == 0) of x_dtype; q: rows*K/2 bytes, first element in the low nibble; scales: [rows, K/16] e4m3 */
+int orc_dynamic_quantize_nvfp4(const void *x, int x_dtype, int64_t rows, int64_t K, float double_quant_scale, uint8_t *q,
+                               uint8_t *scales) {
+  if (K % 16 != 0) return -1;
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; r++) {
+    for (int64_t b = 0; b < K / 16; b++) {
+      const int64_t base = r * K + b * 16;
+      float amax = 0.0f;
+      for (int i = 0; i < 16; i++) amax = fmaxf(amax, fabsf(load_as_f32(x, x_dtype, base + i)));
+      const uint8_t sq = orc_f32_to_f8e4m3((amax / 6.0f) / double_quant_scale);
+      scales[r * (K / 16) + b] = sq;
+      const float s = orc_f8e4m3_to_f32(sq) * double_quant_scale;
+      for (int i = 0; i < 16; i += 2) {
+        uint8_t lo = 0, hi = 0;
+        if (s != 0.0f) {
+          lo = orc_f32_to_f4e2m1(load_as_f32(x, x_dtype, base + i) / s);
+          hi = orc_f32_to_f4e2m1(load_as_f32(x, x_dtype, base + i + 1) / s);
+        }
+        q[(base + i) / 2] = (uint8_t)(lo | (hi << 4));
+      }
+    }
+  }
+  return 0;
+}
+
+/* y = e2m1 value * (e4m3 block scale * double_quant_scale): the two tensorrt.dequantize steps of the operator's
+ * documented use, each one f32 multiply, the last rounded to y_dtype */
+int orc_dequantize_nvfp4(const uint8_t *q, const uint8_t *scales, float double_quant_scale, int64_t rows, int64_t K, void *y,
+                         int y_dtype) {
+  if (K % 16 != 0) return -1;
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; r++)
+    for (int64_t k = 0; k < K; k++) {
+      const int64_t i = r * K + k;
+      const float s = orc_f8e4m3_to_f32(scales[r * (K / 16) + k / 16]) * double_quant_scale;
+      const uint8_t nib = (i & 1) ? (q[i / 2] >> 4) : (q[i / 2] & 0xF);
+      store_from_f32(y, y_dtype, i, orc_f4e2m1_to_f32(nib) * s);
+    }
+  return 0;
+}
+
 int orc_num_threads(void) {
   int n = 1;
 #ifdef _OPENMP

@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(os.path.dirname(HERE), "lib", "libqlinear_b200.so")
 QL_MAX_RANK = 8
 
 # ql_dtype
-F32, F16, BF16, I8, I4, F8E4M3 = 0, 1, 2, 3, 4, 5
+F32, F16, BF16, I8, I4, F8E4M3, F4E2M1 = 0, 1, 2, 3, 4, 5, 6
 # ql_status
 OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_NO_DEVICE, ERR_DEVICE_TIMEOUT = range(6)
 # ql_fp8_mode
@@ -65,6 +65,8 @@ SIGNATURES = {
     "ql_quantize_dequantize": ([_T, _T, _T, _T, _A, _S], ctypes.c_int),
     "ql_amax_scale": ([_T, _T, _A, ctypes.c_float, _S], ctypes.c_int),
     "ql_amax_scale_noalloc": ([_T, _T, _A, ctypes.c_float, _S], ctypes.c_int),
+    "ql_dynamic_quantize": ([_T, _T, ctypes.c_int32, ctypes.c_int32, _T, _T, _S], ctypes.c_int),
+    "ql_dequantize_nvfp4": ([_T, _T, _T, _T, _S], ctypes.c_int),
     "ql_linear_w8a16": ([_T, _T, _T, _T, _S], ctypes.c_int),
     "ql_linear_w4a16": ([_T, _T, _T, _T, _S], ctypes.c_int),
     "ql_gemm_fp8": ([_T, _T, _T, _T, _T, _S], ctypes.c_int),

@@ -25,6 +25,7 @@ bfloat16 = dtype("bfloat16", _lib.BF16, torch.bfloat16, 16)
 int8 = dtype("int8", _lib.I8, torch.int8, 8)
 int4 = dtype("int4", _lib.I4, None, 4)
 float8 = dtype("float8", _lib.F8E4M3, torch.float8_e4m3fn, 8)
+float4 = dtype("float4", _lib.F4E2M1, None, 4)   # e2m1; only produced by dynamic_quantize
 
 # plain types `cast` converts between (no kernel of this library involved)
 int32 = dtype("int32", -1, torch.int32, 32)

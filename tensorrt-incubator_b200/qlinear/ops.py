@@ -10,7 +10,7 @@ import torch
 
 from . import _lib
 from . import dtypes as dt
-from .tensor import Int4Tensor, current_stream, dtype_of, empty_quantized, ql_view, require_cuda
+from .tensor import Float4Tensor, Int4Tensor, current_stream, dtype_of, empty_quantized, ql_view, require_cuda
 
 
 class QuantizeError(ValueError):
@@ -174,3 +174,38 @@ def cast(input, dtype: dt.dtype):
         x = input if input.dtype == torch.float32 else input.to(torch.float32)
         return quantize(x, 1.0, dtype)
     return input.to(dtype.torch)
+
+
+def _global_scale(value, device) -> torch.Tensor:
+    t = value if isinstance(value, torch.Tensor) else torch.tensor(float(value), dtype=torch.float32)
+    if t.dim() != 0:
+        raise QuantizeError(f"double_quant_scale must be a scalar tensor, got rank={t.dim()}.")
+    return t.to(device).contiguous()
+
+
+def dynamic_quantize(input: torch.Tensor, double_quant_scale=1.0, axis: int = -1, block_size: int = 16):
+    """tensorrt.dynamic_quantize (NVFP4; tensorrt/include/mlir-tensorrt-dialect/TensorRT/IR/TensorRTOps.td:3279-3358):
+    returns (data, scales): `data` a Float4Tensor of the input's shape, `scales` e4m3 with one entry per block of 16
+    along `axis`, scales = (max|block| / 6) / double_quant_scale, data = input / (scales * double_quant_scale)."""
+    require_cuda(input, "input")
+    x = input.contiguous()
+    ax = axis if axis >= 0 else x.dim() + axis
+    gs = _global_scale(double_quant_scale, x.device)
+    shape = tuple(x.shape)
+    last = shape[-1] if shape else 0
+    data = Float4Tensor(torch.empty(max(x.numel() // 2, 0), dtype=torch.uint8, device=x.device), shape) if x.numel() % 2 == 0 else None
+    if data is None:
+        raise QuantizeError("shape(input)[axis] must be divisible by 16.")
+    scales = torch.empty(shape[:-1] + (last // 16,), dtype=torch.float8_e4m3fn, device=x.device)
+    _lib.check(_lib.lib().ql_dynamic_quantize(ql_view(x), ql_view(gs), ax, block_size, ql_view(data), ql_view(scales), current_stream(x.device)))
+    return data, scales
+
+
+def dequantize_nvfp4(data: Float4Tensor, scales: torch.Tensor, double_quant_scale=1.0, dtype: dt.dtype = dt.float32) -> torch.Tensor:
+    """The inverse of dynamic_quantize: data * (scales * double_quant_scale) as `dtype` (the two tensorrt.dequantize
+    steps of the operator's documented use, in one pass)."""
+    require_cuda(data, "data")
+    gs = _global_scale(double_quant_scale, data.device)
+    y = torch.empty(data.shape, dtype=dtype.torch, device=data.device)
+    _lib.check(_lib.lib().ql_dequantize_nvfp4(ql_view(data), ql_view(scales.contiguous()), ql_view(gs), ql_view(y), current_stream(data.device)))
+    return y

@@ -46,7 +46,36 @@ class Int4Tensor:
         return Int4Tensor(packed, values.shape)
 
 
+class Float4Tensor:
+    """e2m1 values, two per byte with the first element in the low nibble; `packed` is a flat uint8 tensor of
+    numel / 2 bytes, `shape` the logical shape (last dimension a multiple of 16: NVFP4 blocks)."""
+
+    dtype = dt.float4
+    _VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+    def __init__(self, packed: torch.Tensor, shape):
+        self.shape = tuple(int(s) for s in shape)
+        assert packed.dtype == torch.uint8 and packed.numel() * 2 == math.prod(self.shape)
+        self.packed = packed.contiguous()
+
+    @property
+    def device(self):
+        return self.packed.device
+
+    def numel(self) -> int:
+        return math.prod(self.shape)
+
+    def unpack(self) -> torch.Tensor:
+        """float32 tensor of the logical shape (a host-side convenience for tests)."""
+        p = self.packed.to(torch.int64)
+        codes = torch.stack([p & 0xF, (p >> 4) & 0xF], dim=1).reshape(-1)
+        lut = torch.tensor(self._VALUES + tuple(-v for v in self._VALUES), dtype=torch.float32, device=codes.device)
+        return lut[codes].reshape(self.shape)
+
+
 def dtype_of(t) -> dt.dtype:
+    if isinstance(t, Float4Tensor):
+        return dt.float4
     if isinstance(t, Int4Tensor):
         return dt.int4
     return dt.from_torch(t.dtype)
@@ -56,6 +85,8 @@ def ql_view(t) -> _lib.QlTensor:
     """QlTensor over a CUDA torch tensor or Int4Tensor (no copy; the caller keeps `t` alive)."""
     if isinstance(t, Int4Tensor):
         return _lib.make_tensor(t.packed.data_ptr(), _lib.I4, t.shape)
+    if isinstance(t, Float4Tensor):
+        return _lib.make_tensor(t.packed.data_ptr(), _lib.F4E2M1, t.shape)
     if not t.is_contiguous():
         raise _lib.QlError(_lib.ERR_INVALID_ARGUMENT, "tensors must be contiguous (dense row-major)")
     return _lib.make_tensor(t.data_ptr(), dt.from_torch(t.dtype).code, t.shape)

@@ -1,0 +1,64 @@
+"""NVFP4 (tensorrt.dynamic_quantize and its inverse) on the GPU against the oracle: e2m1 data and e4m3 block
+scales bit for bit, the dequantized values bit for bit; the reference's own known answer
+(compiler/test/python/IntegrationTests/test_tensorrt_fp4.py:74-82) through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as orc
+import qlinear as ql
+from helpers import code_of, randn, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+def test_reference_known_answer(kat):
+    case = kat["nvfp4_dynamic_quantize"]
+    x = torch.tensor(case["input"], dtype=torch.float32, device="cuda")
+    data, scales = ql.dynamic_quantize(x, case["double_quant_scale"], axis=1)
+    assert data.shape == (2, 32) and tuple(scales.shape) == (2, 2)
+    y = ql.dequantize_nvfp4(data, scales, case["double_quant_scale"], ql.float32)
+    assert np.array_equal(y.cpu().numpy(), np.array(case["expected"], dtype=np.float32))
+    assert torch.equal(data.unpack() * scales.float().repeat_interleave(16, dim=1), y)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape,gscale", [((7, 48), 1.0), ((3, 5, 160), 0.25), ((1024, 4096), 2.0), ((16,), 1.0)])
+def test_matches_oracle(dtype, shape, gscale):
+    x = randn(shape, dtype, 900 + len(shape), std=3.0)
+    data, scales = ql.dynamic_quantize(x, gscale)
+    want_q, want_s = orc.dynamic_quantize_nvfp4(to_np(x), code_of(x), gscale)
+    assert np.array_equal(to_np(scales), want_s)
+    assert np.array_equal(data.packed.cpu().numpy().reshape(want_q.shape), want_q)
+    for out in (ql.float32, dtype and ql.dtypes.from_torch(dtype)):
+        y = ql.dequantize_nvfp4(data, scales, gscale, out)
+        want_y = orc.dequantize_nvfp4(want_q, want_s, gscale, out.code)
+        assert np.array_equal(to_np(y).view(np.uint8), want_y.view(np.uint8))
+
+
+def test_edge_values():
+    # zeros (scale rounds to zero -> zeros), ties, saturation, a huge block and a tiny one next to each other
+    x = torch.zeros((4, 32), device="cuda")
+    x[1, :16] = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, -6.0])
+    x[2, :16] = 1e30
+    x[2, 16:] = 1e-30
+    x[3, 5] = float("inf")
+    data, scales = ql.dynamic_quantize(x, 1.0)
+    want_q, want_s = orc.dynamic_quantize_nvfp4(x.cpu().numpy(), orc.F32, 1.0)
+    assert np.array_equal(to_np(scales), want_s)
+    assert np.array_equal(data.packed.cpu().numpy().reshape(want_q.shape), want_q)
+    assert torch.equal(data.unpack()[0], torch.zeros(32, device="cuda"))
+    # block of row 1: scale 1 exactly, so the e2m1 rounding is visible: ties to even
+    assert data.unpack()[1, :8].tolist() == [0.0, 1.0, 1.0, 2.0, 2.0, 4.0, 4.0, 6.0]
+
+
+def test_argument_rules():
+    x = torch.ones((4, 24), device="cuda")
+    with pytest.raises(ql.QlError, match="must be divisible by 16"):
+        ql.dynamic_quantize(x)
+    with pytest.raises(ql.QlError, match="only block size of 16"):
+        ql.dynamic_quantize(torch.ones((4, 32), device="cuda"), block_size=32)
+    with pytest.raises(ql.QlError, match="invalid axis"):
+        ql.dynamic_quantize(torch.ones((2, 4, 32), device="cuda"), axis=0)
+    with pytest.raises(ql.QlError, match="second last dimension are not built"):
+        ql.dynamic_quantize(torch.ones((32, 32), device="cuda"), axis=0)

@@ -150,3 +150,22 @@ def test_fp8_modes_differ_where_documented(orc):
     y = np.array([1.0625 + 2.0 ** -12], dtype=np.float32)
     assert _f8_decode(orc, orc.quantize(y, 0, s, 0, CODE["f8"], 0, fp8_mode=0)).tolist() == [1.125]
     assert _f8_decode(orc, orc.quantize(y, 0, s, 0, CODE["f8"], 0, fp8_mode=1)).tolist() == [1.0]
+
+
+def test_nvfp4_dynamic_quantize_known_answer(orc, kat):
+    """The reference's only NVFP4 execution test: quantize to e2m1 with e4m3 block-16 scales, dequantize back."""
+    case = kat["nvfp4_dynamic_quantize"]
+    x = np.array(case["input"], dtype=np.float32)
+    q, s = orc.dynamic_quantize_nvfp4(x, orc.F32, case["double_quant_scale"])
+    assert q.shape == (2, 16) and s.shape == (2, 2)
+    y = orc.dequantize_nvfp4(q, s, case["double_quant_scale"], orc.F32)
+    assert np.array_equal(y, np.array(case["expected"], dtype=np.float32))
+
+
+def test_e2m1_rounding_is_nearest_even_and_saturating(orc):
+    L = orc.lib()
+    values = [L.orc_f4e2m1_to_f32(i) for i in range(16)]
+    assert values[:8] == [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0] and values[9] == -0.5 and values[15] == -6.0
+    # ties go to the code with an even mantissa: 0.25 -> 0, 0.75 -> 1, 1.25 -> 1, 1.75 -> 2, 2.5 -> 2, 3.5 -> 4, 5 -> 4
+    for x, want in [(0.25, 0.0), (0.75, 1.0), (1.25, 1.0), (1.75, 2.0), (2.5, 2.0), (3.5, 4.0), (5.0, 4.0), (5.01, 6.0), (1e9, 6.0), (-7.0, -6.0), (0.26, 0.5)]:
+        assert L.orc_f4e2m1_to_f32(L.orc_f32_to_f4e2m1(x)) == want, x
