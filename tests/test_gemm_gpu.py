@@ -113,3 +113,36 @@ def test_config4_slice_and_linearity():
     ref = (x.double() @ w.double().T).cpu().numpy()
     err = np.abs(float_values(y) - ref).max() / np.abs(ref).max()
     assert err < 0.1
+
+
+def test_config4_full_size():
+    """Config 4 at its full size (8192 x 8192 x 28672, the CTA-pair kernel over 3584 tiles): bands of rows and columns
+    against the oracle, exact linearity in the scale, and a checksum of checksums: the column sums of Y equal the
+    product of X's column sums with W (a property that involves every tile)."""
+    M, K, N = 8192, 8192, 28672
+    g = torch.Generator(device="cuda").manual_seed(1004)
+    xq = torch.randn((M, K), generator=g, device="cuda").to(torch.float8_e4m3fn)
+    wq = (torch.randn((N, K), generator=g, device="cuda") * 0.5).to(torch.float8_e4m3fn)
+    sx = torch.tensor(2.0 ** -6, device="cuda")
+    sw = torch.tensor(2.0 ** -5, device="cuda")
+    y = ql.gemm_fp8(xq, wq, sx, sw)
+    _status_ok()
+    for rows, cols in [(slice(0, 40), slice(0, 48)), (slice(M - 40, M), slice(N - 48, N)), (slice(4000, 4040), slice(14300, 14348))]:
+        want = orc.gemm_fp8(to_np(xq[rows]), to_np(wq[cols]), to_np(sx), to_np(sw), orc.F32)
+        assert_close_rel(float_values(y[rows, cols]), want, 2.0 ** -8, f"config 4 band {rows} x {cols}")
+    y2 = ql.gemm_fp8(xq, wq, sx * 2, sw)
+    assert torch.equal(y2, y * 2)
+    del y2
+    # checksum of checksums in f64: sum_m Y[m, n] against (sum_m X[m, :]) . W[n, :] * sx * sw; bf16 rounding of the
+    # 8192 summands averages out, so the bound is far below one rounding step of a single element
+    col_sums = torch.zeros(N, dtype=torch.float64, device="cuda")
+    for r0 in range(0, M, 1024):
+        col_sums += y[r0:r0 + 1024].double().sum(0)
+    x_sums = torch.zeros(K, dtype=torch.float64, device="cuda")
+    for r0 in range(0, M, 1024):
+        x_sums += xq[r0:r0 + 1024].double().sum(0)
+    want_sums = torch.zeros(N, dtype=torch.float64, device="cuda")
+    for n0 in range(0, N, 4096):
+        want_sums[n0:n0 + 4096] = (wq[n0:n0 + 4096].double() @ x_sums) * float(sx) * float(sw)
+    rms = float((y[:256].double() ** 2).mean().sqrt())
+    assert float((col_sums - want_sums).abs().max()) < 2.0 ** -8 * rms * M ** 0.5 * 4

@@ -84,3 +84,22 @@ def test_column_row_split_sums_to_the_unsharded_block():
     total = (parts[0] + parts[1]).double()
     rel = float((total - full.double()).norm() / full.double().norm())
     assert rel < 0.06, rel
+
+
+def test_config5_full_size_first_tokens_against_the_oracle():
+    """Config 5 at its full size (4096 tokens, 8192 -> 28672 -> 8192): the GPU runs the whole block; the oracle runs
+    the same weights on the first and the last four tokens (every token's result depends on all of both weight
+    matrices, so these rows exercise every column tile of both GEMMs)."""
+    T, H, I = 4096, 8192, 28672
+    g = torch.Generator(device="cuda").manual_seed(1005)
+    def w(shape):
+        return (torch.randn(shape, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    wg, wu, wd = w((I, H)), w((I, H)), w((H, I))
+    x = torch.randn((T, H), generator=g, device="cuda").to(torch.bfloat16)
+    mlp = ql.QuantizedMLP(wg, wu, wd)
+    y = mlp(x)
+    assert ql.lib().ql_gemm_status(None) == 0
+    rows = torch.cat([x[:4], x[-4:]]).contiguous()
+    want = _oracle_mlp(rows, wg, wu, wd, orc.BF16)
+    got = torch.cat([y[:4], y[-4:]])
+    assert_close_rel(float_values(got), want, 1e-2, "config 5 full size")
