@@ -620,6 +620,19 @@ def cpu_reference(workload: str, budget_s: float = 12.0):
     raise SystemExit(f"no CPU restatement for workload {workload}")
 
 
+def reference_config(wl, gpus):
+    """The workload's `config` object without a GPU: the same keys the product arm prints."""
+    obj = object.__new__(wl)
+    if hasattr(wl, "N"):
+        obj.nl = wl.N // max(1, gpus)
+    if hasattr(wl, "I"):
+        obj.il = wl.I // max(1, gpus)
+    try:
+        return wl.config(obj)
+    except AttributeError:
+        return {"workload": wl.name}
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -640,8 +653,9 @@ def run_reference_arm(args):
     line = {"impl": "reference", "metric": wl.metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": wl.dtype, "data": "synthetic (seeded)",
-            "config": {"workload": wl.name, "arm": "CPU restatement of the reference's host path (oracle/ql_oracle.c); "
-                       "the reference itself cannot be built here"},
+            "config": dict(reference_config(wl, args.gpus), parallelism=f"{cores} host threads (OpenMP)", timing="wall clock",
+                           arm="CPU restatement of the reference's host path (oracle/ql_oracle.c); the reference itself cannot "
+                               "be built here"),
             "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
