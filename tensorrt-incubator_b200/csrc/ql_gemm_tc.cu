@@ -445,6 +445,10 @@ __device__ __forceinline__ uint32_t make_instr_desc_pair() {
 // only the first wave waits noticeably (one chunk per CTA), and the rest of the conversion's HBM traffic hides
 // under the MMAs.  The launch is cooperative (all CTAs resident), so a waiting producer cannot starve the CTA
 // that owes it a chunk; waits are bounded all the same.  The last CTA to finish clears the counters.
+// (Widening per tile in shared memory inside this kernel, with converter warps feeding the MMA's B operand, was
+// built and measured: 362 us at M = 2048 with sixteen warps converting every k-block together, 202-215 us with the
+// warps split into four groups taking k-blocks in turn, against 147 us here; deeper rings changed nothing.  ncu
+// showed the converter warps stalled in the proxy fence and on the barriers; the limiter was not identified.)
 constexpr int kWidenThreads = 256;
 constexpr int kWidenChunkRows = 8;
 struct WidenArgs {
