@@ -521,7 +521,72 @@ class Fp8Mlp(Workload):
                 "l2": "weights and activations (>= 150 MiB per GPU) exceed the 126 MiB L2", "seed": 1005}
 
 
-WORKLOADS = {"c1": QdqInt8, "c2": W8A16Linear, "c3": W4A16Linear, "c4": Fp8Gemm, "c5": Fp8Mlp}
+class Nvfp4Qdq(Workload):
+    """Not a BASELINE config: tensorrt.dynamic_quantize (NVFP4, blocks of 16, e4m3 block scales) of x bf16 [8192,8192]
+    ~ N(0,1) and the inverse, timed as two parts."""
+
+    name = "nvfp4_dynamic_quantize_round_trip"
+    metric = "Q/DQ HBM GB/s (NVFP4 dynamic quantize + dequantize, bf16 [8192,8192])"
+    unit = "GB/s"
+    dtype = "bf16 -> e2m1 + e4m3 block scales -> bf16"
+    SHAPE = (8192, 8192)
+    REPLICAS = 3  # 3 x (128 + 32 + 4 + 128) MiB
+
+    def __init__(self, torch, ql, device, dist=None, seed=1006):
+        self.torch, self.ql, self.device = torch, ql, device
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        self.x_host = torch.randn(self.SHAPE, generator=g, dtype=torch.float32).to(torch.bfloat16).pin_memory()
+        x = self.x_host.to(device)
+        n = self.SHAPE[0] * self.SHAPE[1]
+        self.gs = torch.ones((), dtype=torch.float32, device=device)
+        self.x = [x] + [x.clone() for _ in range(self.REPLICAS - 1)]
+        self.q = [ql.Float4Tensor(torch.empty(n // 2, dtype=torch.uint8, device=device), self.SHAPE) for _ in range(self.REPLICAS)]
+        self.s = [torch.empty((self.SHAPE[0], self.SHAPE[1] // 16), dtype=torch.float8_e4m3fn, device=device) for _ in range(self.REPLICAS)]
+        self.y = [torch.empty(self.SHAPE, dtype=torch.bfloat16, device=device) for _ in range(self.REPLICAS)]
+        self.y_host = torch.empty(self.SHAPE, dtype=torch.bfloat16).pin_memory()
+        self.turn = 0
+        from qlinear import _lib
+        from qlinear.tensor import current_stream, ql_view
+        self._lib, self._view, self._stream = _lib, ql_view, current_stream
+
+    def p_quant(self):
+        i = self.turn % self.REPLICAS
+        L = self._lib
+        L.check(L.lib().ql_dynamic_quantize(self._view(self.x[i]), self._view(self.gs), 1, 16, self._view(self.q[i]), self._view(self.s[i]),
+                                            self._stream(self.device)))
+
+    def p_dequant(self):
+        i = self.turn % self.REPLICAS
+        self.turn += 1
+        L = self._lib
+        L.check(L.lib().ql_dequantize_nvfp4(self._view(self.q[i]), self._view(self.s[i]), self._view(self.gs), self._view(self.y[i]),
+                                            self._stream(self.device)))
+
+    def parts(self):
+        n = self.SHAPE[0] * self.SHAPE[1]
+        packed = n // 2 + n // 16
+        return [("dynamic_quantize", self.p_quant, 0, 2 * n + packed, "hbm"), ("dequantize", self.p_dequant, 0, packed + 2 * n, "hbm")]
+
+    def e2e_units(self, step):
+        i = step % self.REPLICAS
+
+        def run():
+            self.turn = i
+            self.p_quant()
+            self.p_dequant()
+        return [(("x", i), ("y", i), (lambda: self.x[i].copy_(self.x_host, non_blocking=True)), run,
+                 (lambda: self.y_host.copy_(self.y[i], non_blocking=True)))]
+
+    def e2e_bytes(self):
+        n = self.SHAPE[0] * self.SHAPE[1]
+        return 2 * n, 2 * n
+
+    def config(self):
+        return {"workload": self.name, "shape": list(self.SHAPE), "double_quant_scale": 1.0, "block": 16,
+                "l2": f"{self.REPLICAS} input/output replicas (876 MiB > 126 MiB L2) cycled per step", "seed": 1006}
+
+
+WORKLOADS = {"c1": QdqInt8, "c2": W8A16Linear, "c3": W4A16Linear, "c4": Fp8Gemm, "c5": Fp8Mlp, "nvfp4": Nvfp4Qdq}
 
 
 # ----------------------------------------------------------------------------------------------
@@ -617,6 +682,18 @@ def cpu_reference(workload: str, budget_s: float = 12.0):
             reps += 1
         dt = time.perf_counter() - t0
         return 9.0 * n * reps / dt / 1e9, "GB/s", 1, f"{reps} x (quantize + dequantize) of {n} f32 elements, scalar loop, {dt:.1f} s"
+    if workload == "nvfp4":
+        rows, K = 512, 8192
+        x = orc.from_f32(rng.standard_normal((rows, K)).astype(np.float32), orc.BF16)
+        reps = 0
+        t0 = time.perf_counter()
+        while time.perf_counter() - t0 < budget_s:
+            q, sc = orc.dynamic_quantize_nvfp4(x, orc.BF16, 1.0)
+            orc.dequantize_nvfp4(q, sc, 1.0, orc.BF16)
+            reps += 1
+        dt = time.perf_counter() - t0
+        n = rows * K
+        return (2 * n + n // 2 + n // 16) * 2.0 * reps / dt / 1e9, "GB/s", cores, f"{reps} x (dynamic_quantize + dequantize) of {rows} x {K} bf16 elements, {dt:.1f} s"
     raise SystemExit(f"no CPU restatement for workload {workload}")
 
 
