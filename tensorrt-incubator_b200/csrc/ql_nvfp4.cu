@@ -27,6 +27,10 @@ __device__ __forceinline__ float2 e2m1x2_to_f32x2(uint32_t byte) {
   return __half22float2(*reinterpret_cast<__half2 *>(&h2));
 }
 
+constexpr int kUnrollF4 = 4; // blocks whose loads one thread has in flight at once
+
+// (Keeping several blocks' loads in flight per thread, as the dequantize kernel does, was measured slower here:
+// 64 more live registers for 75 us against 47 us.)
 template <typename InT>
 __global__ void __launch_bounds__(kThreadsF4)
 nvfp4_quantize_kernel(const InT *__restrict__ x, const void *__restrict__ gs, int gsdt, uint8_t *__restrict__ q,
@@ -57,18 +61,32 @@ nvfp4_dequantize_kernel(const uint8_t *__restrict__ q, const uint8_t *__restrict
                         OutT *__restrict__ y, int64_t nblocks) {
   const float g = load_scale(gs, gsdt, 0);
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < nblocks; b += stride) {
-    const uint2 w = *reinterpret_cast<const uint2 *>(q + b * 8);
-    const float s = e4m3x2_to_f32x2((uint32_t)scales[b]).x * g;
-    const uint32_t ww[2] = {w.x, w.y};
-    float v[16];
+  for (int64_t b0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b0 < nblocks; b0 += stride * kUnrollF4) {
+    uint2 w[kUnrollF4];
+    uint32_t sq[kUnrollF4];
 #pragma unroll
-    for (int i = 0; i < 16; i += 2) {
-      const float2 f = e2m1x2_to_f32x2((ww[i >> 3] >> (4 * (i & 7))) & 0xFFu);
-      v[i] = f.x * s;
-      v[i + 1] = f.y * s;
+    for (int u = 0; u < kUnrollF4; u++) {
+      const int64_t b = b0 + u * stride;
+      if (b < nblocks) {
+        w[u] = __ldcs(reinterpret_cast<const uint2 *>(q + b * 8));
+        sq[u] = scales[b];
+      }
     }
-    store_vec_f32<OutT, 16>(y + b * 16, v);
+#pragma unroll
+    for (int u = 0; u < kUnrollF4; u++) {
+      const int64_t b = b0 + u * stride;
+      if (b >= nblocks) break;
+      const float s = e4m3x2_to_f32x2(sq[u]).x * g;
+      const uint32_t ww[2] = {w[u].x, w[u].y};
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; i += 2) {
+        const float2 f = e2m1x2_to_f32x2((ww[i >> 3] >> (4 * (i & 7))) & 0xFFu);
+        v[i] = f.x * s;
+        v[i + 1] = f.y * s;
+      }
+      store_vec_f32<OutT, 16>(y + b * 16, v);
+    }
   }
 }
 
@@ -98,8 +116,8 @@ int check_nvfp4(const char *op, const ql_tensor *x, const ql_tensor *gs, const q
   return QL_OK;
 }
 
-unsigned grid_for(int64_t nblocks) {
-  int64_t blocks = (nblocks + kThreadsF4 - 1) / kThreadsF4;
+unsigned grid_for(int64_t nblocks, int per_thread) {
+  int64_t blocks = (nblocks + kThreadsF4 * per_thread - 1) / (kThreadsF4 * per_thread);
   const int64_t cap = (int64_t)sm_count() * 8;
   return (unsigned)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
 }
@@ -129,9 +147,9 @@ int ql_dynamic_quantize(const ql_tensor *input, const ql_tensor *double_quant_sc
   uint8_t *q = static_cast<uint8_t *>(result->data), *s = static_cast<uint8_t *>(scales->data);
   const void *gs = double_quant_scale->data;
   const int gsdt = double_quant_scale->dtype;
-  if (input->dtype == QL_F32) nvfp4_quantize_kernel<float><<<grid_for(nblocks), kThreadsF4, 0, st>>>(static_cast<const float *>(input->data), gs, gsdt, q, s, nblocks);
-  else if (input->dtype == QL_F16) nvfp4_quantize_kernel<__half><<<grid_for(nblocks), kThreadsF4, 0, st>>>(static_cast<const __half *>(input->data), gs, gsdt, q, s, nblocks);
-  else nvfp4_quantize_kernel<__nv_bfloat16><<<grid_for(nblocks), kThreadsF4, 0, st>>>(static_cast<const __nv_bfloat16 *>(input->data), gs, gsdt, q, s, nblocks);
+  if (input->dtype == QL_F32) nvfp4_quantize_kernel<float><<<grid_for(nblocks, 1), kThreadsF4, 0, st>>>(static_cast<const float *>(input->data), gs, gsdt, q, s, nblocks);
+  else if (input->dtype == QL_F16) nvfp4_quantize_kernel<__half><<<grid_for(nblocks, 1), kThreadsF4, 0, st>>>(static_cast<const __half *>(input->data), gs, gsdt, q, s, nblocks);
+  else nvfp4_quantize_kernel<__nv_bfloat16><<<grid_for(nblocks, 1), kThreadsF4, 0, st>>>(static_cast<const __nv_bfloat16 *>(input->data), gs, gsdt, q, s, nblocks);
   count_launches(1);
   QL_CUDA_TRY(cudaGetLastError());
   return QL_OK;
@@ -151,9 +169,9 @@ int ql_dequantize_nvfp4(const ql_tensor *data, const ql_tensor *scales, const ql
   const uint8_t *q = static_cast<const uint8_t *>(data->data), *s = static_cast<const uint8_t *>(scales->data);
   const void *gs = double_quant_scale->data;
   const int gsdt = double_quant_scale->dtype;
-  if (output->dtype == QL_F32) nvfp4_dequantize_kernel<float><<<grid_for(nblocks), kThreadsF4, 0, st>>>(q, s, gs, gsdt, static_cast<float *>(output->data), nblocks);
-  else if (output->dtype == QL_F16) nvfp4_dequantize_kernel<__half><<<grid_for(nblocks), kThreadsF4, 0, st>>>(q, s, gs, gsdt, static_cast<__half *>(output->data), nblocks);
-  else nvfp4_dequantize_kernel<__nv_bfloat16><<<grid_for(nblocks), kThreadsF4, 0, st>>>(q, s, gs, gsdt, static_cast<__nv_bfloat16 *>(output->data), nblocks);
+  if (output->dtype == QL_F32) nvfp4_dequantize_kernel<float><<<grid_for(nblocks, kUnrollF4), kThreadsF4, 0, st>>>(q, s, gs, gsdt, static_cast<float *>(output->data), nblocks);
+  else if (output->dtype == QL_F16) nvfp4_dequantize_kernel<__half><<<grid_for(nblocks, kUnrollF4), kThreadsF4, 0, st>>>(q, s, gs, gsdt, static_cast<__half *>(output->data), nblocks);
+  else nvfp4_dequantize_kernel<__nv_bfloat16><<<grid_for(nblocks, kUnrollF4), kThreadsF4, 0, st>>>(q, s, gs, gsdt, static_cast<__nv_bfloat16 *>(output->data), nblocks);
   count_launches(1);
   QL_CUDA_TRY(cudaGetLastError());
   return QL_OK;
