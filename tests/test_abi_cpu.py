@@ -107,3 +107,56 @@ def test_no_cpu_fallback():
     rc = _lib.lib().ql_quantize(_t(_lib.F32, [64], p(buf)), _t(_lib.F32, [], p(sc)), _t(_lib.I8, [64], p(out)), _lib.make_attrs(), None)
     assert rc in (_lib.ERR_NO_DEVICE, _lib.ERR_CUDA)
     assert bytes(out) == bytes(64)
+
+
+def _peer(world=2, rank=0, base=0x10000, with_all=True):
+    b = _lib.QlPeerBuffer()
+    for r in range(min(world, _lib.QL_MAX_PEERS)):
+        b.replica[r] = base + r * 0x100000
+    b.all = 0x9000000 if with_all else None
+    b.world, b.rank = world, rank
+    return b
+
+
+def test_peer_entry_points_validate_before_touching_a_device():
+    """Argument rules of the fused GEMM + collective path (no reference counterpart)."""
+    L = _lib.lib()
+    xq, wq = _t(_lib.F8E4M3, [256, 128]), _t(_lib.F8E4M3, [512, 128])
+    sx, sw = _t(_lib.F32, []), _t(_lib.F32, [])
+    ok = _peer()
+    assert "bad world / rank" in _err(L.ql_gemm_fp8_peer(xq, wq, sx, sw, _peer(world=9), _lib.BF16, 512, 0, _lib.PEER_STORE_ALL, None))
+    assert "unknown peer mode" in _err(L.ql_gemm_fp8_peer(xq, wq, sx, sw, ok, _lib.BF16, 512, 0, 7, None))
+    assert "smaller than N" in _err(L.ql_gemm_fp8_peer(xq, wq, sx, sw, ok, _lib.BF16, 256, 0, _lib.PEER_STORE_ALL, None))
+    assert "no address for this mode" in _err(L.ql_gemm_fp8_peer(xq, wq, sx, sw, _peer(with_all=False), _lib.BF16, 512, 0, _lib.PEER_ADD_ALL, None))
+    assert "offset % 8 == 0" in _err(L.ql_gemm_fp8_peer(xq, wq, sx, sw, ok, _lib.BF16, 512, 4, _lib.PEER_STORE_ALL, None))
+    wq_odd = _t(_lib.F8E4M3, [520, 128])
+    assert "N % 32 == 0" in _err(L.ql_gemm_fp8_peer(xq, wq_odd, sx, sw, ok, _lib.BF16, 1024, 0, _lib.PEER_ADD_ALL, None))
+    # owner blocks must be whole 128-row tiles
+    assert "multiple of 128 x world" in _err(L.ql_gemm_fp8_peer(_t(_lib.F8E4M3, [384, 128]), wq, sx, sw, _peer(world=2), _lib.BF16, 512, 0,
+                                                                 _lib.PEER_ADD_OWNER, None))
+    assert "replica 1 has no address" in _err(L.ql_peer_barrier(_missing_replica(), None))
+    assert "multiples of 16 bytes" in _err(L.ql_peer_broadcast(ok, 8, 64, None))
+    assert "must be bf16 or f16" in _err(L.ql_peer_reduce(ok, _lib.F32, 0, 64, None))
+    assert "no replication address" in _err(L.ql_peer_reduce(_peer(with_all=False), _lib.BF16, 0, 64, None))
+
+
+def _missing_replica():
+    b = _peer(world=2)
+    b.replica[1] = None
+    return b
+
+
+def test_nvfp4_entry_points_use_the_verifier_wording():
+    """tensorrt/lib/TensorRT/IR/Verification.cpp:1270-1290."""
+    L = _lib.lib()
+    x, gs = _t(_lib.F32, [4, 32]), _t(_lib.F32, [])
+    q, s = _t(_lib.F4E2M1, [4, 32]), _t(_lib.F8E4M3, [4, 2])
+    assert "currently only block size of 16 is supported!" in _err(L.ql_dynamic_quantize(x, gs, 1, 32, q, s, None))
+    assert "invalid axis! Axis can be either last or second last dimension of the input." in _err(
+        L.ql_dynamic_quantize(_t(_lib.F32, [2, 4, 32]), gs, 0, 16, _t(_lib.F4E2M1, [2, 4, 32]), _t(_lib.F8E4M3, [2, 4, 2]), None))
+    assert "shape(input)[axis] must be divisible by 16." in _err(
+        L.ql_dynamic_quantize(_t(_lib.F32, [4, 24]), gs, 1, 16, _t(_lib.F4E2M1, [4, 24]), _t(_lib.F8E4M3, [4, 1]), None))
+    assert "second last dimension are not built" in _err(L.ql_dynamic_quantize(_t(_lib.F32, [32, 32]), gs, 0, 16, q, s, None))
+    assert "one entry per block of 16" in _err(L.ql_dynamic_quantize(x, gs, 1, 16, q, _t(_lib.F8E4M3, [4, 4]), None))
+    assert "rank-0" in _err(L.ql_dynamic_quantize(x, _t(_lib.F32, [1]), 1, 16, q, s, None))
+    assert "data must be f4E2M1FN and scales f8E4M3FN" in _err(L.ql_dequantize_nvfp4(_t(_lib.I4, [4, 32]), s, gs, x, None))
