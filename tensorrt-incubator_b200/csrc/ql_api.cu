@@ -91,6 +91,9 @@ constexpr int kFusedWidenMaxRows = 256;
 int gemm16_device(int dtype, const void *X, const void *W, const float *sb, int sb_n, void *Y, int M, int N, int K,
                   cudaStream_t st);
 
+// ql_nvfp4.cu
+int launch_f4_block_dequantize(const ql_tensor *q, const ql_tensor *scale, ql_tensor *y, cudaStream_t st);
+
 // Above this many rows of X the weight-only layers leave the streaming kernel for the tcgen05 GEMM.
 constexpr int kWeightOnlyMaxRows = 64;
 
@@ -254,6 +257,15 @@ int ql_quantize(const ql_tensor *input, const ql_tensor *scale, ql_tensor *outpu
 
 int ql_dequantize(const ql_tensor *input, const ql_tensor *scale, ql_tensor *output, const ql_qdq_attrs *attrs,
                   void *stream) {
+  if (input && input->dtype == QL_F4E2M1) { // NVFP4 data: block scales along the last axis (ql_nvfp4.cu)
+    int rc;
+    if ((rc = check_tensor(output, "tensorrt.dequantize", "floating-point tensor")) != QL_OK) return rc;
+    if ((rc = check_tensor(scale, "tensorrt.dequantize", "scale")) != QL_OK) return rc;
+    if (!is_float_dtype(output->dtype) || !is_float_dtype(scale->dtype))
+      return set_error(QL_ERR_INVALID_ARGUMENT, "tensorrt.dequantize: f4E2M1FN dequantizes to f32, f16 or bf16 with scales of one of those types");
+    if (!same_shape(output, input)) return set_error(QL_ERR_INVALID_ARGUMENT, "tensorrt.dequantize: input and output shapes differ");
+    return launch_f4_block_dequantize(input, scale, output, (cudaStream_t)stream);
+  }
   int rc = check_qdq_common(output, scale, input, "tensorrt.dequantize");
   if (rc != QL_OK) return rc;
   QdqPlan plan;

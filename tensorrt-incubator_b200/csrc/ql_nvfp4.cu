@@ -90,6 +90,29 @@ nvfp4_dequantize_kernel(const uint8_t *__restrict__ q, const uint8_t *__restrict
   }
 }
 
+// tensorrt.dequantize of e2m1 data with floating-point block scales along the last axis (the second step of the
+// operator's documented use: the scales are themselves the result of dequantizing the e4m3 block scales).
+// One thread per 16 values; `block` (a multiple of 16) values share one scale.
+template <typename OutT>
+__global__ void __launch_bounds__(kThreadsF4)
+f4_block_dequantize_kernel(const uint8_t *__restrict__ q, const void *__restrict__ scale, int sdt, OutT *__restrict__ y, int64_t n16,
+                           int chunks_per_scale) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < n16; b += stride) {
+    const uint2 w = __ldcs(reinterpret_cast<const uint2 *>(q + b * 8));
+    const float s = load_scale(scale, sdt, b / chunks_per_scale);
+    const uint32_t ww[2] = {w.x, w.y};
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+      const float2 f = e2m1x2_to_f32x2((ww[i >> 3] >> (4 * (i & 7))) & 0xFFu);
+      v[i] = f.x * s;
+      v[i + 1] = f.y * s;
+    }
+    store_vec_f32<OutT, 16>(y + b * 16, v);
+  }
+}
+
 int64_t numel_of(const ql_tensor *t) {
   int64_t n = 1;
   for (int i = 0; i < t->rank; i++) n *= t->shape[i];
@@ -123,6 +146,31 @@ unsigned grid_for(int64_t nblocks, int per_thread) {
 }
 
 } // namespace
+
+// q: e2m1 [..., K]; scale: f32 | f16 | bf16 [..., K / block], block % 16 == 0; y: [..., K].  Called by ql_dequantize.
+int launch_f4_block_dequantize(const ql_tensor *q, const ql_tensor *scale, ql_tensor *y, cudaStream_t st) {
+  const char *op = "tensorrt.dequantize";
+  if (q->rank < 1 || scale->rank != q->rank)
+    return set_error(QL_ERR_UNSUPPORTED, "%s: f4E2M1FN input is dequantized with block scales of the input's rank", op);
+  for (int i = 0; i + 1 < q->rank; i++)
+    if (scale->shape[i] != q->shape[i]) return set_error(QL_ERR_UNSUPPORTED, "%s: f4E2M1FN blocks must run along the last axis", op);
+  const int64_t K = q->shape[q->rank - 1], nb = scale->shape[q->rank - 1];
+  if (nb <= 0 || K % nb != 0 || (K / nb) % 16 != 0)
+    return set_error(QL_ERR_UNSUPPORTED, "%s: f4E2M1FN block size must be a multiple of 16 (last axis %lld, %lld scales)", op, (long long)K, (long long)nb);
+  const int64_t n16 = numel_of(q) / 16;
+  if (n16 == 0) return QL_OK;
+  if (!aligned16(y->data) || (reinterpret_cast<uintptr_t>(q->data) & 7)) return set_error(QL_ERR_UNSUPPORTED, "%s: buffers must be 16-byte (data: 8-byte) aligned", op);
+  const int cps = (int)((K / nb) / 16);
+  const uint8_t *qp = static_cast<const uint8_t *>(q->data);
+  const unsigned grid = grid_for(n16, 1);
+  if (y->dtype == QL_F32) f4_block_dequantize_kernel<float><<<grid, kThreadsF4, 0, st>>>(qp, scale->data, scale->dtype, static_cast<float *>(y->data), n16, cps);
+  else if (y->dtype == QL_F16) f4_block_dequantize_kernel<__half><<<grid, kThreadsF4, 0, st>>>(qp, scale->data, scale->dtype, static_cast<__half *>(y->data), n16, cps);
+  else f4_block_dequantize_kernel<__nv_bfloat16><<<grid, kThreadsF4, 0, st>>>(qp, scale->data, scale->dtype, static_cast<__nv_bfloat16 *>(y->data), n16, cps);
+  count_launches(1);
+  QL_CUDA_TRY(cudaGetLastError());
+  return QL_OK;
+}
+
 } // namespace ql
 
 using namespace ql;

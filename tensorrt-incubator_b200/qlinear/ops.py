@@ -93,7 +93,14 @@ def quantize_to(input: torch.Tensor, scale: torch.Tensor, out, dim=None, *, fp8_
 
 
 def dequantize(input, scale, dtype: dt.dtype, dim=None, *, out=None) -> torch.Tensor:
-    """output = input * scale as `dtype` (float32, float16 or bfloat16)."""
+    """output = input * scale as `dtype` (float32, float16 or bfloat16).  A `Float4Tensor` (NVFP4 data) takes block
+    scales of its own rank along the last axis, as in the documented use of tensorrt.dynamic_quantize."""
+    if isinstance(input, Float4Tensor):
+        require_cuda(input, "input")
+        s = scale.to(input.device).contiguous()
+        y = out if out is not None else torch.empty(input.shape, dtype=dtype.torch, device=input.device)
+        _lib.check(_lib.lib().ql_dequantize(ql_view(input), ql_view(s), ql_view(y), _lib.make_attrs(None), current_stream(input.device)))
+        return y
     if dtype not in dt.QUANTIZABLE_DTYPES:
         check_qdq_args(input, torch.zeros(()), dtype, dim, False)
     s = _as_scale(scale, dtype)

@@ -62,3 +62,29 @@ def test_argument_rules():
         ql.dynamic_quantize(torch.ones((2, 4, 32), device="cuda"), axis=0)
     with pytest.raises(ql.QlError, match="second last dimension are not built"):
         ql.dynamic_quantize(torch.ones((32, 32), device="cuda"), axis=0)
+
+
+def test_reference_program_as_written(kat):
+    """The reference's test program step by step: dynamic_quantize, tensorrt.dequantize of the e4m3 block scales by
+    the per-tensor scale, tensorrt.dequantize of the e2m1 data by those scales
+    (compiler/test/python/IntegrationTests/test_tensorrt_fp4.py:20-24)."""
+    case = kat["nvfp4_dynamic_quantize"]
+    x = torch.tensor(case["input"], dtype=torch.float32, device="cuda")
+    data, scales = ql.dynamic_quantize(x, 1.0, axis=1)
+    block_scales = ql.dequantize(scales, 1.0, ql.float32)
+    assert tuple(block_scales.shape) == (2, 2)
+    y = ql.dequantize(data, block_scales, ql.float32)
+    assert np.array_equal(y.cpu().numpy(), np.array(case["expected"], dtype=np.float32))
+
+
+@pytest.mark.parametrize("out", [ql.float32, ql.float16, ql.bfloat16])
+@pytest.mark.parametrize("block", [16, 32, 64])
+def test_f4_dequantize_with_float_block_scales(out, block):
+    x = randn((33, 192), torch.float32, 950, std=2.0)
+    data, _ = ql.dynamic_quantize(x, 1.0)
+    s = (torch.rand((33, 192 // block), generator=torch.Generator().manual_seed(3)) + 0.25).to(out.torch).cuda()
+    y = ql.dequantize(data, s, out)
+    want = (data.unpack() * s.float().repeat_interleave(block, dim=1)).to(out.torch)   # one f32 multiply, one rounding
+    assert torch.equal(y, want)
+    with pytest.raises(ql.QlError, match="multiple of 16"):
+        ql.dequantize(data, torch.ones((33, 24), device="cuda"), ql.float32)
