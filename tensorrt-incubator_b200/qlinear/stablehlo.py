@@ -10,7 +10,8 @@ The reference recognises quantize / dequantize in three spellings and this modul
   (mlir-tensorrt/compiler/lib/Dialect/StablehloExt/Transforms/StablehloRaiseQDQ.cpp:138-265, 348-418);
 * `stablehlo.composite "tensorrt.pt_q|pc_q|block_q|pt_dq|pc_dq|block_dq"` with `composite_attributes =
   {axis, scale}` (what that pass produces, StablehloRaiseQDQ.cpp:270-345);
-* `stablehlo.custom_call @tensorrt.quantize / @tensorrt.dequantize` with `mode` and `axis` attributes
+* `stablehlo.custom_call @tensorrt.quantize / @tensorrt.dequantize` with `mode` and `axis` attributes, and
+  `@tensorrt.dynamic_quantize` (two results: NVFP4 data and block scales)
   (what the JAX plug-in emits, integrations/PJRT/python/mlir_tensorrt_jax/mtrt_ops/quantize.py:134; examples
   in compiler/test/Passes/0_Frontend/StablehloToTensorRT/stablehlo-to-tensorrt-trt10.mlir:401-440).
 
@@ -32,9 +33,10 @@ from . import _lib
 from . import dtypes as dt
 from . import linear as _linear
 from . import ops
-from .tensor import Int4Tensor, current_stream, empty_quantized, ql_view
+from .tensor import Float4Tensor, Int4Tensor, current_stream, empty_quantized, ql_view
 
-_ELEM = {"f32": dt.float32, "f16": dt.float16, "bf16": dt.bfloat16, "i8": dt.int8, "i4": dt.int4, "f8E4M3FN": dt.float8}
+_ELEM = {"f32": dt.float32, "f16": dt.float16, "bf16": dt.bfloat16, "i8": dt.int8, "i4": dt.int4, "f8E4M3FN": dt.float8,
+         "f4E2M1FN": dt.float4}
 _BOUNDS = {dt.int8: (-128.0, 127.0), dt.int4: (-8.0, 7.0), dt.float8: (-448.0, 448.0)}
 
 
@@ -215,6 +217,19 @@ class Program:
                     result_slots.append(realise(vals[nm]))
                     result_types.append(TensorType.parse(ty))
                 continue
+            dq = re.match(r"(%[\w.-]+):2\s*=\s*stablehlo\.custom_call\s+@tensorrt\.dynamic_quantize\((%[\w.#-]+),\s*(%[\w.#-]+)\)\s*\{(.*)\}\s*:"
+                          r"\s*\(.*\)\s*->\s*\((.*)\)$", line)
+            if dq:
+                # NVFP4: two results, %name#0 (e2m1 data) and %name#1 (e4m3 block scales)
+                name2, x, gs, attrs = dq.group(1), vals[dq.group(2)], vals[dq.group(3)], dq.group(4)
+                tys = [TensorType.parse(t) for t in _split_top(dq.group(5))]
+                axis = int(re.search(r"axis\s*=\s*(-?\d+)", attrs).group(1))
+                bm = re.search(r"block_size\s*=\s*(\d+)", attrs)
+                data, scales = Val("real", tys[0], slot=new_slot()), Val("real", tys[1], slot=new_slot())
+                steps.append(Step("dynamic_quantize", data.slot, (realise(x), realise(gs)),
+                                  {"axis": axis, "block_size": int(bm.group(1)) if bm else 16, "scales_slot": scales.slot}))
+                vals[name2 + "#0"], vals[name2 + "#1"] = data, scales
+                continue
             lm = re.match(r"(%[\w.#-]+)\s*=\s*(.*)", line)
             if not lm:
                 raise UnsupportedProgram(f"cannot read: {line[:80]}")
@@ -347,9 +362,12 @@ class Program:
                 x = x.contiguous()
                 out = empty_quantized(x.shape, st.attrs["dtype"], x.device)
                 slots[st.out] = ops.quantize_to(x, s.contiguous(), out, st.attrs["axis"], fp8_mode=st.attrs["fp8_mode"])
+            elif st.op == "dynamic_quantize":
+                x, gs = ins
+                slots[st.out], slots[st.attrs["scales_slot"]] = ops.dynamic_quantize(x, gs, st.attrs["axis"], st.attrs["block_size"])
             elif st.op == "dequantize":
                 q, s = ins
-                q = q if isinstance(q, Int4Tensor) else q.contiguous()
+                q = q if isinstance(q, (Int4Tensor, Float4Tensor)) else q.contiguous()
                 y = torch.empty(tuple(q.shape), dtype=st.attrs["dtype"].torch, device=q.device)
                 _lib.check(_lib.lib().ql_dequantize(ql_view(q), ql_view(s.contiguous()), ql_view(y), _lib.make_attrs(st.attrs["axis"]),
                                                     current_stream(y.device)))

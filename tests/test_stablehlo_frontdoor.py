@@ -93,6 +93,16 @@ func.func @main(%arg0: tensor<32x20xf32>, %scale: tensor<32xf32>) -> tensor<32x2
 """
 
 
+NVFP4 = """
+func.func public @nvfp4_round_trip(%arg0: tensor<2x32xf32>, %scale: tensor<f32>) -> tensor<2x32xf32> {
+  %0:2 = stablehlo.custom_call @tensorrt.dynamic_quantize(%arg0, %scale) {api_version = 2 : i32, axis = 1 : i32, block_size = 16 : i32, operand_layouts = [dense<[1, 0]> : tensor<2xindex>, dense<> : tensor<0xindex>], result_layouts = [dense<[1, 0]> : tensor<2xindex>, dense<[1, 0]> : tensor<2xindex>]} : (tensor<2x32xf32>, tensor<f32>) -> (tensor<2x32xf4E2M1FN>, tensor<2x2xf8E4M3FN>)
+  %1 = stablehlo.custom_call @tensorrt.dequantize(%0#1, %scale) {api_version = 2 : i32, mode = "tensorrt.pt_dq"} : (tensor<2x2xf8E4M3FN>, tensor<f32>) -> tensor<2x2xf32>
+  %2 = stablehlo.custom_call @tensorrt.dequantize(%0#0, %1) {api_version = 2 : i32, mode = "tensorrt.block_dq"} : (tensor<2x32xf4E2M1FN>, tensor<2x2xf32>) -> tensor<2x32xf32>
+  return %2 : tensor<2x32xf32>
+}
+"""
+
+
 def _linear_program(M, N, K, act="bf16"):
     """Tripy's quantized Linear as StableHLO: x @ transpose(dequantize(Wq)) with per-channel int8 weights."""
     return f"""
@@ -148,6 +158,16 @@ def test_matches_custom_call_with_runtime_scale():
     p = Program.from_text(CUSTOM_CALL)
     st, = p.steps
     assert st.attrs["mode"] == "pc" and st.attrs["axis"] == 0 and st.ins == (0, 1) and not p.constants
+
+
+def test_matches_nvfp4_dynamic_quantize_with_two_results():
+    """Spelling of compiler/test/Passes/0_Frontend/StablehloToTensorRT/stablehlo-to-tensorrt-trt10.mlir:477-480."""
+    p = Program.from_text(NVFP4)
+    assert [s.op for s in p.steps] == ["dynamic_quantize", "dequantize", "dequantize"]
+    dq = p.steps[0]
+    assert dq.attrs["axis"] == 1 and dq.attrs["block_size"] == 16 and dq.ins == (0, 1)
+    assert p.steps[1].ins[0] == dq.attrs["scales_slot"] and p.steps[2].ins == (dq.out, p.steps[1].out)
+    assert p.steps[2].attrs["mode"] == "block"
 
 
 def test_linear_fuses_the_dequantize_into_the_weight_only_kernel():
@@ -258,3 +278,14 @@ def test_runs_quantized_linear(M):
     want = orc.linear_w8(_np(x), orc.BF16, _np(wq), _np(s), orc.BF16, orc.BF16)
     assert tuple(y.shape) == (M, N)
     assert_close_rel(float_values(y), orc.to_f32(want, orc.BF16), 1e-2, "linear through the front door")
+
+
+@pytest.mark.gpu
+def test_runs_the_nvfp4_program_of_the_reference(kat):
+    """The reference's NVFP4 execution test as a StableHLO program: same input, same expected output
+    (compiler/test/python/IntegrationTests/test_tensorrt_fp4.py:10-26, 74-82)."""
+    case = kat["nvfp4_dynamic_quantize"]
+    x = torch.tensor(case["input"], dtype=torch.float32, device="cuda")
+    gs = torch.tensor(case["double_quant_scale"], dtype=torch.float32, device="cuda")
+    y = Program.from_text(NVFP4)(x, gs)
+    assert np.array_equal(y.cpu().numpy(), np.array(case["expected"], dtype=np.float32))
