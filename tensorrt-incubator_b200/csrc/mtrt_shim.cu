@@ -136,6 +136,7 @@ int dtype_of(const std::string &s) {
   if (s == "i8") return QL_I8;
   if (s == "i4") return QL_I4;
   if (s == "f8" || s == "f8E4M3FN") return QL_F8E4M3;
+  if (s == "f4" || s == "f4E2M1FN") return QL_F4E2M1;
   return -1;
 }
 
@@ -205,6 +206,25 @@ void launch_library_kernel(const OpSpec &s, CUstream stream, void **args) {
     ql_tensor sx{ptr_arg(args, 2), QL_F32, nsx == 1 ? 0 : 1, {nsx}}, sw{ptr_arg(args, 3), QL_F32, nsw == 1 ? 0 : 1, {nsw}};
     ql_tensor y{ptr_arg(args, 4), dtype_of(get(s, "out", "bf16")), 2, {M, N}};
     rc = s.op == "gemm_fp8" ? ql_gemm_fp8(&x, &w, &sx, &sw, &y, stream) : ql_gemm_i8(&x, &w, &sx, &sw, &y, stream);
+  } else if (s.op == "dynamic_quantize") {
+    // args: input, double_quant_scale (rank 0), result (f4), scales (f8)
+    ql_tensor in{}, gs{}, out{}, sc{};
+    in.dtype = dtype_of(get(s, "in", "f32"));
+    gs.dtype = dtype_of(get(s, "scale", "f32"));
+    out.dtype = QL_F4E2M1;
+    sc.dtype = QL_F8E4M3;
+    if (!shape_of(get(s, "shape"), &in) || in.rank < 1) return fail("bad shape in kernel spec");
+    const int axis = atoi(get(s, "axis", "-1").c_str());
+    const int ax = axis < 0 ? in.rank + axis : axis;
+    out.rank = sc.rank = in.rank;
+    memcpy(out.shape, in.shape, sizeof(in.shape));
+    memcpy(sc.shape, in.shape, sizeof(in.shape));
+    if (ax >= 0 && ax < in.rank) sc.shape[ax] = in.shape[ax] / 16;
+    in.data = ptr_arg(args, 0);
+    gs.data = ptr_arg(args, 1);
+    out.data = ptr_arg(args, 2);
+    sc.data = ptr_arg(args, 3);
+    rc = ql_dynamic_quantize(&in, &gs, ax, atoi(get(s, "block_size", "16").c_str()), &out, &sc, stream);
   } else {
     return fail("unknown library kernel '%s'", s.op.c_str());
   }

@@ -177,3 +177,33 @@ def test_library_kernels_through_the_launch_abi(rt):
     assert torch.equal(wq, ql.quantize(w, ws, ql.int8, 0))
     assert torch.equal(y, ql.linear_w8a16(xa, wq, ws))
     rt.mtrt_cuda_module_unload(mod)
+
+
+@pytest.mark.gpu
+def test_nvfp4_through_the_launch_abi(rt):
+    """tensorrt.dynamic_quantize and the block dequantize of its data as library kernels named by their specs."""
+    mod = rt.mtrt_cuda_module_load_from_ptx(b"", 0)
+    g = torch.Generator(device="cpu").manual_seed(11)
+    x = (torch.randn((8, 64), generator=g) * 3).cuda()
+    gs = torch.ones((), device="cuda")
+    data = torch.empty(8 * 64 // 2, dtype=torch.uint8, device="cuda")
+    scales = torch.empty((8, 4), dtype=torch.float8_e4m3fn, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    name = b"ql:dynamic_quantize;in=f32;shape=8x64;axis=1"
+    arr, keep = _args(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(gs.data_ptr()), ctypes.c_void_p(data.data_ptr()), ctypes.c_void_p(scales.data_ptr()))
+    rt.mtrt_cuda_launch_kernel(rt.mtrt_cuda_module_get_function(mod, name, len(name)), 1, 1, 1, 1, 1, 1, 0, stream, arr)
+    torch.cuda.synchronize()
+    assert rt.mtrt_cuda_last_error() == b""
+    want_q, want_s = orc.dynamic_quantize_nvfp4(x.cpu().numpy(), orc.F32, 1.0)
+    assert np.array_equal(data.cpu().numpy().reshape(want_q.shape), want_q)
+    assert np.array_equal(scales.view(torch.uint8).cpu().numpy(), want_s)
+    # second step: data * f32 block scales
+    block_scales = scales.float().contiguous()
+    y = torch.empty((8, 64), device="cuda")
+    name = b"ql:dequantize;in=f4;out=f32;scale=f32;shape=8x64;scale_shape=8x4"
+    arr, keep = _args(ctypes.c_void_p(data.data_ptr()), ctypes.c_void_p(block_scales.data_ptr()), ctypes.c_void_p(y.data_ptr()))
+    rt.mtrt_cuda_launch_kernel(rt.mtrt_cuda_module_get_function(mod, name, len(name)), 1, 1, 1, 1, 1, 1, 0, stream, arr)
+    torch.cuda.synchronize()
+    assert rt.mtrt_cuda_last_error() == b""
+    assert np.array_equal(y.cpu().numpy(), orc.dequantize_nvfp4(want_q, want_s, 1.0, orc.F32))
+    rt.mtrt_cuda_module_unload(mod)
