@@ -140,8 +140,10 @@ QL_API int ql_linear_w4a16(const ql_tensor *x, const ql_tensor *w, const ql_tens
                            ql_tensor *y, void *stream);
 
 /* Quantized GEMMs on the tensor cores, Y[M,N] = (Xq[M,K] . Wq[N,K]^T) * sx * sw, f32 (fp8) or
- * s32 (int8) accumulation, scales applied in the epilogue, Y bf16 or f16.
- * sx: f32 scalar or [M] (per token); sw: f32 scalar or [N] (per output channel). */
+ * s32 (int8) accumulation, scales applied in the epilogue, Y bf16, f16 or f32.
+ * sx: f32 scalar or [M] (per token); sw: f32 scalar or [N] (per output channel).
+ * Shapes the tensor-core kernels cannot take (K not a multiple of 16 bytes, operands not 16-byte aligned) run on
+ * a general CUDA-core kernel with the same arithmetic. */
 QL_API int ql_gemm_fp8(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx,
                        const ql_tensor *sw, ql_tensor *y, void *stream);
 QL_API int ql_gemm_i8(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx,
@@ -180,6 +182,9 @@ QL_API int ql_gemm_fp8_peer(const ql_tensor *xq, const ql_tensor *wq, const ql_t
                             const ql_peer_buffer *dest, int32_t y_dtype, int64_t ldy, int64_t offset, int peer_mode,
                             void *stream);
 QL_API int ql_peer_barrier(const ql_peer_buffer *flags, void *stream);
+/* Diagnostics: how many SM clock cycles ql_peer_barrier waits for a peer before it gives up (0 restores the
+ * default of 2^34, about ten seconds).  Process-wide; applies to barriers launched after the call. */
+QL_API int ql_set_peer_wait_limit(int64_t cycles);
 /* In-switch all-reduce of bytes [offset, offset + bytes) (bf16 or f16 elements, 16-byte units): the NVSwitch adds
  * that range of all replicas in f32 and the sum replaces it in every replica.  Ranks call it on disjoint ranges
  * between two ql_peer_barrier calls; with a GEMM that wrote its partial result into the local replica this is a
@@ -190,6 +195,20 @@ QL_API int ql_peer_broadcast(const ql_peer_buffer *buf, int64_t offset, int64_t 
 /* 16-bit GEMM Y = (X . W^T) * sw, X and W both bf16 or both f16 ([M,K], [N,K]); sw may be null. */
 QL_API int ql_gemm_16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *sw, ql_tensor *y,
                       void *stream);
+
+/* The forward of tp.Linear (tripy/nvtripy/frontend/module/linear.py:127-151) once its quantize / dequantize pairs are
+ * folded into scales: Y[M,N] = (X[M,K] . W[N,K]^T) * sx * sw + bias[n].  X and W share one type: f32, f16, bf16
+ * (then Y has that type, as tp.matmul requires: frontend/ops/matmul.py:31-34), e4m3 or int8 (Y f32, f16 or bf16).
+ * sx, sw: null, f32 scalar, or one value per row of X / of W.  bias: null or [N] of any float type, added in f32
+ * before the single rounding to Y's type.  16-bit and 8-bit operands with 16-byte aligned rows run on the
+ * tensor cores; everything else (f32 operands, K = 4, unaligned views) on a general CUDA-core kernel. */
+QL_API int ql_linear(const ql_tensor *x, const ql_tensor *w, const ql_tensor *sx, const ql_tensor *sw,
+                     const ql_tensor *bias, ql_tensor *y, void *stream);
+/* C = A @ B: tensorrt.matrix_multiply with both operands kNONE (TensorRTOps.td:1986-2080), what tp.matmul emits
+ * (tripy/nvtripy/frontend/ops/matmul.py:29-108).  A [..., M, K], B [..., K, N], C [..., M, N]: equal ranks >= 2, one
+ * float type, f32 accumulation.  The leading dimensions of an operand are all equal to C's or all 1 (broadcast);
+ * 1-D operands and mixed broadcasts are reshaped by the caller (the Python layer does). */
+QL_API int ql_matmul(const ql_tensor *a, const ql_tensor *b, ql_tensor *c, void *stream);
 
 /* Row kernels of the quantized MLP block (RMSNorm / SwiGLU are not reference operators; the quantize
  * step inside them is tensorrt.quantize with one scale per row, scale = max|row| / 448):

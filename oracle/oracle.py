@@ -51,6 +51,7 @@ def lib():
         L.orc_scale_from_amax.argtypes = [vp, i64, f, vp, ci]
         L.orc_linear_w8.argtypes = [vp, ci, vp, vp, ci, i64, i64, i64, vp, ci, ci]
         L.orc_linear_w4.argtypes = [vp, ci, vp, vp, ci, i64, i64, i64, i64, vp, ci, ci]
+        L.orc_matmul.argtypes = [vp, vp, vp, ci, i64, i64, i64, i64, i64, i64, i64, i64, i64, i64, vp, ci]
         L.orc_gemm_fp8.argtypes = [vp, vp, vp, i64, vp, i64, i64, i64, i64, vp, ci, ci]
         L.orc_gemm_i8.argtypes = [vp, vp, vp, i64, vp, i64, i64, i64, i64, vp, ci]
         L.orc_rmsnorm_quant_fp8.argtypes = [vp, ci, i64, i64, f, vp, vp]
@@ -220,6 +221,59 @@ def linear_w4(X, x_code, Wp, scale, s_code, y_code, block, acc64=True):
     lib().orc_linear_w4(_ptr(np.ascontiguousarray(X)), x_code, _ptr(np.ascontiguousarray(Wp)),
                         _ptr(np.ascontiguousarray(scale)), s_code, M, N, K, block, _ptr(Y), y_code, int(acc64))
     return Y
+
+
+def matmul(a, b, code, acc64=False):
+    """a @ b with numpy's rank rules, operands and result of the float type `code` (bit patterns for 16-bit types)."""
+    a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
+    va, vb = a.ndim == 1, b.ndim == 1
+    a2 = a[None, :] if va else a
+    b2 = b[:, None] if vb else b
+    lead = np.broadcast_shapes(a2.shape[:-2], b2.shape[:-2])
+    a2 = np.ascontiguousarray(np.broadcast_to(a2, lead + a2.shape[-2:]))
+    b2 = np.ascontiguousarray(np.broadcast_to(b2, lead + b2.shape[-2:]))
+    M, K = a2.shape[-2:]
+    N = b2.shape[-1]
+    batch = int(np.prod(lead)) if lead else 1
+    c = np.zeros(lead + (M, N), dtype=_NP_OF[code])
+    lib().orc_matmul(_ptr(a2), _ptr(b2), None, code, batch, M, N, K, K, 1, N, 1, M * K, K * N, _ptr(c), int(acc64))
+    if va:
+        c = c.reshape(c.shape[:-2] + (N,))
+    if vb:
+        c = c.reshape(c.shape[:-1])
+    return c
+
+
+def linear_float(x, w, bias, code, acc64=False):
+    """x @ transpose(w) (+ bias): x [M,K], w [N,K], bias [N] or None, all of the float type `code`."""
+    x, w = np.ascontiguousarray(x), np.ascontiguousarray(w)
+    M, K = x.shape
+    N = w.shape[0]
+    y = np.zeros((M, N), dtype=_NP_OF[code])
+    bp = _ptr(np.ascontiguousarray(bias)) if bias is not None else None
+    lib().orc_matmul(_ptr(x), _ptr(w), bp, code, 1, M, N, K, K, 1, 1, K, 0, 0, _ptr(y), int(acc64))
+    return y
+
+
+_Q_MODE_OF_RANK = {0: PER_TENSOR, 1: PER_CHANNEL, 2: BLOCK}
+
+
+def linear_module(x, weight, bias, code, quant_code=None, weight_quant_dim=None, weight_scale=None, input_scale=None, acc64=False):
+    """The forward of tp.Linear, op by op (tripy/nvtripy/frontend/module/linear.py:127-151): an optional
+    quantize -> dequantize of the input (per tensor), quantize -> dequantize of the weight (mode from
+    weight_quant_dim and the scale's rank), x @ transpose(weight), + bias.  Everything in the float type `code`."""
+    if quant_code is not None:
+        if input_scale is not None:
+            if weight_quant_dim == 1:
+                raise ValueError("Unsupported quantization parameters for Linear module.")
+            s = from_f32(np.asarray(input_scale, dtype=np.float32).reshape(()), code)
+            q = quantize(x, code, s, code, quant_code)
+            x = dequantize(q, quant_code, s, code, code, x.shape)
+        ws = np.asarray(weight_scale)
+        mode = _Q_MODE_OF_RANK[ws.ndim]
+        q = quantize(weight, code, ws, code, quant_code, mode, weight_quant_dim)
+        weight = dequantize(q, quant_code, ws, code, code, weight.shape, mode, weight_quant_dim)
+    return linear_float(x, weight, bias, code, acc64)
 
 
 def gemm_fp8(Xq, Wq, sx, sw, y_code=BF16, acc64=True):

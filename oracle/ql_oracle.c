@@ -330,6 +330,36 @@ int orc_linear_w4(const void *X, int x_dtype, const uint8_t *Wp, const void *sca
   return 0;
 }
 
+/* C[b] = A[b] @ B[b] for operands of one float type: tensorrt.matrix_multiply with both operands kNONE
+ * (tensorrt/include/mlir-tensorrt-dialect/TensorRT/IR/TensorRTOps.td:1986-2080), which is what tp.matmul emits
+ * (tripy/nvtripy/frontend/ops/matmul.py:29-108).  Strides are in elements, so that x @ transpose(W)
+ * (tripy/nvtripy/frontend/module/linear.py:148) is the same loop with b_k = 1, b_n = K; a batch stride of 0
+ * broadcasts an operand.  f32 sums in k order (double when acc64), one rounding to the result type; `bias`
+ * (same type, one value per column, may be null) is then added and the sum rounded again, as the reference's
+ * separate add does (linear.py:149-150). */
+int orc_matmul(const void *A, const void *B, const void *bias, int dtype, int64_t batch, int64_t M, int64_t N, int64_t K,
+               int64_t a_m, int64_t a_k, int64_t b_k, int64_t b_n, int64_t a_batch, int64_t b_batch, void *C, int acc64) {
+#pragma omp parallel for schedule(static) collapse(2)
+  for (int64_t b = 0; b < batch; b++) {
+    for (int64_t m = 0; m < M; m++) {
+      for (int64_t n = 0; n < N; n++) {
+        double acc = 0.0;
+        float accf = 0.0f;
+        for (int64_t k = 0; k < K; k++) {
+          float av = load_as_f32(A, dtype, b * a_batch + m * a_m + k * a_k);
+          float bv = load_as_f32(B, dtype, b * b_batch + k * b_k + n * b_n);
+          if (acc64) acc += (double)av * (double)bv;
+          else accf += av * bv;
+        }
+        float v = round_to(acc64 ? (float)acc : accf, dtype);
+        if (bias) v = v + load_as_f32(bias, dtype, n);
+        store_from_f32(C, dtype, (b * M + m) * N + n, v);
+      }
+    }
+  }
+  return 0;
+}
+
 /* Y[M,N] = (Xq[M,K] . Wq[N,K]^T) * sx[m or 0] * sw[n or 0]; e4m3 operands, f32 scales.
  * sx_n / sw_n give the scale counts (1 = per-tensor, M / N = per-row / per-channel). */
 int orc_gemm_fp8(const uint8_t *Xq, const uint8_t *Wq, const float *sx, int64_t sx_n,

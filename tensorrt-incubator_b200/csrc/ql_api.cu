@@ -259,6 +259,7 @@ int ql_dequantize(const ql_tensor *input, const ql_tensor *scale, ql_tensor *out
                   void *stream) {
   if (input && input->dtype == QL_F4E2M1) { // NVFP4 data: block scales along the last axis (ql_nvfp4.cu)
     int rc;
+    if ((rc = check_tensor(input, "tensorrt.dequantize", "quantized tensor")) != QL_OK) return rc;
     if ((rc = check_tensor(output, "tensorrt.dequantize", "floating-point tensor")) != QL_OK) return rc;
     if ((rc = check_tensor(scale, "tensorrt.dequantize", "scale")) != QL_OK) return rc;
     if (!is_float_dtype(output->dtype) || !is_float_dtype(scale->dtype))

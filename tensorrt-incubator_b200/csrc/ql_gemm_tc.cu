@@ -23,9 +23,31 @@
 #include "ql_tc_common.cuh"
 
 namespace ql {
+// ql_gemm_simt.cu
+int launch_gemm_simt(int dtype, const void *A, const void *B, const float *sa, int sa_n, const float *sb, int sb_n, const void *bias,
+                     int bias_dtype, void *Y, int y_dtype, int batch, int M, int N, int K, int64_t a_m, int64_t a_k, int64_t b_k,
+                     int64_t b_n, int64_t ldy, int64_t a_batch, int64_t b_batch, int64_t y_batch, cudaStream_t st);
 namespace {
 
 constexpr int STAGES = 4;
+
+// Tuning switches from the environment, read once per process (not on every launch).
+struct Tuning {
+  bool one_cta, two_kernels, not_cooperative;
+  int group_m;
+};
+const Tuning &tuning() {
+  static const Tuning t = [] {
+    Tuning v;
+    v.one_cta = getenv("QL_GEMM_ONE_CTA") != nullptr;
+    v.two_kernels = getenv("QL_W8_TWO_KERNELS") != nullptr;
+    v.not_cooperative = getenv("QL_W8_NOT_COOPERATIVE") != nullptr;
+    const char *e = getenv("QL_GEMM_GROUP_M");
+    v.group_m = e ? atoi(e) : 0;
+    return v;
+  }();
+  return t;
+}
 constexpr int A_STAGE_BYTES = BM * BK_BYTES;
 constexpr int kGemmThreads = 192;
 
@@ -35,6 +57,8 @@ struct GemmArgs {
   const float *sa; // null = 1, else one value (sa_n == 1) or one per row of A
   const void *sb;  // null = 1, else one value (sb_n == 1) or one per row of B, of type sb_dtype
   int sb_dtype;
+  const void *bias; // null, or one value per column of Y (type bias_dtype), added after the scales
+  int bias_dtype;
   int sa_n, sb_n;
   int M, N;
   int num_kb;      // K blocks of 128 bytes (the last may be partial: TMA fills zeros)
@@ -174,25 +198,40 @@ __device__ __forceinline__ void emit_chunk(const GemmArgs &args, OutT *Y, bool v
     float acc = (KIND == KIND_I8) ? (float)(int)r[j] : __uint_as_float(r[j]);
     v[j] = acc * s[j];
   }
-  if (peer) {
-    uint8_t *p = stage + lane * kPeerRowBytes + (c & 1) * 64;
+  if (args.bias) { // the same address in every lane: one broadcast load per column
 #pragma unroll
-    for (int j = 0; j < 32; j += 8)
-      *reinterpret_cast<uint4 *>(p + j * 2) = make_uint4(pack2<OutT>(v[j], v[j + 1]), pack2<OutT>(v[j + 2], v[j + 3]),
-                                                         pack2<OutT>(v[j + 4], v[j + 5]), pack2<OutT>(v[j + 6], v[j + 7]));
-    if ((c & 1) || last) peer_flush<OutT>(stage, lane, Y, args, m - lane, n - (c & 1) * 32, (c & 1) ? 64 : 32);
-    return;
+    for (int j = 0; j < 32; j++) v[j] += (n + j < args.N) ? load_scale(args.bias, args.bias_dtype, n + j) : 0.f;
   }
-  OutT *row = Y + (size_t)m * (size_t)args.ldy + n;
-  if (vec_ok && n + 32 <= args.N) {
+  if constexpr (sizeof(OutT) == 4) {
+    // f32 result (never a peer mode): 128 bytes per lane and chunk
+    float *row = reinterpret_cast<float *>(Y) + (size_t)m * (size_t)args.ldy + n;
+    if (vec_ok && n + 32 <= args.N) {
 #pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-      uint4 o = make_uint4(pack2<OutT>(v[j], v[j + 1]), pack2<OutT>(v[j + 2], v[j + 3]), pack2<OutT>(v[j + 4], v[j + 5]),
-                           pack2<OutT>(v[j + 6], v[j + 7]));
-      __stcs(reinterpret_cast<uint4 *>(row + j), o); // written once, never re-read here: keep it out of L2's way
+      for (int j = 0; j < 32; j += 4) __stcs(reinterpret_cast<float4 *>(row + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
+    } else {
+      for (int j = 0; j < 32 && n + j < args.N; j++) row[j] = v[j];
     }
   } else {
-    for (int j = 0; j < 32 && n + j < args.N; j++) row[j] = FloatIO<OutT>::from_f32(v[j]);
+    if (peer) {
+      uint8_t *p = stage + lane * kPeerRowBytes + (c & 1) * 64;
+#pragma unroll
+      for (int j = 0; j < 32; j += 8)
+        *reinterpret_cast<uint4 *>(p + j * 2) = make_uint4(pack2<OutT>(v[j], v[j + 1]), pack2<OutT>(v[j + 2], v[j + 3]),
+                                                           pack2<OutT>(v[j + 4], v[j + 5]), pack2<OutT>(v[j + 6], v[j + 7]));
+      if ((c & 1) || last) peer_flush<OutT>(stage, lane, Y, args, m - lane, n - (c & 1) * 32, (c & 1) ? 64 : 32);
+      return;
+    }
+    OutT *row = Y + (size_t)m * (size_t)args.ldy + n;
+    if (vec_ok && n + 32 <= args.N) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 o = make_uint4(pack2<OutT>(v[j], v[j + 1]), pack2<OutT>(v[j + 2], v[j + 3]), pack2<OutT>(v[j + 4], v[j + 5]),
+                             pack2<OutT>(v[j + 6], v[j + 7]));
+        __stcs(reinterpret_cast<uint4 *>(row + j), o); // written once, never re-read here: keep it out of L2's way
+      }
+    } else {
+      for (int j = 0; j < 32 && n + j < args.N; j++) row[j] = FloatIO<OutT>::from_f32(v[j]);
+    }
   }
 }
 
@@ -320,7 +359,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int quad = warp & 3; // tensor-memory lanes [32*quad, 32*quad+32) belong to this warp
     OutT *Y = static_cast<OutT *>(args.Y);
     uint8_t *stage = smem + L::kPeerStage + quad * kPeerStageWarp;
-    const bool vec_ok = (args.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
+    const bool vec_ok = (args.ldy % (16 / (int)sizeof(OutT)) == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
     int it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, it++) {
@@ -408,6 +447,10 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
   asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(x), "r"(y)
                : "memory");
+}
+// A role that gave up tells the pair's other CTA, whose roles would otherwise each run into their own limit.
+__device__ __forceinline__ void signal_partner_abort(uint32_t abort_addr, uint32_t rank) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(map_to_cta(abort_addr, rank ^ 1u)), "r"(1u) : "memory");
 }
 __device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
@@ -565,7 +608,20 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           if (++stage == STAGES2) { stage = 0; phase ^= 1; }
         }
       }
-      (void)issued;
+      if (!ok) {
+        signal_partner_abort(smem_u32((const void *)abort_flag), rank);
+        if (rank == 0) {
+          // Both CTAs' loads complete on the leader's barriers: let the ones still in flight land before either
+          // CTA's shared memory goes away (the partner cannot leave before the cluster barrier at the end).
+          const long long pending = issued < STAGES2 ? issued : STAGES2;
+          for (long long i = 0; i < pending; i++) {
+            stage = (stage == 0) ? STAGES2 - 1 : stage - 1;
+            if (stage == STAGES2 - 1) phase ^= 1;
+            const long long t0 = clock64();
+            while (!mbar_try_wait(full_bar(stage), phase) && clock64() - t0 < kWaitLimitCycles) {}
+          }
+        }
+      }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader only)
@@ -598,6 +654,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           tc_commit_pair(map_to_cta(tfull_bar(buf), 1));
         }
       }
+      if (!ok) signal_partner_abort(smem_u32((const void *)abort_flag), rank);
       tc_commit_pair(map_to_cta(drain_bar, 0));
       const long long t0 = clock64();
       while (!mbar_try_wait(drain_bar, 0)) {
@@ -629,7 +686,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int quad = warp & 3;
     OutT *Y = static_cast<OutT *>(args.Y);
     uint8_t *stage = PEER ? smem + L::kPeerStage + quad * kPeerStageWarp : nullptr;
-    const bool vec_ok = (args.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
+    const bool vec_ok = (args.ldy % (16 / (int)sizeof(OutT)) == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
     int it = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, it++) {
@@ -657,6 +714,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0)); // the leader owns the accumulator hand-over
     }
+    if (!ok && lane == 0) signal_partner_abort(smem_u32((const void *)abort_flag), rank);
   }
 
   tc_fence_before();
@@ -744,7 +802,7 @@ int launch_gemm_pair(const void *A, const void *B, GemmArgs args, int64_t K, int
     cfg.stream = st;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeCooperative; // every CTA resident: producers wait on chunks other CTAs widen
-    attr.val.cooperative = getenv("QL_W8_NOT_COOPERATIVE") ? 0 : 1;
+    attr.val.cooperative = tuning().not_cooperative ? 0 : 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, pair_kernel<KIND, OutT, V>(), ma, mb, args, wargs);
@@ -783,11 +841,11 @@ int launch_gemm_bn(const CUtensorMap &ma, const CUtensorMap &mb, GemmArgs args, 
 template <int KIND, typename OutT>
 int launch_gemm_kind(const void *A, const void *B, GemmArgs args, int64_t K, cudaStream_t st) {
   const int sms = sm_count();
-  if (args.M > 256 && args.N >= 512 && !getenv("QL_GEMM_ONE_CTA")) {
+  if (args.M > 256 && args.N >= 512 && !tuning().one_cta) {
     // (256 x 512 tiles per pair were built and measured: a quarter less L2 traffic per flop, but with a single
     // accumulator the hand-over between tiles is exposed; 1.51 ms against 1.44 ms for 8192 x 28672 x 8192 fp8.)
     const long long tiles2 = (long long)((args.M + 255) / 256) * ((args.N + BN2 - 1) / BN2);
-    if constexpr (KIND == KIND_F8) {
+    if constexpr (KIND == KIND_F8 && sizeof(OutT) == 2) {
       if (args.peer_mode != QL_PEER_NONE) {
         const int pairs = max_resident_pairs<KIND, OutT, PAIR_PEER>();
         if (pairs > 0 && tiles2 >= pairs) return launch_gemm_pair<KIND, OutT, PAIR_PEER>(A, B, args, K, pairs, st);
@@ -815,14 +873,15 @@ int launch_gemm_kind(const void *A, const void *B, GemmArgs args, int64_t K, cud
   }
 }
 
-int check_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_tensor *sa, const ql_tensor *sb,
+// Shapes, types and scales of Y = (A . B^T) * sa * sb + bias.  Says nothing about which kernel can run it.
+int check_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_tensor *sa, const ql_tensor *sb, const ql_tensor *bias,
                const ql_tensor *y, int want_dtype_a, int want_dtype_b) {
   if (!a || !b || !y) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: null tensor", op);
   if (a->rank != 2 || b->rank != 2 || y->rank != 2)
     return set_error(QL_ERR_INVALID_ARGUMENT, "%s: operands must be 2-D ([M,K], [N,K], [M,N])", op);
   if (a->dtype != want_dtype_a || b->dtype != want_dtype_b)
     return set_error(QL_ERR_INVALID_ARGUMENT, "%s: unexpected operand types %d, %d", op, a->dtype, b->dtype);
-  if (!(y->dtype == QL_BF16 || y->dtype == QL_F16)) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: y must be bf16 or f16", op);
+  if (!is_float_dtype(y->dtype)) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: y must be f32, bf16 or f16", op);
   if (a->shape[1] != b->shape[1])
     return set_error(QL_ERR_INVALID_ARGUMENT, "%s: inner dimensions differ (%lld vs %lld)", op, (long long)a->shape[1], (long long)b->shape[1]);
   if (y->shape[0] != a->shape[0] || y->shape[1] != b->shape[0])
@@ -832,31 +891,67 @@ int check_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_
   for (int i = 0; i < 2; i++) {
     if (!sc[i]) continue;
     if (sc[i]->dtype != QL_F32) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: scales must be f32", op);
+    if (sc[i]->rank < 0 || sc[i]->rank > QL_MAX_RANK) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: bad scale rank", op);
     int64_t n = numel(sc[i]);
     if (!(n == 1 || (sc[i]->rank == 1 && n == want[i])))
       return set_error(QL_ERR_INVALID_ARGUMENT, "%s: a scale must be a scalar or one value per row of its operand", op);
     if (!sc[i]->data) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: scale has no data pointer", op);
   }
-  if (!aligned16(a->data) || !aligned16(b->data))
-    return set_error(QL_ERR_INVALID_ARGUMENT, "%s: operands must be 16-byte aligned", op);
+  if (bias) {
+    if (!is_float_dtype(bias->dtype) || bias->rank != 1 || bias->shape[0] != b->shape[0])
+      return set_error(QL_ERR_INVALID_ARGUMENT, "%s: bias must be a float vector with one value per output column", op);
+    if (!bias->data && bias->shape[0] > 0) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: bias has no data pointer", op);
+  }
+  if (numel(a) > 0 && !a->data) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: x has no data pointer", op);
+  if (numel(b) > 0 && !b->data) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: w has no data pointer", op);
+  if (numel(y) > 0 && !y->data) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: y has no data pointer", op);
   if (a->shape[0] > INT32_MAX || b->shape[0] > INT32_MAX || a->shape[1] > INT32_MAX)
     return set_error(QL_ERR_UNSUPPORTED, "%s: dimension too large", op);
   return QL_OK;
 }
 
+// The tensor-core kernels take K-major operands whose rows are whole 16-byte units from a 16-byte aligned base
+// (the TMA rules) and write 16-bit results, or f32 results of the quantized kinds.  Everything else -- f32
+// operands, K = 4, odd strides, unaligned views -- runs on the general kernel (ql_gemm_simt.cu).
 template <int KIND>
-int run_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_tensor *sa, const ql_tensor *sb, ql_tensor *y,
-             void *stream, int64_t ldy = 0, int peer_mode = QL_PEER_NONE, const ql_peer_buffer *dest = nullptr, int64_t offset = 0) {
+bool tensor_core_ok(const ql_tensor *a, const ql_tensor *b, const ql_tensor *y) {
+  const int esize = (KIND == KIND_F8 || KIND == KIND_I8) ? 1 : 2;
+  const int64_t K = a->shape[1];
+  if (K == 0 || (K * esize) % 16 != 0) return false;
+  if (!aligned16(a->data) || !aligned16(b->data)) return false;
+  if (y->dtype == QL_F32) return KIND == KIND_F8 || KIND == KIND_I8;
+  return true;
+}
+
+int run_simt(const ql_tensor *a, const ql_tensor *b, const ql_tensor *sa, const ql_tensor *sb, const ql_tensor *bias, ql_tensor *y,
+             void *stream) {
+  const int64_t M = a->shape[0], K = a->shape[1], N = b->shape[0];
+  return launch_gemm_simt(a->dtype, a->data, b->data, sa ? static_cast<const float *>(sa->data) : nullptr, sa ? (int)numel(sa) : 1,
+                          sb ? static_cast<const float *>(sb->data) : nullptr, sb ? (int)numel(sb) : 1, bias ? bias->data : nullptr,
+                          bias ? bias->dtype : QL_F32, y->data, y->dtype, 1, (int)M, (int)N, (int)K, K, 1, 1, K, N, 0, 0, 0,
+                          (cudaStream_t)stream);
+}
+
+template <int KIND>
+int run_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_tensor *sa, const ql_tensor *sb, const ql_tensor *bias,
+             ql_tensor *y, void *stream, int64_t ldy = 0, int peer_mode = QL_PEER_NONE, const ql_peer_buffer *dest = nullptr,
+             int64_t offset = 0) {
   const int64_t M = a->shape[0], K = a->shape[1], N = b->shape[0];
   if (M == 0 || N == 0) return QL_OK;
   const int esize = (KIND == KIND_F8 || KIND == KIND_I8) ? 1 : 2;
-  if (K == 0 || (K * esize) % 16 != 0)
-    return set_error(QL_ERR_UNSUPPORTED, "%s: K * element size must be a non-zero multiple of 16 bytes (K=%lld)", op, (long long)K);
+  if (!tensor_core_ok<KIND>(a, b, y)) {
+    if (peer_mode != QL_PEER_NONE)
+      return set_error(QL_ERR_UNSUPPORTED, "%s: peer modes need K * element size to be a non-zero multiple of 16 bytes (K=%lld) and aligned operands",
+                       op, (long long)K);
+    return run_simt(a, b, sa, sb, bias, y, stream);
+  }
   GemmArgs args;
   args.Y = y->data;
   args.sa = sa ? static_cast<const float *>(sa->data) : nullptr;
   args.sb = sb ? sb->data : nullptr;
   args.sb_dtype = sb ? sb->dtype : QL_F32;
+  args.bias = bias ? bias->data : nullptr;
+  args.bias_dtype = bias ? bias->dtype : QL_F32;
   args.sa_n = sa ? (int)numel(sa) : 1;
   args.sb_n = sb ? (int)numel(sb) : 1;
   args.M = (int)M;
@@ -874,7 +969,7 @@ int run_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_te
     const int64_t wide = (64ll << 20) / tile_bytes;
     if (band < 16) band = wide < 16 ? wide : 16;
     args.group_m = (int)(band < 4 ? 4 : band);
-    if (const char *e = getenv("QL_GEMM_GROUP_M")) args.group_m = atoi(e) > 0 ? atoi(e) : args.group_m; // tuning aid
+    if (tuning().group_m > 0) args.group_m = tuning().group_m; // tuning aid
     if (args.group_m > args.tiles_m) args.group_m = args.tiles_m;
   }
   args.ldy = ldy > 0 ? ldy : N;
@@ -889,7 +984,9 @@ int run_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_te
   if (!args.status) return set_error(QL_ERR_CUDA, "%s: could not allocate the device status word", op);
   cudaStream_t st = (cudaStream_t)stream;
   if (y->dtype == QL_BF16) return launch_gemm_kind<KIND, __nv_bfloat16>(a->data, b->data, args, K, st);
-  return launch_gemm_kind<KIND, __half>(a->data, b->data, args, K, st);
+  if (y->dtype == QL_F16) return launch_gemm_kind<KIND, __half>(a->data, b->data, args, K, st);
+  if constexpr (KIND == KIND_F8 || KIND == KIND_I8) return launch_gemm_kind<KIND, float>(a->data, b->data, args, K, st);
+  return set_error(QL_ERR_UNSUPPORTED, "%s: unreachable output type", op);
 }
 
 } // namespace
@@ -899,8 +996,8 @@ int gemm16_device(int dtype, const void *X, const void *W, const float *sb, int 
                   cudaStream_t st) {
   ql_tensor x{const_cast<void *>(X), dtype, 2, {M, K}}, w{const_cast<void *>(W), dtype, 2, {N, K}}, y{Y, dtype, 2, {M, N}};
   ql_tensor s{const_cast<float *>(sb), QL_F32, 1, {sb_n}};
-  if (dtype == QL_BF16) return run_gemm<KIND_BF16>("gemm_16", &x, &w, nullptr, sb ? &s : nullptr, &y, st);
-  return run_gemm<KIND_F16>("gemm_16", &x, &w, nullptr, sb ? &s : nullptr, &y, st);
+  if (dtype == QL_BF16) return run_gemm<KIND_BF16>("gemm_16", &x, &w, nullptr, sb ? &s : nullptr, nullptr, &y, st);
+  return run_gemm<KIND_F16>("gemm_16", &x, &w, nullptr, sb ? &s : nullptr, nullptr, &y, st);
 }
 
 // Y[M,N] = (X[M,K] . widen(Wq[N,K])^T) * scale[n] in one launch: the pair kernel with the int8 -> 16-bit conversion
@@ -920,6 +1017,8 @@ int gemm16_widen_t(const void *X, const void *Wraw, void *wide, int *counters, c
   args.sa = nullptr;
   args.sb = scale;
   args.sb_dtype = sdt;
+  args.bias = nullptr;
+  args.bias_dtype = QL_F32;
   args.sa_n = 1;
   args.sb_n = N;
   args.M = M;
@@ -946,7 +1045,7 @@ int gemm16_widen_t(const void *X, const void *Wraw, void *wide, int *counters, c
 
 int gemm16_widen_device(int dtype, const void *X, const void *Wraw, void *wide, int *counters, const void *scale, int sdt, void *Y,
                         int M, int N, int K, cudaStream_t st) {
-  if (M <= 256 || N < 512 || K % 16 != 0 || !aligned16(Wraw) || !aligned16(wide) || !aligned16(X) || getenv("QL_W8_TWO_KERNELS"))
+  if (M <= 256 || N < 512 || K % 16 != 0 || !aligned16(Wraw) || !aligned16(wide) || !aligned16(X) || tuning().two_kernels)
     return QL_ERR_UNSUPPORTED;
   if (dtype == QL_BF16) return gemm16_widen_t<KIND_BF16, __nv_bfloat16>(X, Wraw, wide, counters, scale, sdt, Y, M, N, K, st);
   return gemm16_widen_t<KIND_F16, __half>(X, Wraw, wide, counters, scale, sdt, Y, M, N, K, st);
@@ -959,9 +1058,9 @@ using namespace ql;
 extern "C" {
 
 int ql_gemm_fp8(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx, const ql_tensor *sw, ql_tensor *y, void *stream) {
-  int rc = check_gemm("gemm_fp8", xq, wq, sx, sw, y, QL_F8E4M3, QL_F8E4M3);
+  int rc = check_gemm("gemm_fp8", xq, wq, sx, sw, nullptr, y, QL_F8E4M3, QL_F8E4M3);
   if (rc != QL_OK) return rc;
-  return run_gemm<KIND_F8>("gemm_fp8", xq, wq, sx, sw, y, stream);
+  return run_gemm<KIND_F8>("gemm_fp8", xq, wq, sx, sw, nullptr, y, stream);
 }
 
 int ql_gemm_fp8_peer(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx, const ql_tensor *sw,
@@ -972,12 +1071,13 @@ int ql_gemm_fp8_peer(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *
   if (peer_mode < QL_PEER_NONE || peer_mode > QL_PEER_ADD_OWNER)
     return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_fp8_peer: unknown peer mode %d", peer_mode);
   if (xq->rank != 2 || wq->rank != 2) return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_fp8_peer: operands must be 2-D");
+  if (!(y_dtype == QL_BF16 || y_dtype == QL_F16)) return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_fp8_peer: y must be bf16 or f16");
   const int64_t M = xq->shape[0], N = wq->shape[0];
   char *base = static_cast<char *>((peer_mode == QL_PEER_STORE_ALL || peer_mode == QL_PEER_ADD_ALL) ? dest->all : dest->replica[dest->rank]);
   if (!base) return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_fp8_peer: the buffer has no address for this mode");
   if (offset < 0 || ldy < N) return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_fp8_peer: ldy (%lld) is smaller than N (%lld)", (long long)ldy, (long long)N);
   ql_tensor y{base + offset * 2, y_dtype, 2, {M, N}};
-  int rc = check_gemm("gemm_fp8_peer", xq, wq, sx, sw, &y, QL_F8E4M3, QL_F8E4M3);
+  int rc = check_gemm("gemm_fp8_peer", xq, wq, sx, sw, nullptr, &y, QL_F8E4M3, QL_F8E4M3);
   if (rc != QL_OK) return rc;
   if (peer_mode != QL_PEER_NONE) {
     // the peer writes exist as 16-byte vectors only
@@ -990,22 +1090,77 @@ int ql_gemm_fp8_peer(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *
     for (int r = 0; r < dest->world; r++)
       if (!dest->replica[r]) return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_fp8_peer: replica %d has no address", r);
   }
-  return run_gemm<KIND_F8>("gemm_fp8_peer", xq, wq, sx, sw, &y, stream, ldy, peer_mode, dest, offset);
+  return run_gemm<KIND_F8>("gemm_fp8_peer", xq, wq, sx, sw, nullptr, &y, stream, ldy, peer_mode, dest, offset);
 }
 
 int ql_gemm_i8(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx, const ql_tensor *sw, ql_tensor *y, void *stream) {
-  int rc = check_gemm("gemm_i8", xq, wq, sx, sw, y, QL_I8, QL_I8);
+  int rc = check_gemm("gemm_i8", xq, wq, sx, sw, nullptr, y, QL_I8, QL_I8);
   if (rc != QL_OK) return rc;
-  return run_gemm<KIND_I8>("gemm_i8", xq, wq, sx, sw, y, stream);
+  return run_gemm<KIND_I8>("gemm_i8", xq, wq, sx, sw, nullptr, y, stream);
 }
 
 int ql_gemm_16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *sw, ql_tensor *y, void *stream) {
   if (!x || !w) return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_16: null tensor");
-  int rc = check_gemm("gemm_16", x, w, nullptr, sw, y, x->dtype, x->dtype);
+  if (!(x->dtype == QL_BF16 || x->dtype == QL_F16)) return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_16: operands must be bf16 or f16");
+  int rc = check_gemm("gemm_16", x, w, nullptr, sw, nullptr, y, x->dtype, x->dtype);
   if (rc != QL_OK) return rc;
-  if (x->dtype == QL_BF16) return run_gemm<KIND_BF16>("gemm_16", x, w, nullptr, sw, y, stream);
-  if (x->dtype == QL_F16) return run_gemm<KIND_F16>("gemm_16", x, w, nullptr, sw, y, stream);
-  return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_16: operands must be bf16 or f16");
+  if (y->dtype != x->dtype) return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_16: y must have the operands' type");
+  if (x->dtype == QL_BF16) return run_gemm<KIND_BF16>("gemm_16", x, w, nullptr, sw, nullptr, y, stream);
+  return run_gemm<KIND_F16>("gemm_16", x, w, nullptr, sw, nullptr, y, stream);
+}
+
+// Y = (X . W^T) * sx * sw + bias: the forward of tp.Linear (tripy/nvtripy/frontend/module/linear.py:127-151) after
+// its quantize / dequantize pairs have been folded into scales.  X [M,K] and W [N,K] share one type
+// (f32, f16, bf16, e4m3 or int8); Y is f32, f16 or bf16.
+int ql_linear(const ql_tensor *x, const ql_tensor *w, const ql_tensor *sx, const ql_tensor *sw, const ql_tensor *bias, ql_tensor *y,
+              void *stream) {
+  if (!x || !w) return set_error(QL_ERR_INVALID_ARGUMENT, "linear: null tensor");
+  const int d = x->dtype;
+  if (!(is_float_dtype(d) || d == QL_F8E4M3 || d == QL_I8))
+    return set_error(QL_ERR_INVALID_ARGUMENT, "linear: operands must be f32, f16, bf16, e4m3 or int8");
+  int rc = check_gemm("linear", x, w, sx, sw, bias, y, d, d);
+  if (rc != QL_OK) return rc;
+  if (is_float_dtype(d) && y->dtype != d)
+    return set_error(QL_ERR_INVALID_ARGUMENT, "linear: floating-point operands give a result of their own type"); // matmul.py:31-34
+  switch (d) {
+  case QL_F8E4M3: return run_gemm<KIND_F8>("linear", x, w, sx, sw, bias, y, stream);
+  case QL_I8: return run_gemm<KIND_I8>("linear", x, w, sx, sw, bias, y, stream);
+  case QL_BF16: return run_gemm<KIND_BF16>("linear", x, w, sx, sw, bias, y, stream);
+  case QL_F16: return run_gemm<KIND_F16>("linear", x, w, sx, sw, bias, y, stream);
+  default: return y->shape[0] == 0 || y->shape[1] == 0 ? QL_OK : run_simt(x, w, sx, sw, bias, y, stream);
+  }
+}
+
+// C = A @ B (tensorrt.matrix_multiply with both operands kNONE, TensorRTOps.td:1986-2080; tp.matmul,
+// tripy/nvtripy/frontend/ops/matmul.py:29-108): A [..., M, K], B [..., K, N], C [..., M, N], equal ranks >= 2, one
+// float type.  Leading dimensions of an operand are either all equal to C's or all 1 (broadcast).
+int ql_matmul(const ql_tensor *a, const ql_tensor *b, ql_tensor *c, void *stream) {
+  const char *op = "matmul";
+  if (!a || !b || !c) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: null tensor", op);
+  if (!is_float_dtype(a->dtype) || b->dtype != a->dtype || c->dtype != a->dtype)
+    return set_error(QL_ERR_INVALID_ARGUMENT, "%s: operands and result must share one of f32, f16, bf16", op);
+  const int R = a->rank;
+  if (R < 2 || R > QL_MAX_RANK || b->rank != R || c->rank != R)
+    return set_error(QL_ERR_INVALID_ARGUMENT, "%s: operands and result must have equal ranks >= 2", op);
+  const int64_t M = a->shape[R - 2], K = a->shape[R - 1], N = b->shape[R - 1];
+  if (b->shape[R - 2] != K || c->shape[R - 2] != M || c->shape[R - 1] != N)
+    return set_error(QL_ERR_INVALID_ARGUMENT, "%s: [..., %lld, %lld] @ [..., %lld, %lld] does not give [..., %lld, %lld]", op, (long long)M,
+                     (long long)K, (long long)b->shape[R - 2], (long long)N, (long long)c->shape[R - 2], (long long)c->shape[R - 1]);
+  int64_t batch = 1, a_lead = 1, b_lead = 1;
+  for (int i = 0; i < R - 2; i++) {
+    batch *= c->shape[i];
+    a_lead *= a->shape[i];
+    b_lead *= b->shape[i];
+    if (!((a->shape[i] == c->shape[i] || a->shape[i] == 1) && (b->shape[i] == c->shape[i] || b->shape[i] == 1)))
+      return set_error(QL_ERR_INVALID_ARGUMENT, "%s: leading dimension %d does not broadcast", op, i);
+  }
+  if (!((a_lead == batch || a_lead == 1) && (b_lead == batch || b_lead == 1)))
+    return set_error(QL_ERR_UNSUPPORTED, "%s: leading dimensions of an operand must be all equal to the result's or all 1", op);
+  if (batch == 0 || M == 0 || N == 0) return QL_OK;
+  if (!a->data || !b->data || !c->data) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: tensor without a data pointer", op);
+  if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX || batch > INT32_MAX) return set_error(QL_ERR_UNSUPPORTED, "%s: dimension too large", op);
+  return launch_gemm_simt(a->dtype, a->data, b->data, nullptr, 1, nullptr, 1, nullptr, QL_F32, c->data, c->dtype, (int)batch, (int)M, (int)N,
+                          (int)K, K, 1, N, 1, N, a_lead == 1 ? 0 : M * K, b_lead == 1 ? 0 : K * N, M * N, (cudaStream_t)stream);
 }
 
 // Last status code a GEMM kernel recorded on the current device (0 = none); synchronises the device.

@@ -380,43 +380,7 @@ __global__ void __launch_bounds__(256) scale_to_f32_kernel(const void *__restric
   if (i < n) out[i] = load_scale(s, sdt, i);
 }
 
-// Grow-only scratch buffer per device for the widened weights (allocated with cudaMalloc on first
-// use or growth, so the first call of a given size must not happen inside a stream capture; calls
-// on different streams that may overlap would share it, and the tile counters below, and must be
-// ordered by the caller).
-int widen_workspace(size_t bytes, uint8_t **out) {
-  static uint8_t *buf[64] = {nullptr};
-  static size_t cap[64] = {0};
-  int dev = 0;
-  QL_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return set_error(QL_ERR_UNSUPPORTED, "linear_w8a16: device index %d out of range", dev);
-  if (cap[dev] < bytes) {
-    if (buf[dev]) QL_CUDA_TRY(cudaFree(buf[dev]));
-    buf[dev] = nullptr;
-    cap[dev] = 0;
-    QL_CUDA_TRY(cudaMalloc(&buf[dev], bytes));
-    cap[dev] = bytes;
-  }
-  *out = buf[dev];
-  return QL_OK;
-}
-
-// Tile counters of the single-launch route: allocated and zeroed once per device; the kernel leaves them at zero.
-constexpr int kWidenCounters = 1024;
-int widen_counters(int **out) {
-  static int *ctr[64] = {nullptr};
-  int dev = 0;
-  QL_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return set_error(QL_ERR_UNSUPPORTED, "linear_w8a16: device index %d out of range", dev);
-  if (!ctr[dev]) {
-    int *p = nullptr;
-    QL_CUDA_TRY(cudaMalloc(&p, kWidenCounters * sizeof(int)));
-    QL_CUDA_TRY(cudaMemset(p, 0, kWidenCounters * sizeof(int)));
-    ctr[dev] = p;
-  }
-  *out = ctr[dev];
-  return QL_OK;
-}
+constexpr int kWidenCounters = 1024; // tile counters of the single-launch route (ceil(N / 256) + 1 are used)
 
 } // namespace
 
@@ -431,25 +395,39 @@ int gemm16_widen_device(int dtype, const void *X, const void *Wraw, void *wide, 
 // kernel applies, the widening runs inside it, ahead of the tiles that need it; otherwise in a kernel of its own.
 int launch_w8a16_widen(int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M, int N, int K,
                        cudaStream_t st) {
+  // Scratch of this call alone, from the stream-ordered allocator: the 16-bit copy of the weights, f32 scales and the
+  // tile counters.  Nothing is shared between calls, so calls on different streams may overlap, a later call with
+  // larger weights cannot invalidate an address an earlier (or captured) call still uses, and inside a stream
+  // capture the allocation becomes a node of the graph.
   const int64_t n = (int64_t)N * K;
   const size_t wide_bytes = (size_t)n * 2, scale_off = (wide_bytes + 255) & ~size_t(255);
+  const size_t ctr_off = (scale_off + (size_t)N * sizeof(float) + 255) & ~size_t(255);
   uint8_t *scratch = nullptr;
-  int rc = widen_workspace(scale_off + (size_t)N * sizeof(float), &scratch);
-  if (rc != QL_OK) return rc;
+  keep_scratch_pool_warm();
+  QL_CUDA_TRY(cudaMallocAsync(&scratch, ctr_off + kWidenCounters * sizeof(int), st));
   float *sf = reinterpret_cast<float *>(scratch + scale_off);
+  int rc = QL_ERR_UNSUPPORTED;
   if ((N + 255) / 256 + 1 <= kWidenCounters) {
-    int *counters = nullptr;
-    if ((rc = widen_counters(&counters)) != QL_OK) return rc;
+    int *counters = reinterpret_cast<int *>(scratch + ctr_off);
+    cudaError_t me = cudaMemsetAsync(counters, 0, kWidenCounters * sizeof(int), st);
+    if (me != cudaSuccess) {
+      cudaFreeAsync(scratch, st);
+      return cuda_error(me, "cudaMemsetAsync");
+    }
     rc = gemm16_widen_device(xdt, X, W, scratch, counters, scale, sdt, Y, M, N, K, st);
-    if (rc != QL_ERR_UNSUPPORTED) return rc;
   }
-  const int64_t n16 = n / 16; // K % 64 == 0
-  if (xdt == QL_F16) widen_i8_kernel<__half><<<(unsigned)((n16 + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t *>(W), reinterpret_cast<__half *>(scratch), n16);
-  else widen_i8_kernel<__nv_bfloat16><<<(unsigned)((n16 + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t *>(W), reinterpret_cast<__nv_bfloat16 *>(scratch), n16);
-  scale_to_f32_kernel<<<(N + 255) / 256, 256, 0, st>>>(scale, sdt, sf, N);
-  count_launches(2);
-  QL_CUDA_TRY(cudaGetLastError());
-  return gemm16_device(xdt, X, scratch, sf, N, Y, M, N, K, st);
+  if (rc == QL_ERR_UNSUPPORTED) {
+    const int64_t n16 = n / 16; // K % 64 == 0
+    if (xdt == QL_F16) widen_i8_kernel<__half><<<(unsigned)((n16 + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t *>(W), reinterpret_cast<__half *>(scratch), n16);
+    else widen_i8_kernel<__nv_bfloat16><<<(unsigned)((n16 + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t *>(W), reinterpret_cast<__nv_bfloat16 *>(scratch), n16);
+    scale_to_f32_kernel<<<(N + 255) / 256, 256, 0, st>>>(scale, sdt, sf, N);
+    count_launches(2);
+    cudaError_t le = cudaGetLastError();
+    rc = le != cudaSuccess ? cuda_error(le, "widen_i8_kernel") : gemm16_device(xdt, X, scratch, sf, N, Y, M, N, K, st);
+  }
+  cudaError_t fe = cudaFreeAsync(scratch, st);
+  if (rc == QL_OK && fe != cudaSuccess) return cuda_error(fe, "cudaFreeAsync");
+  return rc;
 }
 
 // Y = (X . Wq^T) * scale[n] with the int8 -> 16-bit conversion inside the kernel (K % 64 == 0).

@@ -183,7 +183,8 @@ int ql_dynamic_quantize(const ql_tensor *input, const ql_tensor *double_quant_sc
   if (!input) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: null tensor", op);
   // the verifier's three checks, in its order and words
   if (block_size != 16) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: currently only block size of 16 is supported!", op);
-  if (axis < input->rank - 2 || axis >= input->rank)
+  if (input->rank < 0 || input->rank > QL_MAX_RANK) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: input has rank %d (0..%d supported)", op, input->rank, QL_MAX_RANK);
+  if (axis < 0 || axis < input->rank - 2 || axis >= input->rank)
     return set_error(QL_ERR_INVALID_ARGUMENT, "%s: invalid axis! Axis can be either last or second last dimension of the input.", op);
   if (input->shape[axis] % 16 != 0) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: shape(input)[axis] must be divisible by 16.", op);
   if (axis != input->rank - 1) return set_error(QL_ERR_UNSUPPORTED, "%s: blocks along the second last dimension are not built", op);

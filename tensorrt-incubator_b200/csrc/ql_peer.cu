@@ -1,6 +1,8 @@
 // Cross-GPU helpers of the fused GEMM + collective path: a barrier between the ranks of one box and a
 // broadcast of a rank's rows to every replica.  One process per GPU; each rank launches these on its own
 // GPU, so the barrier's ranks never share a device.  The reference has no multi-GPU execution of this path.
+#include <atomic>
+
 #include "ql_common.cuh"
 
 namespace ql {
@@ -8,6 +10,7 @@ namespace {
 
 constexpr long long kPeerWaitLimitCycles = 1ll << 34; // about ten seconds: ranks are separate processes
 constexpr int ST_TIMEOUT_PEER = 7;
+std::atomic<long long> g_peer_wait_limit{kPeerWaitLimitCycles};
 
 struct FlagPtrs {
   uint32_t *flags[QL_MAX_PEERS];
@@ -15,7 +18,7 @@ struct FlagPtrs {
 
 // flags (per rank, uint32): [0, world) = the barrier number each peer has reached, written by that peer;
 // [world] = how many barriers this rank has entered (touched by this kernel only).
-__global__ void peer_barrier_kernel(FlagPtrs p, int world, int rank, int *status) {
+__global__ void peer_barrier_kernel(FlagPtrs p, int world, int rank, int *status, long long limit_cycles) {
   __shared__ uint32_t epoch_s;
   const int t = threadIdx.x;
   if (t == 0) {
@@ -34,7 +37,7 @@ __global__ void peer_barrier_kernel(FlagPtrs p, int world, int rank, int *status
       uint32_t v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
       if ((int32_t)(v - epoch) >= 0) break;
-      if (clock64() - t0 > kPeerWaitLimitCycles) { // a peer never arrived: record it and let the stream go on
+      if (clock64() - t0 > limit_cycles) { // a peer never arrived: record it and let the stream go on
         atomicCAS(status, 0, ST_TIMEOUT_PEER);
         break;
       }
@@ -98,9 +101,14 @@ int ql_peer_barrier(const ql_peer_buffer *flags, void *stream) {
   if (!status) return set_error(QL_ERR_CUDA, "peer_barrier: could not allocate the device status word");
   FlagPtrs p;
   for (int r = 0; r < QL_MAX_PEERS; r++) p.flags[r] = r < flags->world ? static_cast<uint32_t *>(flags->replica[r]) : nullptr;
-  peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(p, flags->world, flags->rank, status);
+  peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(p, flags->world, flags->rank, status, g_peer_wait_limit.load(std::memory_order_relaxed));
   count_launches(1);
   QL_CUDA_TRY(cudaGetLastError());
+  return QL_OK;
+}
+
+int ql_set_peer_wait_limit(int64_t cycles) {
+  g_peer_wait_limit.store(cycles > 0 ? (long long)cycles : kPeerWaitLimitCycles, std::memory_order_relaxed);
   return QL_OK;
 }
 

@@ -183,8 +183,25 @@ inline int get_encode_fn(EncodeTiledFn *out) {
   return QL_OK;
 }
 
-// [rows, K] row-major matrix of `esize`-byte elements, box = [box_rows, 128 bytes], 128-byte swizzle
+// [rows, K] row-major matrix of `esize`-byte elements, box = [box_rows, 128 bytes], 128-byte swizzle.
+// A tensor map is a pure function of (address, shape, box, type), so the last few are kept per thread: a decode
+// loop that calls the same layers again and again does not pay the driver's encoder on every launch, and an
+// entry whose buffer was freed and reallocated at the same address with the same shape is still correct.
 inline int make_map(CUtensorMap *map, int kind, const void *ptr, int64_t rows, int64_t K, int box_rows) {
+  struct Entry {
+    const void *ptr;
+    int64_t rows, K;
+    int box_rows, kind;
+    CUtensorMap map;
+  };
+  constexpr int kEntries = 32;
+  static thread_local Entry cache[kEntries] = {};
+  const uintptr_t h = reinterpret_cast<uintptr_t>(ptr) >> 8;
+  Entry &e = cache[(h ^ (h >> 7) ^ (uintptr_t)box_rows ^ ((uintptr_t)rows << 1)) % kEntries];
+  if (e.ptr == ptr && ptr != nullptr && e.rows == rows && e.K == K && e.box_rows == box_rows && e.kind == kind) {
+    *map = e.map;
+    return QL_OK;
+  }
   EncodeTiledFn enc;
   int rc = get_encode_fn(&enc);
   if (rc != QL_OK) return rc;
@@ -199,6 +216,12 @@ inline int make_map(CUtensorMap *map, int kind, const void *ptr, int64_t rows, i
   CUresult r = enc(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return set_error(QL_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  e.ptr = ptr;
+  e.rows = rows;
+  e.K = K;
+  e.box_rows = box_rows;
+  e.kind = kind;
+  e.map = *map;
   return QL_OK;
 }
 

@@ -2,7 +2,7 @@
 B200 (sm_100a) kernels in ../csrc, reached through the C ABI in include/qlinear_b200.h."""
 from ._lib import QlError, lib  # noqa: F401
 from .dtypes import bfloat16, bool, float4, float8, float16, float32, int4, int8, int32, int64  # noqa: F401,A004
-from .linear import Linear, gemm_16, gemm_fp8, gemm_i8, linear_w4a16, linear_w8a16  # noqa: F401
+from .linear import Linear, gemm_16, gemm_fp8, gemm_i8, linear, linear_w4a16, linear_w8a16, matmul  # noqa: F401
 from .ops import (QuantizeError, amax_scale, cast, dequantize, dequantize_nvfp4, dynamic_quantize, quantize,  # noqa: F401
                   quantize_dequantize, quantize_to)
 from .tensor import Float4Tensor, Int4Tensor  # noqa: F401

@@ -76,6 +76,9 @@ SIGNATURES = {
     "ql_peer_broadcast": ([_P, ctypes.c_int64, ctypes.c_int64, _S], ctypes.c_int),
     "ql_gemm_i8": ([_T, _T, _T, _T, _T, _S], ctypes.c_int),
     "ql_gemm_16": ([_T, _T, _T, _T, _S], ctypes.c_int),
+    "ql_linear": ([_T, _T, _T, _T, _T, _T, _S], ctypes.c_int),
+    "ql_matmul": ([_T, _T, _T, _S], ctypes.c_int),
+    "ql_set_peer_wait_limit": ([ctypes.c_int64], ctypes.c_int),
     "ql_rmsnorm_quant_fp8": ([_T, ctypes.c_float, _T, _T, _S], ctypes.c_int),
     "ql_swiglu_quant_fp8": ([_T, _T, _T, _S], ctypes.c_int),
     "ql_gemm_status": ([ctypes.POINTER(ctypes.c_int32)], ctypes.c_int),

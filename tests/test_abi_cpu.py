@@ -160,3 +160,46 @@ def test_nvfp4_entry_points_use_the_verifier_wording():
     assert "one entry per block of 16" in _err(L.ql_dynamic_quantize(x, gs, 1, 16, q, _t(_lib.F8E4M3, [4, 4]), None))
     assert "rank-0" in _err(L.ql_dynamic_quantize(x, _t(_lib.F32, [1]), 1, 16, q, s, None))
     assert "data must be f4E2M1FN and scales f8E4M3FN" in _err(L.ql_dequantize_nvfp4(_t(_lib.I4, [4, 32]), s, gs, x, None))
+
+
+def test_nvfp4_axis_and_rank_are_checked_before_any_shape_is_read():
+    L = _lib.lib()
+    gs = _t(_lib.F32, [])
+    q, s = _t(_lib.F4E2M1, [32]), _t(_lib.F8E4M3, [2])
+    # a vector with axis -1, a scalar with axis 0 or -1, a rank beyond the structure's capacity
+    assert "invalid axis!" in _err(L.ql_dynamic_quantize(_t(_lib.F32, [32]), gs, -1, 16, q, s, None))
+    assert "invalid axis!" in _err(L.ql_dynamic_quantize(_t(_lib.F32, []), gs, 0, 16, q, s, None))
+    assert "invalid axis!" in _err(L.ql_dynamic_quantize(_t(_lib.F32, []), gs, -1, 16, q, s, None))
+    bad = _t(_lib.F32, [32])
+    bad.rank = 9
+    assert "rank 9" in _err(L.ql_dynamic_quantize(bad, gs, 8, 16, q, s, None))
+    # tensorrt.dequantize of f4 data checks the data tensor like every other argument
+    f4 = _t(_lib.F4E2M1, [4, 32], ptr=0)
+    assert "no data pointer" in _err(L.ql_dequantize(f4, _t(_lib.F8E4M3, [4, 2]), _t(_lib.F32, [4, 32]), _lib.make_attrs(None), None))
+    f4 = _t(_lib.F4E2M1, [4, 32])
+    f4.rank = 11
+    assert "rank 11" in _err(L.ql_dequantize(f4, _t(_lib.F8E4M3, [4, 2]), _t(_lib.F32, [4, 32]), _lib.make_attrs(None), None))
+
+
+def test_linear_and_matmul_argument_rules():
+    """tp.matmul wants operands of one float type (tripy/nvtripy/frontend/ops/matmul.py:31-34); the shapes are those of
+    tensorrt.matrix_multiply.  All of it is checked before a device is touched."""
+    L = _lib.lib()
+    x, w, y = _t(_lib.F32, [3, 4]), _t(_lib.F32, [2, 4]), _t(_lib.F32, [3, 2])
+    assert "result of their own type" in _err(L.ql_linear(x, w, None, None, None, _t(_lib.BF16, [3, 2]), None))
+    assert "inner dimensions differ" in _err(L.ql_linear(x, _t(_lib.F32, [2, 5]), None, None, None, y, None))
+    assert "unexpected operand types" in _err(L.ql_linear(x, _t(_lib.F16, [2, 4]), None, None, None, y, None))
+    assert "operands must be f32, f16, bf16, e4m3 or int8" in _err(L.ql_linear(_t(_lib.I4, [3, 4]), _t(_lib.I4, [2, 4]), None, None, None, y, None))
+    assert "bias must be a float vector" in _err(L.ql_linear(x, w, None, None, _t(_lib.F32, [3]), y, None))
+    assert "scalar or one value per row" in _err(L.ql_linear(x, w, _t(_lib.F32, [2]), None, None, y, None))
+    assert "y must be [M,N]" in _err(L.ql_linear(x, w, None, None, None, _t(_lib.F32, [3, 3]), None))
+    a, b, c = _t(_lib.F32, [2, 3, 4]), _t(_lib.F32, [1, 4, 5]), _t(_lib.F32, [2, 3, 5])
+    assert "share one of f32, f16, bf16" in _err(L.ql_matmul(a, _t(_lib.F16, [1, 4, 5]), c, None))
+    assert "equal ranks >= 2" in _err(L.ql_matmul(_t(_lib.F32, [4]), _t(_lib.F32, [4]), _t(_lib.F32, []), None))
+    assert "does not give" in _err(L.ql_matmul(a, _t(_lib.F32, [1, 5, 5]), c, None))
+    assert "does not broadcast" in _err(L.ql_matmul(a, _t(_lib.F32, [3, 4, 5]), c, None))
+    # a mixed broadcast is left to the caller to expand
+    assert "all equal to the result's or all 1" in _err(
+        L.ql_matmul(_t(_lib.F32, [2, 1, 3, 4]), _t(_lib.F32, [2, 6, 4, 5]), _t(_lib.F32, [2, 6, 3, 5]), None))
+    # empty products are no-ops even without a device
+    assert L.ql_matmul(_t(_lib.F32, [0, 3, 4]), _t(_lib.F32, [0, 4, 5]), _t(_lib.F32, [0, 3, 5]), None) == 0

@@ -86,3 +86,14 @@ def test_cast_between_plain_types_is_an_ordinary_conversion():
     assert ql.cast(x, ql.int32).tolist() == [1, -2, 3]
     assert ql.cast(torch.tensor([0, 5], dtype=torch.int8), ql.float32).tolist() == [0.0, 5.0]
     assert ql.cast(torch.tensor([False, True]), ql.int8).tolist() == [0, 1]
+
+
+def test_matmul_contract():
+    """tripy/nvtripy/frontend/ops/matmul.py:31-34 (one float type for both operands) and :98-102 (no scalars)."""
+    x = torch.ones(2, 2)
+    with pytest.raises(ql.QuantizeError, match="at least 1 dimension"):
+        ql.matmul(torch.ones(()), x)
+    with pytest.raises(ql.QuantizeError, match="__matmul__"):
+        ql.matmul(x, x.half())
+    with pytest.raises(ql.QuantizeError, match="__matmul__"):
+        ql.matmul(x.to(torch.int8), x.to(torch.int8))

@@ -5,6 +5,8 @@ import math
 import numpy as np
 import pytest
 
+from linear_cases import iota as _iota, linear_cases as _linear_cases
+
 CODE = {"f32": 0, "f16": 1, "bf16": 2, "i8": 3, "i4": 4, "f8": 5}
 MODE = {"pt": 0, "pc": 1, "block": 2}
 
@@ -169,3 +171,33 @@ def test_e2m1_rounding_is_nearest_even_and_saturating(orc):
     # ties go to the code with an even mantissa: 0.25 -> 0, 0.75 -> 1, 1.25 -> 1, 1.75 -> 2, 2.5 -> 2, 3.5 -> 4, 5 -> 4
     for x, want in [(0.25, 0.0), (0.75, 1.0), (1.25, 1.0), (1.75, 2.0), (2.5, 2.0), (3.5, 4.0), (5.0, 4.0), (5.01, 6.0), (1e9, 6.0), (-7.0, -6.0), (0.26, 0.5)]:
         assert L.orc_f4e2m1_to_f32(L.orc_f32_to_f4e2m1(x)) == want, x
+
+
+def test_linear_module_known_answers(orc, kat):
+    """tripy/tests/integration/test_linear.py: float Linear, the twelve int8 / float8 combinations (two rejected)
+    and the four int4 weight-only modes, through the oracle's op-by-op restatement of Linear.forward."""
+    seen = 0
+    for cid, kw, want in _linear_cases(kat):
+        if want is None:
+            with pytest.raises(ValueError, match=kat["linear_module"]["quant"]["rejected"]["message"]):
+                orc.linear_module(**kw)
+        else:
+            assert np.array_equal(orc.linear_module(**kw), want), cid
+        seen += 1
+    assert seen == 1 + 12 + 4
+
+
+def test_matmul_rank_rules(orc, kat):
+    for case in kat["matmul_doc_examples"]["cases"]:
+        a, b = _iota(case["a_shape"], case["a_iota_dim"]), _iota(case["b_shape"], case["b_iota_dim"])
+        got = orc.matmul(a, b, CODE["f32"])
+        assert got.shape == (a @ b).shape and np.array_equal(got, a @ b), case
+    # the int4 dequantize -> matrix_multiply answers, through the same matmul
+    for case in kat["int4_dq_matmul"]["cases"]:
+        vals = np.array(case["lhs_i4"], dtype=np.int8)
+        packed = np.zeros(2, dtype=np.uint8)
+        for i, v in enumerate(vals):
+            packed[i // 2] |= (int(v) & 0xF) << (4 * (i % 2))
+        lhs = orc.dequantize(packed, CODE["i4"], np.array(case["scale"], dtype=np.float32), 0, 0, [2, 2], 0)
+        out = orc.matmul(lhs, np.array(case["rhs"], dtype=np.float32).reshape(2, 2), CODE["f32"])
+        assert out.reshape(-1).tolist() == case["expect"]

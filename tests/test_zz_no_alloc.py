@@ -1,9 +1,10 @@
 """ql_amax_scale_noalloc: the allocation-free variant of ql_amax_scale, for callers that may not
 allocate device memory while they run (a runtime with a fixed, pre-planned memory budget; a
 serving loop that cannot afford an allocator stall).  Its accumulators sit in a fixed array inside
-the library, so this file checks three things through the C ABI: the results are bit-identical
+the library, so this file checks four things through the C ABI: the results are bit-identical
 to ql_amax_scale's, a second call right after the first is not disturbed by what the first left
-in the shared array, and a request larger than the array is refused with a clear message.
+in the shared array, a request larger than the array is refused with a clear message, and
+repeated calls change neither the driver's free memory nor torch's reservation.
 The file name keeps it last in collection order, so a failure here cannot hide other results."""
 import pytest
 import torch
@@ -45,6 +46,25 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point():
     c = torch.randn((128, 512), generator=g).cuda()
     want, got = _both(c, (128, 4), None, 7.0, torch.float32)
     assert torch.equal(want, got)
+
+
+def test_no_device_memory_is_allocated():
+    """What the entry point is for: after its first call on the device, further calls leave both the driver's free
+    memory and the stream-ordered pool's reservation where they were (16-bit scales are the case in which
+    ql_amax_scale takes scratch from that pool)."""
+    x = (torch.randn((2048, 512)) * 3).to(torch.bfloat16).cuda()
+    s = torch.empty((2048,), dtype=torch.bfloat16, device="cuda")
+    L = _lib.lib()
+    call = lambda: _lib.check(L.ql_amax_scale_noalloc(ql_view(x), ql_view(s), _lib.make_attrs(0), 448.0, current_stream(x.device)))
+    call()   # the first call on a device looks the array's address up
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    reserved0 = torch.cuda.memory_reserved()
+    for _ in range(8):
+        call()
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0 and torch.cuda.memory_reserved() == reserved0
 
 
 def test_request_beyond_the_fixed_array_is_refused():
