@@ -1,14 +1,20 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-linear hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c5|nvfp4] [--impl reference]
 
 One JSON line on stdout (rank 0).  A step is one pass of the workload over one batch of seeded
 synthetic input already resident in HBM; `value` is device-timed throughput over exactly K steps,
 `e2e` the same metric with the step's inputs copied from pinned host memory and its results read
-back inside the timed region.  Default workload: benchmark config 2 (per-channel int8 weights,
-W8A16 linear, M in {1, 16, 128, 2048}); the other configs are selectable and are otherwise
-covered by the parity tests.
+back inside the timed region.  Default workload: benchmark config 5, the fp8 Llama-style MLP block
+(4096 tokens, 8192 -> 28672 -> 8192), unsharded on one GPU and tensor-parallel over N GPUs (strong
+scaling: the same block, split).  At N = 1 the line also carries the fused int8 quantize/dequantize
+round trip of config 1 and the fp8 GEMM of config 4 as extra entries of `parts`, so that one run
+records all three kinds of kernel; the other configs are selectable with --workload and are
+otherwise covered by the parity tests.  Before anything is timed the step's result is checked
+(`parity_check`): against the same block computed stage by stage through the plain entry points,
+against the NCCL all-reduce variant on the same shards when N > 1, and for bit-identity across ranks;
+a mismatch ends the run with a non-zero exit code.
 
 `--impl reference` times the CPU restatement of the reference's host path (oracle/) with all host
 threads on a bounded sample of the same workload.  The product path never touches oracle/.
@@ -432,8 +438,9 @@ class Fp8Gemm(Workload):
 class Fp8Mlp(Workload):
     """Config 5: Llama-style MLP block, hidden 8192, intermediate 28672, 4096 tokens, bf16 activations,
     fp8 e4m3 per-output-channel gate/up/down weights ~ N(0,0.02).  RMSNorm(eps 1e-5, weight 1) fused with
-    per-token fp8 quantize -> gate/up GEMM -> SwiGLU + re-quantize -> down GEMM.  With g GPUs: gate/up
-    column-parallel, down row-parallel, one NCCL all-reduce of the bf16 result (strong scaling)."""
+    per-token fp8 quantize -> gate/up GEMM with SwiGLU in its epilogue -> per-token re-quantize -> down GEMM.
+    With g GPUs: gate/up column-parallel, down row-parallel, the partial results summed over the ranks
+    (strong scaling: the same block, split)."""
 
     name = "config5_fp8_mlp_block"
     metric = "quantized GEMM TFLOP/s (config 5: fp8 e4m3 Llama-style MLP block, 4096 tokens, 8192 -> 28672 -> 8192)"
@@ -442,6 +449,16 @@ class Fp8Mlp(Workload):
     T, H, I = 4096, 8192, 28672
     use_graphs = False
     scaling = "strong"
+    PROTOCOLS = {
+        "add_all": "partial sums added into both GPUs' outputs by the down-projection epilogue (multimem.red), one barrier",
+        "add_owner": "partial sums added into the owner's rows by the down-projection epilogue (red over peer memory), "
+                     "barrier, owners broadcast their rows (multimem.st), barrier",
+        "switch_reduce": "down projection into the local copy, barrier, in-switch sum of each GPU's own rows written to all "
+                         "GPUs (multimem.ld_reduce + multimem.st), barrier",
+        "switch_pipelined": "down projection in token slabs into the local copy; per slab, on a side stream, barrier + in-switch sum of "
+                            "each GPU's own rows written to all GPUs (multimem.ld_reduce + multimem.st) under the next slab's GEMM; "
+                            "one closing barrier",
+        "nccl": "NCCL all-reduce"}
 
     def __init__(self, torch, ql, device, dist=None, seed=1005):
         self.torch, self.ql, self.device, self.dist = torch, ql, device, dist
@@ -454,49 +471,66 @@ class Fp8Mlp(Workload):
         def w(shape):
             return (torch.randn(shape, generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
         self.mlp = ql.QuantizedMLP(w((il, self.H)), w((il, self.H)), w((self.H, il)), eps=1e-5, group=(dist.group.WORLD if dist is not None else None),
-                                    fused_all_reduce=fused)
+                                    fused_all_reduce=fused, fused_swiglu=not os.environ.get("QL_BENCH_UNFUSED_SWIGLU"))
+        if os.environ.get("QL_BENCH_MLP_SLABS"):
+            self.mlp.slabs = int(os.environ["QL_BENCH_MLP_SLABS"])
         gx = torch.Generator(device="cpu").manual_seed(seed)
         self.x_host = torch.randn((self.T, self.H), generator=gx, dtype=torch.float32).to(torch.bfloat16).pin_memory()
         self.x = self.x_host.to(device)
         self.buf = self.mlp._buffers(self.T, device)
         proto = self.buf["protocol"]
-        self.parallelism = (f"tensor-parallel over {self.world} GPUs: gate/up column-parallel, down row-parallel, " +
-                            {"add_all": "partial sums added into both GPUs' outputs by the down-projection epilogue (multimem.red), one barrier",
-                             "add_owner": "partial sums added into the owner's rows by the down-projection epilogue (red over peer memory), "
-                                          "barrier, owners broadcast their rows (multimem.st), barrier",
-                             "switch_reduce": "down projection into the local copy, barrier, in-switch sum of each GPU's own rows written to all "
-                                              "GPUs (multimem.ld_reduce + multimem.st), barrier",
-                             "nccl": "NCCL all-reduce"}[proto])
-        self.y_host = torch.empty((self.T, self.H), dtype=torch.bfloat16).pin_memory()
+        self.parallelism = (f"tensor-parallel over {self.world} GPUs: gate/up column-parallel, down row-parallel, " + self.PROTOCOLS[proto])
+        # every rank ends with the whole result; each reads its own share of the rows back
+        self.rows_out = self.T // self.world
+        self.y_host = torch.empty((self.rows_out, self.H), dtype=torch.bfloat16).pin_memory()
 
     def parts(self):
-        T, H, il = self.T, self.H, self.il
-        ps = [("rmsnorm_quant", lambda: self.mlp.stage_norm_quant(self.x, self.buf), 0, 3 * T * H + 4 * T, "hbm"),
-              ("gate_up_gemm", lambda: self.mlp.stage_gate_up(self.buf), 2 * T * H * 2 * il, T * H + 2 * il * H + 2 * T * 2 * il, "tensor_fp8"),
-              ("swiglu_quant", lambda: self.mlp.stage_swiglu_quant(self.buf), 0, 2 * T * 2 * il + T * il, "hbm")]
-        down = (2 * T * il * H, T * il + H * il + 2 * T * H, "tensor_fp8")
-        proto = self.buf["protocol"]
-        if proto != "nccl":
-            def finish():
-                self.mlp.stage_barrier(self.buf)
-                self.mlp._step += 1
-            if proto == "switch_reduce":
-                ps += [("down_gemm", lambda: self.mlp.stage_down_local(self.buf)) + down,
-                       ("barrier_partials", lambda: self.mlp.stage_barrier(self.buf), 0, 0, "nvlink"),
-                       ("switch_reduce_owned_rows", lambda: self.mlp.stage_switch_reduce_owned(self.buf), 0, 2 * T * H, "nvlink")]
-            else:
-                scatter = proto == "add_owner"
-                ps += [("down_gemm_add_owner" if scatter else "down_gemm_add_all", lambda: self.mlp.stage_down_add(self.buf)) + down,
-                       ("clear_next_output", lambda: self.mlp.stage_clear_next(self.buf), 0, 2 * T * H // (self.world if scatter else 1), "hbm")]
-                if scatter:
-                    ps += [("barrier_sums", lambda: self.mlp.stage_barrier(self.buf), 0, 0, "nvlink"),
-                           ("broadcast_owned_rows", lambda: self.mlp.stage_broadcast_owned(self.buf), 0, 2 * T * H * (self.world - 1) // self.world, "nvlink")]
-            ps.append(("barrier", finish, 0, 0, "nvlink"))
+        T, H, il, m, b = self.T, self.H, self.il, self.mlp, self.buf
+        ps = [("rmsnorm_quant", lambda: m.stage_norm_quant(self.x, b), 0, 3 * T * H + 4 * T, "hbm")]
+        if m.fused_swiglu:
+            ps += [("gate_up_gemm_swiglu", lambda: m.stage_gate_up(b), 2 * T * H * 2 * il, T * H + 2 * il * H + 2 * T * il, "tensor_fp8"),
+                   ("quantize_rows", lambda: m.stage_swiglu_quant(b), 0, 2 * T * il + T * il, "hbm")]
         else:
-            ps.append(("down_gemm", lambda: self.mlp.stage_down(self.buf)) + down)
+            ps += [("gate_up_gemm", lambda: m.stage_gate_up(b), 2 * T * H * 2 * il, T * H + 2 * il * H + 2 * T * 2 * il, "tensor_fp8"),
+                   ("swiglu_quant", lambda: m.stage_swiglu_quant(b), 0, 2 * T * 2 * il + T * il, "hbm")]
+        down = (2 * T * il * H, T * il + H * il + 2 * T * H, "tensor_fp8")
+        proto = b["protocol"]
+        nv_bytes = 2 * T * H                       # what crosses NVLink per GPU and direction in an all-reduce of Y, at most
+        if proto == "nccl":
+            ps.append(("down_gemm", lambda: m.stage_down(b)) + down)
             if self.world > 1:
-                ps.append(("all_reduce_y", lambda: self.mlp.stage_all_reduce(self.buf), 0, 2 * 2 * T * H * (self.world - 1) // self.world, "nvlink"))
+                ps.append(("all_reduce_y", lambda: m.stage_all_reduce(b), 0, nv_bytes, "nvlink"))
+            return ps
+
+        def finish():
+            m.stage_barrier(b)
+            m._step += 1
+        if proto == "switch_pipelined":
+            def down_slabs():
+                for s_ in range(b["slabs"]):
+                    m.stage_down_slab(b, s_)
+
+            def reduce_slabs():
+                for s_ in range(b["slabs"]):
+                    m.stage_reduce_slab(b, s_)
+            ps += [("down_gemm_slabs", down_slabs) + down,
+                   ("barrier_and_switch_reduce_slabs", reduce_slabs, 0, nv_bytes, "nvlink")]
+        elif proto == "switch_reduce":
+            ps += [("down_gemm", lambda: m.stage_down_local(b)) + down,
+                   ("barrier_partials", lambda: m.stage_barrier(b), 0, 0, "nvlink"),
+                   ("switch_reduce_owned_rows", lambda: m.stage_switch_reduce_owned(b), 0, nv_bytes, "nvlink")]
+        else:
+            scatter = proto == "add_owner"
+            ps += [("down_gemm_add_owner" if scatter else "down_gemm_add_all", lambda: m.stage_down_add(b)) + down,
+                   ("clear_next_output", lambda: m.stage_clear_next(b), 0, 2 * T * H // (self.world if scatter else 1), "hbm")]
+            if scatter:
+                ps += [("barrier_sums", lambda: m.stage_barrier(b), 0, 0, "nvlink"),
+                       ("broadcast_owned_rows", lambda: m.stage_broadcast_owned(b), 0, 2 * T * H * (self.world - 1) // self.world, "nvlink")]
+        ps.append(("barrier", finish, 0, 0, "nvlink"))
         return ps
+
+    def run_step(self):
+        return self.mlp(self.x)
 
     def reset(self):
         self.mlp.reset_peer_buffers()
@@ -504,16 +538,113 @@ class Fp8Mlp(Workload):
     def step_flops_global(self):
         return 3 * 2 * self.T * self.H * self.I
 
+    def parity_check(self):
+        """The step's result against independent routes, before anything is timed.  (1) A band of tokens recomputed
+        stage by stage through the plain entry points: RMSNorm+quantize, the gate/up GEMM with an f32 result, SwiGLU
+        and the row maximum in torch, tensorrt.quantize per row, the down GEMM with an f32 result, partial results
+        summed over the ranks by NCCL in f32.  (2) With several ranks, the whole result of the NCCL all-reduce
+        variant of the block on the same shards.  (3) Every rank holds the same bits.  (4) No kernel gave up a wait."""
+        import copy
+        import ctypes
+        torch, ql, dist, m = self.torch, self.ql, self.dist, self.mlp
+        y = self.run_step().clone()
+        torch.cuda.synchronize()
+        out = {"rows_checked_stage_by_stage": 0}
+        worst = 0.0
+        for r0 in (0, self.T - 128):
+            xb = self.x[r0:r0 + 128].contiguous()
+            xq, sx = ql.rmsnorm_quant_fp8(xb, 1e-5)
+            gu = ql.gemm_fp8(xq, m.wq_gu, sx, m.s_gu, out_dtype=ql.float32)
+            if m.fused_swiglu:
+                gu = gu.reshape(128, -1, 2, 32)
+                g_, u_ = gu[:, :, 0, :].reshape(128, -1), gu[:, :, 1, :].reshape(128, -1)
+            else:
+                gu = gu.to(torch.bfloat16).float()   # the row kernel reads the projection in the activation type
+                g_, u_ = gu[:, :self.il], gu[:, self.il:]
+            a = (torch.nn.functional.silu(g_) * u_)
+            a = a.to(torch.bfloat16).contiguous() if m.fused_swiglu else a.contiguous()
+            am = a.float().abs().amax(dim=1)
+            s_a = torch.div(am, torch.full_like(am, 448.0))   # tensor / tensor: an IEEE division (a Python scalar divisor becomes a reciprocal multiply)
+            s_a = torch.where(s_a == 0, torch.ones_like(s_a), s_a)
+            aq = torch.empty(a.shape, dtype=torch.float8_e4m3fn, device=a.device)
+            ql.quantize_to(a, s_a, aq, dim=0)
+            part = ql.gemm_fp8(aq, m.wq_d, s_a, m.s_d, out_dtype=ql.float32)
+            if dist is not None:
+                dist.all_reduce(part)
+            ref = part.double()
+            err = float((y[r0:r0 + 128].double() - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+            worst = max(worst, err)
+            out["rows_checked_stage_by_stage"] += 128
+        out["max_rel_vs_stage_by_stage"] = worst
+        ok = worst < 1e-2
+        if dist is not None and self.buf["protocol"] != "nccl":
+            plain = copy.copy(m)
+            plain.fused_all_reduce, plain._force, plain._buf, plain._comm = False, None, {}, None
+            y2 = plain(self.x)
+            e2 = float((y.double() - y2.double()).abs().max() / y2.double().abs().max().clamp_min(1e-30))
+            out["max_rel_vs_nccl_all_reduce"] = e2
+            ok = ok and e2 < 1e-2
+            del plain, y2
+        if dist is not None:
+            v = y.view(torch.int16).to(torch.int64)
+            sig = torch.stack([v.sum(), (v * torch.arange(1, v.shape[1] + 1, device=v.device)).sum()])
+            lo, hi = sig.clone(), sig.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            out["ranks_identical"] = bool(torch.equal(lo, hi))
+            ok = ok and out["ranks_identical"]
+        code = ctypes.c_int32(0)
+        rc = ql.lib().ql_gemm_status(ctypes.byref(code))
+        out["device_wait_status"] = int(code.value)
+        ok = ok and rc == 0
+        if dist is not None:
+            t = torch.tensor([1.0 if ok else 0.0, out["max_rel_vs_stage_by_stage"]], device=self.device, dtype=torch.float64)
+            agree, worst_all = t[:1].clone(), t[1:].clone()
+            dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+            dist.all_reduce(worst_all, op=dist.ReduceOp.MAX)
+            ok, out["max_rel_vs_stage_by_stage"] = bool(agree.item() > 0.5), float(worst_all)
+        out["max_rel"] = max(out["max_rel_vs_stage_by_stage"], out.get("max_rel_vs_nccl_all_reduce", 0.0))
+        out["ok"] = bool(ok)
+        self.reset()
+        return out
+
+    def compare(self, steps):
+        """Library kernel on the gate/up projection's operands, same box, same process (comparison only, never the
+        product path): cuBLASLt fp8 through torch._scaled_mm, per-tensor scales, bf16 result."""
+        torch = self.torch
+        out = {}
+        try:
+            b = self.buf
+            one = torch.tensor(1.0, device=self.device)
+            fn = lambda: torch._scaled_mm(b["xq"], self.mlp.wq_gu.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            for _ in range(3):
+                fn()
+            a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a_.record()
+            for _ in range(steps):
+                fn()
+            b_.record()
+            torch.cuda.synchronize()
+            ms = a_.elapsed_time(b_) / steps
+            out["cublaslt_fp8_gate_up_shape"] = {"ms": ms, "TFLOP/s": 2 * self.T * self.H * 2 * self.il / ms / 1e9}
+        except Exception as e:  # comparison is best effort
+            out["cublaslt_fp8_gate_up_shape"] = {"error": repr(e)[:200]}
+        return out
+
     def e2e_units(self, step):
         box = {}
 
         def run():
-            box["y"] = self.mlp(self.x)
-        return [(("x", 0), ("y", 0), (lambda: self.x.copy_(self.x_host, non_blocking=True)), run,
-                 (lambda: self.y_host.copy_(box["y"], non_blocking=True)))]
+            box["y"] = self.run_step()
+
+        def out():
+            r0 = self.rank * self.rows_out
+            self.y_host.copy_(box["y"][r0:r0 + self.rows_out], non_blocking=True)
+        return [(("x", 0), ("y", 0), (lambda: self.x.copy_(self.x_host, non_blocking=True)), run, out)]
 
     def e2e_bytes(self):
-        return self.T * self.H * 2, self.T * self.H * 2
+        return self.T * self.H * 2, self.rows_out * self.H * 2
 
     def config(self):
         return {"workload": self.name, "tokens": self.T, "hidden": self.H, "intermediate": self.I, "intermediate_per_gpu": self.il,
@@ -728,7 +859,7 @@ def run_reference_arm(args):
     value = sum(vals) / len(vals)
     ms = (time.perf_counter() - t0) * 1e3 / (args.steps + args.warmup)
     line = {"impl": "reference", "metric": wl.metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None,
             "dtype": wl.dtype, "data": "synthetic (seeded)",
             "config": dict(reference_config(wl, args.gpus), parallelism=f"{cores} host threads (OpenMP)", timing="wall clock",
                            arm="CPU restatement of the reference's host path (oracle/ql_oracle.c); the reference itself cannot "
@@ -741,14 +872,103 @@ def run_reference_arm(args):
 # ----------------------------------------------------------------------------------------------
 # the product arm
 # ----------------------------------------------------------------------------------------------
+def bind_to_gpu_numa_node(torch, local):
+    """Best effort: run this rank's host threads on the CPUs of the NUMA node its GPU hangs off, before any pinned
+    staging buffer is allocated (first touch then places the buffer on that node).  Reads sysfs only."""
+    info = {"bound": False}
+    try:
+        pr = torch.cuda.get_device_properties(local)
+        dev = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{dev}/numa_node") as f:
+            node = int(f.read().strip())
+        info["gpu_numa_node"] = node
+        if node < 0:
+            return info
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0)
+        use = cpus & allowed
+        info["allowed_cpus"] = len(allowed)
+        if use and use != allowed:
+            os.sched_setaffinity(0, use)
+            info["bound"] = True
+        info["cpus_on_node"] = len(use)
+    except Exception as e:  # topology unreadable: leave the affinity alone
+        info["error"] = repr(e)[:120]
+    return info
+
+
+def time_parts(torch, L, wl, parts, K, device, barrier):
+    """Each part on its own: K launches back to back (captured graphs, one launch per buffer rotation, where the
+    workload asks for graphs), CUDA events on the launching stream.  Returns milliseconds per launch."""
+    stream = torch.cuda.current_stream(device)
+    rot = getattr(wl, "REPLICAS", 1)
+    part_ms = []
+    for _, fn, _, _, _ in parts:
+        a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        if wl.use_graphs:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(rot):
+                    fn()
+            stream = torch.cuda.current_stream(device)
+            reps = max(1, (K + rot - 1) // rot)
+            g.replay()
+            barrier()
+            a_.record(stream)
+            for _ in range(reps):
+                g.replay()
+            b_.record(stream)
+            barrier()
+            part_ms.append(a_.elapsed_time(b_) / (reps * rot))
+        else:
+            a_.record(stream)
+            for _ in range(K):
+                fn()
+            b_.record(stream)
+            barrier()
+            part_ms.append(a_.elapsed_time(b_) / K)
+    return part_ms
+
+
+def peak_of(bound, peaks, lib_fp8=None):
+    """(bound name for the roofline object, peak, unit, where the peak comes from).  Parts are timed alone, a few
+    dozen launches back to back, so tensor-core parts are held against the burst figure."""
+    if bound == "tensor":
+        return "tensor", peaks["bf16_tflops"], "TFLOP/s", "measured cuBLAS bf16, burst"
+    if bound == "tensor_fp8":
+        note = "2 x measured cuBLAS bf16 burst (no fp8 peak is measured by the driver)"
+        if lib_fp8:
+            note += f"; cuBLASLt fp8 on the same operands in this process: {lib_fp8:.0f} TFLOP/s"
+        return "tensor", 2 * peaks["bf16_tflops"], "TFLOP/s", note
+    if bound == "nvlink":
+        return "nvlink", 770.0, "GB/s", "peer copy per direction measured on this pool (900 nominal)"
+    return "hbm", peaks["hbm_gbs"], "GB/s", "measured copy bandwidth"
+
+
+def part_table(parts, part_ms, peaks):
+    out = {}
+    for (nm, _, f, b, bd), ms in zip(parts, part_ms):
+        sec = ms * 1e-3
+        _, peak, unit, _ = peak_of(bd, peaks)
+        ach = (f / sec / 1e12) if unit == "TFLOP/s" else (b / sec / 1e9)
+        out[nm] = {"ms": ms, "GB/s": b / sec / 1e9, "TFLOP/s": f / sec / 1e12, "bound": bd, "frac": ach / peak if (f or b) else None}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra-parts", action="store_true", help="skip the config 1 / config 4 kernels added to `parts` at one GPU")
     ap.add_argument("--compare", action="store_true", help="also time library kernels on the same operands (comparison only)")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -768,6 +988,7 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    numa = bind_to_gpu_numa_node(torch, local)
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -785,9 +1006,24 @@ def main():
     L = ql.lib()
     K = args.steps
 
+    # -------- the result is checked before anything is timed
+    parity = None
+    if hasattr(wl, "parity_check"):
+        parity = wl.parity_check()
+        if not parity["ok"]:
+            if rank == 0:
+                print(json.dumps({"metric": wl.metric, "parity_check": parity, "error": "the step's result failed its parity check; nothing was timed"}),
+                      flush=True)
+            if dist is not None:
+                dist.destroy_process_group()
+            raise SystemExit(3)
+
     def run_step():
-        for _, fn, _, _, _ in parts:
-            fn()
+        if hasattr(wl, "run_step"):
+            wl.run_step()
+        else:
+            for _, fn, _, _, _ in parts:
+                fn()
 
     for _ in range(args.warmup):
         run_step()
@@ -796,9 +1032,9 @@ def main():
     # Optionally replay captured CUDA graphs, so that what is timed is the device work and not the
     # Python/ctypes launch path.  One graph per buffer rotation keeps every launch on cold data.
     rot = getattr(wl, "REPLICAS", 1)
-    step_graphs, part_graphs, launches_per_step = None, None, None
+    step_graphs, launches_per_step = None, None
     if wl.use_graphs:
-        step_graphs, part_graphs = [], [[] for _ in parts]
+        step_graphs = []
         for _ in range(rot):
             g = torch.cuda.CUDAGraph()
             c0 = L.ql_launch_count()
@@ -806,14 +1042,6 @@ def main():
                 run_step()
             launches_per_step = L.ql_launch_count() - c0
             step_graphs.append(g)
-        # per part: one graph holding `rot` launches, one per buffer rotation, so that launches sit back to
-        # back on the device as they do inside a real program's graph
-        for p, (_, fn, _, _, _) in enumerate(parts):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                for _ in range(rot):
-                    fn()
-            part_graphs[p] = g
         stream = torch.cuda.current_stream(device)
         for g in step_graphs:  # one untimed replay each
             g.replay()
@@ -838,28 +1066,11 @@ def main():
     total_ms = t_start.elapsed_time(t_end)
     launches = (launches_per_step * K) if step_graphs else (L.ql_launch_count() - launches0)
 
-    # -------- each part on its own (K launches back to back, rotating buffers): the roofline numbers
-    part_ms = []
-    for p, (_, fn, _, _, _) in enumerate(parts):
-        a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        if part_graphs:
-            reps = max(1, (K + rot - 1) // rot)
-            part_graphs[p].replay()
-            barrier()
-            a_.record(stream)
-            for _ in range(reps):
-                part_graphs[p].replay()
-            b_.record(stream)
-            barrier()
-            part_ms.append(a_.elapsed_time(b_) / (reps * rot))
-        else:
-            a_.record(stream)
-            for _ in range(K):
-                fn()
-            b_.record(stream)
-            barrier()
-            part_ms.append(a_.elapsed_time(b_) / K)
+    # -------- each part on its own: the roofline numbers
+    if hasattr(wl, "reset"):
+        wl.reset()
+    part_ms = time_parts(torch, L, wl, parts, K, device, barrier)
+    comparison = wl.compare(K) if hasattr(wl, "compare") and (args.compare or args.workload == "c5") else None
     clock_info = clocks.stop()
 
     # -------- end to end: inputs from pinned host memory, results read back, every step.  Copies in, kernels and
@@ -913,7 +1124,6 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms, e2e_ms, part_ms = float(t[0]), float(t[1]), [float(v) for v in t[2:]]
 
-    strong = wl.scaling == "strong"
     if hasattr(wl, "step_flops_global"):
         work = wl.step_flops_global()                      # whole job, however many GPUs share it
     else:
@@ -923,26 +1133,45 @@ def main():
     e2e_value = work * K / (e2e_ms * 1e-3) / denom
 
     peaks = measured_peaks()
+    lib_fp8 = None
+    if comparison:
+        for v in comparison.values():
+            if isinstance(v, dict) and "TFLOP/s" in v:
+                lib_fp8 = v["TFLOP/s"]
     dom = max(range(len(parts)), key=lambda p: part_ms[p])
     name, _, f, b, bound = parts[dom]
     sec = part_ms[dom] * 1e-3
-    if bound == "tensor":
-        achieved, peak, unit, note = f / sec / 1e12, peaks["bf16_tflops_sustained"], "TFLOP/s", "measured cuBLAS bf16, sustained"
-    elif bound == "tensor_fp8":
-        achieved, peak, unit, note = f / sec / 1e12, 2 * peaks["bf16_tflops_sustained"], "TFLOP/s", "2 x measured cuBLAS bf16 sustained (no fp8 peak was measured)"
-        bound = "tensor"
-    elif bound == "nvlink":
-        achieved, peak, unit, note = b / sec / 1e9, 770.0, "GB/s", "measured peer copy per direction"
-    else:
-        achieved, peak, unit, note = b / sec / 1e9, peaks["hbm_gbs"], "GB/s", "measured copy bandwidth"
-    roofline = {"kernel": f"{wl.name}:{name}", "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
+    rb, peak, unit, note = peak_of(bound, peaks, lib_fp8)
+    achieved = (f / sec / 1e12) if unit == "TFLOP/s" else (b / sec / 1e9)
+    roofline = {"kernel": f"{wl.name}:{name}", "bound": rb, "achieved": achieved, "peak": peak, "unit": unit,
                 "frac": achieved / peak, "peak_source": f"{peaks['source']}: {note}", "traffic": TRAFFIC.get(f"{wl.name}:{name}"),
                 "algorithmic_bytes_per_launch": b, "algorithmic_flops_per_launch": f, "avg_launch_ms": part_ms[dom]}
-    per_part = {}
-    for p, (nm, _, f, b, bd) in enumerate(parts):
-        sec = part_ms[p] * 1e-3
-        per_part[nm] = {"ms": part_ms[p], "GB/s": b / sec / 1e9, "TFLOP/s": f / sec / 1e12, "bound": bd,
-                        "frac_hbm_measured": b / sec / 1e9 / peaks["hbm_gbs"]}
+    if lib_fp8 and bound == "tensor_fp8":
+        roofline["frac_of_cublaslt_fp8"] = achieved / lib_fp8
+    per_part = part_table(parts, part_ms, peaks)
+
+    # -------- one GPU: the other two kinds of kernel of the path, timed the same way, as further entries of `parts`
+    if world == 1 and args.workload == "c5" and not args.no_extra_parts:
+        del wl.mlp, wl.buf
+        torch.cuda.empty_cache()
+        for key in ("c1", "c4"):
+            w2 = WORKLOADS[key](torch, ql, device, None)
+            p2 = w2.parts()
+            for _ in range(3):
+                for _, fn, _, _, _ in p2:
+                    fn()
+            ms2 = time_parts(torch, L, w2, p2, K, device, barrier)
+            for nm, row in part_table(p2, ms2, peaks).items():
+                row["traffic"] = TRAFFIC.get(f"{w2.name}:{nm}")
+                per_part[f"{w2.name}:{nm}"] = row
+            if key == "c4":
+                cmp4 = w2.compare(K)
+                lib4 = cmp4.get("cublaslt_fp8_scaled_mm", {}).get("TFLOP/s")
+                if lib4:
+                    per_part[f"{w2.name}:fp8_gemm"]["frac_of_cublaslt_fp8"] = per_part[f"{w2.name}:fp8_gemm"]["TFLOP/s"] / lib4
+                    comparison = dict(comparison or {}, cublaslt_fp8_config4_shape=cmp4["cublaslt_fp8_scaled_mm"])
+            del w2, p2
+            torch.cuda.empty_cache()
 
     if rank != 0:
         if dist is not None:
@@ -957,10 +1186,12 @@ def main():
                            timing="CUDA graph replay" if step_graphs else "direct launches"),
             "clocks": clock_info, "gpu_launches": int(launches),
             "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / K,
-                    "overlap": "uploads, kernels and read-backs on three streams, chained per buffer by events"},
+                    "overlap": "uploads, kernels and read-backs on three streams, chained per buffer by events", "host_numa": numa},
             "roofline": roofline, "parts": per_part}
-    if args.compare and hasattr(wl, "compare"):
-        line["comparison"] = wl.compare(K)
+    if parity is not None:
+        line["parity_check"] = parity
+    if comparison:
+        line["comparison"] = comparison
     if not args.no_cpu_baseline and world == 1:
         v, u, cores, sample = cpu_reference(args.workload)
         line["cpu_baseline"] = {"value": v, "unit": u, "cores": cores, "kind": "port", "sample": sample}

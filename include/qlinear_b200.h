@@ -217,12 +217,27 @@ QL_API int ql_matmul(const ql_tensor *a, const ql_tensor *b, ql_tensor *c, void 
  * q is e4m3, scale f32 [T]; row lengths must be multiples of 16. */
 QL_API int ql_rmsnorm_quant_fp8(const ql_tensor *x, float eps, ql_tensor *q, ql_tensor *scale, void *stream);
 QL_API int ql_swiglu_quant_fp8(const ql_tensor *gate_up, ql_tensor *q, ql_tensor *scale, void *stream);
+/* The same two steps with SwiGLU moved into the gate/up projection's epilogue, so that the [T, 2I] projection is
+ * never written to memory:
+ *   gemm_fp8_swiglu:   wq [2I, K] holds the gate and up weights interleaved in groups of 32 rows (rows [64b, 64b+32)
+ *                      = gate channels [32b, 32b+32), rows [64b+32, 64b+64) = up channels [32b, 32b+32)), sw (scalar
+ *                      or [2I]) in the same order.  act[t, i] = silu(g) * u with g, u the scaled f32 sums of channel
+ *                      i, rounded once to act's type (bf16 | f16); row_amax[t] = max_i |act[t, i]| (f32 [T],
+ *                      overwritten).  Needs K % 16 == 0 and 16-byte aligned operands (QL_ERR_UNSUPPORTED otherwise).
+ *   quantize_rows_fp8: tensorrt.quantize per row with the scale formed from row maxima: scale[t] = row_amax[t] / 448
+ *                      (1 for an all-zero row), q = e4m3(a / scale[t]).  a [T, I] bf16 | f16, I % 16 == 0. */
+QL_API int ql_gemm_fp8_swiglu(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx, const ql_tensor *sw,
+                              ql_tensor *act, ql_tensor *row_amax, void *stream);
+QL_API int ql_quantize_rows_fp8(const ql_tensor *a, const ql_tensor *row_amax, ql_tensor *q, ql_tensor *scale, void *stream);
 
 /* The tensor-core kernels bound every on-device wait (mbarrier, tensor-memory hand-over) by a
  * cycle limit; a kernel that runs out records a code and returns early instead of hanging.  This
  * call synchronises the device, returns QL_ERR_DEVICE_TIMEOUT if a code was recorded since the
  * last call (and clears it), and stores the code in *code when code is not null. */
 QL_API int ql_gemm_status(int32_t *code);
+/* Diagnostics: the library reads its QL_* tuning variables from the environment once, at the first GEMM of the
+ * process; this makes it read them again (not thread-safe against GEMM calls in flight on other host threads). */
+QL_API int ql_reload_tuning(void);
 
 #ifdef __cplusplus
 }

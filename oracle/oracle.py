@@ -56,6 +56,7 @@ def lib():
         L.orc_gemm_i8.argtypes = [vp, vp, vp, i64, vp, i64, i64, i64, i64, vp, ci]
         L.orc_rmsnorm_quant_fp8.argtypes = [vp, ci, i64, i64, f, vp, vp]
         L.orc_swiglu_quant_fp8.argtypes = [vp, ci, i64, i64, vp, vp]
+        L.orc_swiglu_interleaved.argtypes = [vp, i64, i64, vp, ci, vp]
         L.orc_f32_to_f8e4m3.argtypes = [f]
         L.orc_f32_to_f8e4m3.restype = ctypes.c_uint8
         L.orc_f8e4m3_to_f32.argtypes = [ctypes.c_uint8]
@@ -312,6 +313,32 @@ def swiglu_quant_fp8(GU, x_code):
     s = np.zeros(M, dtype=np.float32)
     lib().orc_swiglu_quant_fp8(_ptr(np.ascontiguousarray(GU)), x_code, M, I2 // 2, _ptr(Q), _ptr(s))
     return Q, s
+
+
+def interleave_gate_up(gate, up):
+    """Rows of `gate` and `up` ([I, ...] each, I a multiple of 32) interleaved in groups of 32: the weight layout of
+    the gate/up projection whose epilogue applies SwiGLU."""
+    I = gate.shape[0]
+    rest = gate.shape[1:]
+    return np.ascontiguousarray(np.stack([gate.reshape((I // 32, 32) + rest), up.reshape((I // 32, 32) + rest)], axis=1).reshape((2 * I,) + rest))
+
+
+def gemm_fp8_swiglu(Xq, Wq, sx, sw, y_code=BF16, acc64=True):
+    """(act, row_amax) of the gate/up projection with interleaved weights `Wq` [2I, K] and SwiGLU applied to the
+    unrounded f32 projection; act [M, I] of type y_code, row_amax f32 [M]."""
+    gu = gemm_fp8(Xq, Wq, sx, sw, F32, acc64)
+    M, N = gu.shape
+    act = np.zeros((M, N // 2), dtype=_NP_OF[y_code])
+    am = np.zeros(M, dtype=np.float32)
+    lib().orc_swiglu_interleaved(_ptr(gu), M, N, _ptr(act), y_code, _ptr(am))
+    return act, am
+
+
+def quantize_rows_fp8(act, code, row_amax):
+    """tensorrt.quantize per row with scale[t] = row_amax[t] / 448 (1 for an all-zero row): (q, scale)."""
+    s = (np.asarray(row_amax, dtype=np.float32) / np.float32(448.0)).astype(np.float32)
+    s[s == 0] = 1.0
+    return quantize(act, code, s, F32, F8E4M3, PER_CHANNEL, 0), s
 
 
 def dynamic_quantize_nvfp4(x, x_code, double_quant_scale=1.0):

@@ -449,6 +449,27 @@ int orc_swiglu_quant_fp8(const void *GU, int x_dtype, int64_t M, int64_t I, uint
   return 0;
 }
 
+/* SwiGLU over a gate/up projection whose columns are interleaved in groups of 32 (columns [64b, 64b+32) = gate
+ * channels [32b, 32b+32), columns [64b+32, 64b+64) = the up channels of the same indices), as the fused epilogue of
+ * the gate/up GEMM sees them: act[m, i] = silu(g) * u from the unrounded f32 projection, rounded once to y_dtype;
+ * row_amax[m] = max_i |act[m, i]| over the rounded values.  (Not a reference operator: the composition
+ * logistic / multiply of a StableHLO program for the block.) */
+int orc_swiglu_interleaved(const float *GU, int64_t M, int64_t N, void *act, int y_dtype, float *row_amax) {
+  const int64_t I = N / 2;
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; m++) {
+    float mx = 0.0f;
+    for (int64_t i = 0; i < I; i++) {
+      const int64_t col = (i / 32) * 64 + (i % 32);
+      const float a = round_to(orc_silu_mul(GU[m * N + col], GU[m * N + col + 32]), y_dtype);
+      store_from_f32(act, y_dtype, m * I + i, a);
+      if (fabsf(a) > mx) mx = fabsf(a);
+    }
+    row_amax[m] = mx;
+  }
+  return 0;
+}
+
 /* ---- NVFP4 (tensorrt.dynamic_quantize, tensorrt/include/mlir-tensorrt-dialect/TensorRT/IR/TensorRTOps.td:3279-3358):
  * blocks of 16 along the last axis; block scale = max|x| / 6 divided by the per-tensor "double quantization" scale
  * and rounded to e4m3; data = x / (e4m3 scale * double_quant_scale) rounded to e2m1 (values 0, 0.5, 1, 1.5, 2, 3, 4, 6

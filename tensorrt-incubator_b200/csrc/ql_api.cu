@@ -352,8 +352,10 @@ int ql_linear_w8a16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *sca
                      "%s: For per-channel quantization, expected the scales tensor dimension to match the "
                      "quantization axis dimension of input tensor", op);
   if (K % 64 != 0) return set_error(QL_ERR_UNSUPPORTED, "%s: K must be a multiple of 64 (got %lld)", op, (long long)K);
-  int fused_max = kFusedWidenMaxRows;
-  if (const char *e = getenv("QL_W8_FUSED_MAX_M")) fused_max = atoi(e); // tuning aid
+  static const int fused_max = [] { // tuning aid, read once per process
+    const char *e = getenv("QL_W8_FUSED_MAX_M");
+    return e ? atoi(e) : kFusedWidenMaxRows;
+  }();
   if (M > fused_max)
     return launch_w8a16_widen(x->dtype, x->data, w->data, scale->data, scale->dtype, y->data, (int)M, (int)N, (int)K,
                               (cudaStream_t)stream);

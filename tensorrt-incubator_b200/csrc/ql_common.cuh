@@ -171,6 +171,11 @@ __device__ __forceinline__ uint32_t quant_f8_pair(float q0, float q1, int fp8_mo
   return f32x2_to_e4m3x2(r0, r1);
 }
 
+// silu(g) * u.  SiLU is not a reference operator and no rounding of it is specified, so it uses the hardware's fast
+// exponential and reciprocal (a few ulp; the quantize step that follows is the exact one): the kernel is bound by
+// instruction issue, and the exact expf + division cost three times as many instructions.
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

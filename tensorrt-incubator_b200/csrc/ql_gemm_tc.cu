@@ -36,16 +36,17 @@ struct Tuning {
   bool one_cta, two_kernels, not_cooperative;
   int group_m;
 };
-const Tuning &tuning() {
-  static const Tuning t = [] {
-    Tuning v;
-    v.one_cta = getenv("QL_GEMM_ONE_CTA") != nullptr;
-    v.two_kernels = getenv("QL_W8_TWO_KERNELS") != nullptr;
-    v.not_cooperative = getenv("QL_W8_NOT_COOPERATIVE") != nullptr;
-    const char *e = getenv("QL_GEMM_GROUP_M");
-    v.group_m = e ? atoi(e) : 0;
-    return v;
-  }();
+Tuning read_tuning() {
+  Tuning v;
+  v.one_cta = getenv("QL_GEMM_ONE_CTA") != nullptr;
+  v.two_kernels = getenv("QL_W8_TWO_KERNELS") != nullptr;
+  v.not_cooperative = getenv("QL_W8_NOT_COOPERATIVE") != nullptr;
+  const char *e = getenv("QL_GEMM_GROUP_M");
+  v.group_m = e ? atoi(e) : 0;
+  return v;
+}
+Tuning &tuning() {
+  static Tuning t = read_tuning();
   return t;
 }
 constexpr int A_STAGE_BYTES = BM * BK_BYTES;
@@ -66,6 +67,7 @@ struct GemmArgs {
   int tiles_m, tiles_n;
   int group_m;     // m-tiles per scheduling group (see tile_coords)
   int *status;
+  float *row_amax; // non-null: SwiGLU epilogue (see swiglu_chunk); max|result| of every row is merged in here
   int64_t ldy;     // elements between rows of Y (N, or the full width when Y is a column slice)
   int peer_mode;   // QL_PEER_*: how the epilogue writes Y
   int rows_per_rank;               // QL_PEER_ADD_OWNER: rows [r * rows_per_rank, ...) belong to rank r
@@ -235,6 +237,55 @@ __device__ __forceinline__ void emit_chunk(const GemmArgs &args, OutT *Y, bool v
   }
 }
 
+// SwiGLU epilogue of a gate/up projection whose weight rows are interleaved in groups of 32 (rows [64b, 64b + 32) =
+// gate channels [32b, 32b + 32), rows [64b + 32, 64b + 64) = the up channels of the same indices): the two
+// accumulator chunks of a thread hold gate and up of the same 32 channels, so a = silu(gate) * up is formed in
+// registers and written once, in the output type, to Y[m, 32b ..] (Y has N / 2 columns).  The row maximum of the
+// rounded values is kept in `rmax` for the per-token scale of the quantize step that follows.
+template <typename OutT>
+__device__ __forceinline__ void swiglu_chunk(const GemmArgs &args, OutT *Y, bool vec_ok, uint32_t taddr, int m, int n, float sa,
+                                             float sb_scalar, float &rmax) {
+  uint32_t r[32];
+  float s[32], g[32];
+  load_chunk_scales(args, n, sa, sb_scalar, s);
+  tmem_load_32(taddr, r);
+#pragma unroll
+  for (int j = 0; j < 32; j++) g[j] = __uint_as_float(r[j]) * s[j];
+  load_chunk_scales(args, n + 32, sa, sb_scalar, s);
+  tmem_load_32(taddr + 32, r);
+  if (!(m < args.M && n < args.N)) return;
+  uint32_t w[16];
+#pragma unroll
+  for (int j = 0; j < 32; j += 2) {
+    const float a0 = silu_mul(g[j], __uint_as_float(r[j]) * s[j]), a1 = silu_mul(g[j + 1], __uint_as_float(r[j + 1]) * s[j + 1]);
+    w[j >> 1] = pack2<OutT>(a0, a1);
+    const OutT *h = reinterpret_cast<const OutT *>(&w[j >> 1]);
+    rmax = fmaxf(rmax, fmaxf(fabsf(FloatIO<OutT>::to_f32(h[0])), fabsf(FloatIO<OutT>::to_f32(h[1]))));
+  }
+  OutT *row = Y + (size_t)m * (size_t)args.ldy + (n >> 1);
+  if (vec_ok) {
+#pragma unroll
+    for (int j = 0; j < 16; j += 4) __stcs(reinterpret_cast<uint4 *>(row) + (j >> 2), make_uint4(w[j], w[j + 1], w[j + 2], w[j + 3]));
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      const OutT *h = reinterpret_cast<const OutT *>(&w[j]);
+      row[2 * j] = h[0];
+      row[2 * j + 1] = h[1];
+    }
+  }
+}
+
+// The whole accumulator of one tile (BN columns from tensor-memory address taddr) through swiglu_chunk.
+template <int BN, typename OutT>
+__device__ __forceinline__ void swiglu_tile(const GemmArgs &args, OutT *Y, bool vec_ok, uint32_t taddr, int m, int n0, float sa, float sb_scalar) {
+  float rmax = 0.f;
+#pragma unroll 1
+  for (int c = 0; c < BN / 64; c++) swiglu_chunk<OutT>(args, Y, vec_ok, taddr + c * 64, m, n0 + c * 64, sa, sb_scalar, rmax);
+  // non-negative floats order like their bit patterns
+  if (m < args.M && rmax > 0.f) atomicMax(reinterpret_cast<int *>(args.row_amax) + m, __float_as_int(rmax));
+}
+
 template <int BN> struct SmemLayout {
   static constexpr int kBStage = BN * BK_BYTES;
   static constexpr int kStage = A_STAGE_BYTES + kBStage;
@@ -374,8 +425,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (args.sa) sa = (args.sa_n == 1) ? __ldg(args.sa) : (m < args.M ? __ldg(args.sa + m) : 0.f);
       const float sb_scalar = (args.sb && args.sb_n == 1) ? load_scale(args.sb, args.sb_dtype, 0) : 1.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
+      bool fused = false;
+      if constexpr (KIND == KIND_F8 && sizeof(OutT) == 2 && BN >= 64) {
+        if (args.row_amax) {
+          swiglu_tile<BN, OutT>(args, Y, vec_ok, taddr, m, n0, sa, sb_scalar);
+          fused = true;
+        }
+      }
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
+      for (int c = 0; c < (fused ? 0 : BN / 32); c++) {
         uint32_t r[32];
         float sc[32];
         const int n = n0 + c * 32;
@@ -701,8 +759,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       if (args.sa) sa = (args.sa_n == 1) ? __ldg(args.sa) : (m < args.M ? __ldg(args.sa + m) : 0.f);
       const float sb_scalar = (args.sb && args.sb_n == 1) ? load_scale(args.sb, args.sb_dtype, 0) : 1.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN2);
+      bool fused = false;
+      if constexpr (KIND == KIND_F8 && sizeof(OutT) == 2 && !PEER && !WIDEN) {
+        if (args.row_amax) {
+          swiglu_tile<BN2, OutT>(args, Y, vec_ok, taddr, m, n0, sa, sb_scalar);
+          fused = true;
+        }
+      }
 #pragma unroll 1
-      for (int c = 0; c < BN2 / 32; c++) {
+      for (int c = 0; c < (fused ? 0 : BN2 / 32); c++) {
         uint32_t r[32];
         float sc[32];
         const int n = n0 + c * 32;
@@ -861,6 +926,7 @@ int launch_gemm_kind(const void *A, const void *B, GemmArgs args, int64_t K, cud
     if ((int64_t)args.tiles_m * ((args.N + cand - 1) / cand) >= sms) { bn = cand; break; }
   }
   if (args.N <= 32) bn = 32;
+  if (args.row_amax && bn < 64) bn = 64; // the SwiGLU epilogue pairs two 32-column chunks
   CUtensorMap ma, mb;
   int rc;
   if ((rc = make_map(&ma, KIND, A, args.M, K, BM)) != QL_OK) return rc;
@@ -935,11 +1001,12 @@ int run_simt(const ql_tensor *a, const ql_tensor *b, const ql_tensor *sa, const 
 template <int KIND>
 int run_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_tensor *sa, const ql_tensor *sb, const ql_tensor *bias,
              ql_tensor *y, void *stream, int64_t ldy = 0, int peer_mode = QL_PEER_NONE, const ql_peer_buffer *dest = nullptr,
-             int64_t offset = 0) {
+             int64_t offset = 0, float *row_amax = nullptr) {
   const int64_t M = a->shape[0], K = a->shape[1], N = b->shape[0];
   if (M == 0 || N == 0) return QL_OK;
   const int esize = (KIND == KIND_F8 || KIND == KIND_I8) ? 1 : 2;
   if (!tensor_core_ok<KIND>(a, b, y)) {
+    if (row_amax) return QL_ERR_UNSUPPORTED; // the caller says so in its own words
     if (peer_mode != QL_PEER_NONE)
       return set_error(QL_ERR_UNSUPPORTED, "%s: peer modes need K * element size to be a non-zero multiple of 16 bytes (K=%lld) and aligned operands",
                        op, (long long)K);
@@ -982,6 +1049,8 @@ int run_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_te
   }
   args.status = device_status_word();
   if (!args.status) return set_error(QL_ERR_CUDA, "%s: could not allocate the device status word", op);
+  args.row_amax = row_amax;
+  if (row_amax) args.ldy = N / 2;
   cudaStream_t st = (cudaStream_t)stream;
   if (y->dtype == QL_BF16) return launch_gemm_kind<KIND, __nv_bfloat16>(a->data, b->data, args, K, st);
   if (y->dtype == QL_F16) return launch_gemm_kind<KIND, __half>(a->data, b->data, args, K, st);
@@ -1033,6 +1102,7 @@ int gemm16_widen_t(const void *X, const void *Wraw, void *wide, int *counters, c
   args.rows_per_rank = 1;
   for (int r = 0; r < QL_MAX_PEERS; r++) args.owner_y[r] = nullptr;
   args.status = device_status_word();
+  args.row_amax = nullptr;
   if (!args.status) return set_error(QL_ERR_CUDA, "linear_w8a16: could not allocate the device status word");
   WidenArgs w;
   w.raw = static_cast<const uint8_t *>(Wraw);
@@ -1091,6 +1161,28 @@ int ql_gemm_fp8_peer(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *
       if (!dest->replica[r]) return set_error(QL_ERR_INVALID_ARGUMENT, "gemm_fp8_peer: replica %d has no address", r);
   }
   return run_gemm<KIND_F8>("gemm_fp8_peer", xq, wq, sx, sw, nullptr, &y, stream, ldy, peer_mode, dest, offset);
+}
+
+// Gate/up projection of a gated MLP with SwiGLU done by the epilogue; see include/qlinear_b200.h.
+int ql_gemm_fp8_swiglu(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx, const ql_tensor *sw, ql_tensor *act,
+                       ql_tensor *row_amax, void *stream) {
+  const char *op = "gemm_fp8_swiglu";
+  if (!xq || !wq || !act || !row_amax) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: null tensor", op);
+  if (act->rank != 2 || wq->rank != 2 || act->shape[1] * 2 != wq->shape[0])
+    return set_error(QL_ERR_INVALID_ARGUMENT, "%s: act must be [M, N/2] for interleaved gate/up weights [N, K]", op);
+  if (!(act->dtype == QL_BF16 || act->dtype == QL_F16)) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: act must be bf16 or f16", op);
+  if (wq->shape[0] % 64 != 0) return set_error(QL_ERR_UNSUPPORTED, "%s: N (%lld) must be a multiple of 64 (gate and up interleaved in groups of 32)", op, (long long)wq->shape[0]);
+  ql_tensor y{act->data, act->dtype, 2, {act->shape[0], wq->shape[0]}}; // the GEMM's logical result, never materialised
+  int rc = check_gemm(op, xq, wq, sx, sw, nullptr, &y, QL_F8E4M3, QL_F8E4M3);
+  if (rc != QL_OK) return rc;
+  if (row_amax->dtype != QL_F32 || row_amax->rank != 1 || row_amax->shape[0] != act->shape[0] || (!row_amax->data && act->shape[0] > 0))
+    return set_error(QL_ERR_INVALID_ARGUMENT, "%s: row_amax must be f32 [M]", op);
+  if (act->shape[0] == 0 || act->shape[1] == 0) return QL_OK;
+  QL_CUDA_TRY(cudaMemsetAsync(row_amax->data, 0, sizeof(float) * (size_t)act->shape[0], (cudaStream_t)stream));
+  rc = run_gemm<KIND_F8>(op, xq, wq, sx, sw, nullptr, &y, stream, 0, QL_PEER_NONE, nullptr, 0, static_cast<float *>(row_amax->data));
+  if (rc == QL_ERR_UNSUPPORTED)
+    return set_error(QL_ERR_UNSUPPORTED, "%s: needs K (%lld) to be a non-zero multiple of 16 and 16-byte aligned operands", op, (long long)xq->shape[1]);
+  return rc;
 }
 
 int ql_gemm_i8(const ql_tensor *xq, const ql_tensor *wq, const ql_tensor *sx, const ql_tensor *sw, ql_tensor *y, void *stream) {
@@ -1161,6 +1253,12 @@ int ql_matmul(const ql_tensor *a, const ql_tensor *b, ql_tensor *c, void *stream
   if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX || batch > INT32_MAX) return set_error(QL_ERR_UNSUPPORTED, "%s: dimension too large", op);
   return launch_gemm_simt(a->dtype, a->data, b->data, nullptr, 1, nullptr, 1, nullptr, QL_F32, c->data, c->dtype, (int)batch, (int)M, (int)N,
                           (int)K, K, 1, N, 1, N, a_lead == 1 ? 0 : M * K, b_lead == 1 ? 0 : K * N, M * N, (cudaStream_t)stream);
+}
+
+// Re-reads the QL_* tuning variables (they are otherwise read once, at the first GEMM of the process).
+int ql_reload_tuning(void) {
+  tuning() = read_tuning();
+  return QL_OK;
 }
 
 // Last status code a GEMM kernel recorded on the current device (0 = none); synchronises the device.

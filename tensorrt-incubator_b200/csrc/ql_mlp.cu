@@ -83,11 +83,6 @@ rmsnorm_quant_fp8_kernel(const XT *__restrict__ X, uint8_t *__restrict__ Q, floa
   }
 }
 
-// silu(g) * u.  SiLU is not a reference operator and no rounding of it is specified, so it uses the hardware's fast
-// exponential and reciprocal (a few ulp; the quantize step that follows is the exact one): the kernel is bound by
-// instruction issue, and the exact expf + division cost three times as many instructions.
-__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
-
 // One block per token.  GU holds [gate | up] (I columns each); a = silu(gate) * up in f32;
 // s = max|a| / 448; q = e4m3(a / s).  The f32 products of the first pass are parked in shared
 // memory (kCache) so that expf runs once per element; rows too long for that are recomputed.
@@ -153,6 +148,28 @@ swiglu_quant_fp8_kernel(const XT *__restrict__ GU, uint8_t *__restrict__ Q, floa
   }
 }
 
+// q[t, :] = e4m3(a[t, :] / s[t]) with s[t] = amax[t] / 448 (1 where the row is all zero): tensorrt.quantize per
+// channel along axis 0 with the scale formed on the fly from row maxima that an earlier kernel left in `amax`
+// (the SwiGLU epilogue of the gate/up projection).  16 values per thread: 32 bytes in, 16 bytes out.
+template <typename XT>
+__global__ void __launch_bounds__(256) quantize_rows_fp8_kernel(const XT *__restrict__ A, const float *__restrict__ amax, uint8_t *__restrict__ Q,
+                                                                float *__restrict__ S, int64_t n_chunks, int chunks_per_row) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < n_chunks; c += stride) {
+    const int64_t row = c / chunks_per_row;
+    float s = __fdiv_rn(__ldg(amax + row), 448.f);
+    if (s == 0.f) s = 1.f;
+    if (c - row * chunks_per_row == 0) S[row] = s;
+    float v[16];
+    load_vec_f32<XT, 16>(A + c * 16, v);
+    uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; j += 2)
+      w[j >> 2] |= (f32x2_to_e4m3x2(__fdiv_rn(v[j], s), __fdiv_rn(v[j + 1], s)) & 0xFFFFu) << (8 * (j & 3));
+    __stcs(reinterpret_cast<uint4 *>(Q) + c, make_uint4(w[0], w[1], w[2], w[3]));
+  }
+}
+
 template <typename XT>
 int launch_swiglu(const void *gu, void *q, void *s, int64_t T, int64_t I, cudaStream_t st) {
   const size_t cache_bytes = (size_t)I * sizeof(float);
@@ -207,6 +224,31 @@ int ql_rmsnorm_quant_fp8(const ql_tensor *x, float eps, ql_tensor *q, ql_tensor 
     rmsnorm_quant_fp8_kernel<__nv_bfloat16><<<(unsigned)T, kRowThreads, 0, st>>>(static_cast<const __nv_bfloat16 *>(x->data), static_cast<uint8_t *>(q->data), static_cast<float *>(scale->data), (int)H, eps);
   else
     rmsnorm_quant_fp8_kernel<__half><<<(unsigned)T, kRowThreads, 0, st>>>(static_cast<const __half *>(x->data), static_cast<uint8_t *>(q->data), static_cast<float *>(scale->data), (int)H, eps);
+  count_launches(1);
+  QL_CUDA_TRY(cudaGetLastError());
+  return QL_OK;
+}
+
+int ql_quantize_rows_fp8(const ql_tensor *a, const ql_tensor *row_amax, ql_tensor *q, ql_tensor *scale, void *stream) {
+  const char *op = "quantize_rows_fp8";
+  if (!a || !row_amax) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: null tensor", op);
+  int rc = check_rows(op, a, q, scale, a->rank == 2 ? a->shape[1] : 0, a->rank == 2 ? a->shape[1] : 0);
+  if (rc != QL_OK) return rc;
+  if (row_amax->dtype != QL_F32 || row_amax->rank != 1 || row_amax->shape[0] != a->shape[0] || (!row_amax->data && a->shape[0] > 0))
+    return set_error(QL_ERR_INVALID_ARGUMENT, "%s: row_amax must be f32 [T]", op);
+  const int64_t T = a->shape[0], I = a->shape[1];
+  if (T == 0 || I == 0) return QL_OK;
+  const int64_t n_chunks = T * (I / 16);
+  int64_t blocks = (n_chunks + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (a->dtype == QL_BF16)
+    quantize_rows_fp8_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(a->data), static_cast<const float *>(row_amax->data),
+                                                                            static_cast<uint8_t *>(q->data), static_cast<float *>(scale->data), n_chunks, (int)(I / 16));
+  else
+    quantize_rows_fp8_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const __half *>(a->data), static_cast<const float *>(row_amax->data),
+                                                                     static_cast<uint8_t *>(q->data), static_cast<float *>(scale->data), n_chunks, (int)(I / 16));
   count_launches(1);
   QL_CUDA_TRY(cudaGetLastError());
   return QL_OK;

@@ -6,5 +6,6 @@ from .linear import Linear, gemm_16, gemm_fp8, gemm_i8, linear, linear_w4a16, li
 from .ops import (QuantizeError, amax_scale, cast, dequantize, dequantize_nvfp4, dynamic_quantize, quantize,  # noqa: F401
                   quantize_dequantize, quantize_to)
 from .tensor import Float4Tensor, Int4Tensor  # noqa: F401
-from .mlp import QuantizedMLP, quantize_per_channel_fp8, rmsnorm_quant_fp8, shard_range, swiglu_quant_fp8  # noqa: F401
+from .mlp import (QuantizedMLP, gemm_fp8_swiglu, interleave_gate_up, quantize_per_channel_fp8, quantize_rows_fp8, rmsnorm_quant_fp8,  # noqa: F401
+                  shard_range, swiglu_quant_fp8)  # noqa: F401
 from . import peer, stablehlo  # noqa: F401,E402

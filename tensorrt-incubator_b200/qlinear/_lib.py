@@ -81,6 +81,9 @@ SIGNATURES = {
     "ql_set_peer_wait_limit": ([ctypes.c_int64], ctypes.c_int),
     "ql_rmsnorm_quant_fp8": ([_T, ctypes.c_float, _T, _T, _S], ctypes.c_int),
     "ql_swiglu_quant_fp8": ([_T, _T, _T, _S], ctypes.c_int),
+    "ql_gemm_fp8_swiglu": ([_T, _T, _T, _T, _T, _T, _S], ctypes.c_int),
+    "ql_quantize_rows_fp8": ([_T, _T, _T, _T, _S], ctypes.c_int),
+    "ql_reload_tuning": ([], ctypes.c_int),
     "ql_gemm_status": ([ctypes.POINTER(ctypes.c_int32)], ctypes.c_int),
 }
 

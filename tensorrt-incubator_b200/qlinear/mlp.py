@@ -59,26 +59,65 @@ def swiglu_quant_fp8(gate_up: torch.Tensor, q=None, scale=None):
     return q, scale
 
 
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """[2I, H]: rows of the gate and up projections interleaved in groups of 32 (rows [64b, 64b+32) = gate channels
+    [32b, 32b+32), rows [64b+32, 64b+64) = the up channels of the same indices), the layout ql_gemm_fp8_swiglu takes."""
+    I, H = w_gate.shape
+    return torch.stack([w_gate.reshape(I // 32, 32, H), w_up.reshape(I // 32, 32, H)], dim=1).reshape(2 * I, H).contiguous()
+
+
+def gemm_fp8_swiglu(xq, wq_gu, sx, s_gu, act, row_amax):
+    """act = silu(gate) * up of the gate/up projection (interleaved weights), formed in the GEMM's epilogue;
+    row_amax[t] = max|act[t, :]|."""
+    _lib.check(_lib.lib().ql_gemm_fp8_swiglu(ql_view(xq), ql_view(wq_gu), ql_view(sx), ql_view(s_gu), ql_view(act), ql_view(row_amax),
+                                             current_stream(xq.device)))
+    return act, row_amax
+
+
+def quantize_rows_fp8(act, row_amax, q=None, scale=None):
+    """Per-token e4m3 quantize with scale = row_amax / 448: (q, scale)."""
+    T, I = act.shape
+    q = q if q is not None else torch.empty((T, I), dtype=torch.float8_e4m3fn, device=act.device)
+    scale = scale if scale is not None else torch.empty((T,), dtype=torch.float32, device=act.device)
+    _lib.check(_lib.lib().ql_quantize_rows_fp8(ql_view(act), ql_view(row_amax), ql_view(q), ql_view(scale), current_stream(act.device)))
+    return q, scale
+
+
 class QuantizedMLP:
     """One rank's shard of the block.  `w_gate`, `w_up`: [inter_local, hidden]; `w_down`: [hidden, inter_local]
     (bf16 / f16, Linear's [out, in] layout).  Weights are quantized once, here."""
 
     def __init__(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, eps: float = 1e-5, group=None,
-                 fused_all_reduce="auto"):
+                 fused_all_reduce="auto", fused_swiglu="auto"):
         """`fused_all_reduce`: True = the down projection's epilogue does the reduction over peer memory
         (qlinear.peer): with two ranks the epilogue adds its partial result into both outputs; with more it adds
         each row into the output of the rank that owns the row, and the owners broadcast.  False = NCCL all-reduce after the GEMM;
-        "auto" = over peer memory when the box supports it and the group has several ranks; "scatter" / "switch"
-        = a given protocol whatever the group size (see _buffers)."""
+        "auto" = over peer memory when the box supports it and the group has several ranks; "scatter" / "switch" /
+        "pipeline" = a given protocol whatever the group size (see _buffers).
+
+        With a peer protocol the result is this rank's replica of an internal two-buffer set: it stays valid until
+        the call after next starts (the next call clears or overwrites the other buffer, the one after that this
+        one).  Copy it if it must live longer.  The NCCL path returns an internal buffer that the next call
+        overwrites."""
         self.eps, self.group = eps, group
-        self._force = fused_all_reduce if fused_all_reduce in ("scatter", "switch") else None   # a protocol on any group size
+        self._force = fused_all_reduce if fused_all_reduce in ("scatter", "switch", "pipeline") else None   # a protocol on any group size
+        self.slabs = 4        # token slabs of the pipelined protocol
+        self._comm = None     # side stream of the pipelined protocol
         if fused_all_reduce == "auto":
             fused_all_reduce = group is not None and peer.available(group)
         self.fused_all_reduce = bool(fused_all_reduce) and group is not None
         self._step = 0
         self.hidden, self.inter_local = w_gate.shape[1], w_gate.shape[0]
         self.out_dtype = dt.from_torch(w_gate.dtype)
-        self.wq_gu, self.s_gu = quantize_per_channel_fp8(torch.cat([w_gate, w_up], dim=0).contiguous())
+        # SwiGLU in the gate/up projection's epilogue (the [T, 2I] projection is never written) wherever the shapes
+        # allow it: weight rows interleaved in groups of 32, K a multiple of 16 bytes.  Otherwise the projection is
+        # written out, rounded to the activation type, and a row kernel applies SwiGLU and quantizes.
+        can_fuse = self.inter_local % 32 == 0 and self.hidden % 16 == 0
+        self.fused_swiglu = can_fuse if fused_swiglu == "auto" else (bool(fused_swiglu) and can_fuse)
+        if self.fused_swiglu:
+            self.wq_gu, self.s_gu = quantize_per_channel_fp8(interleave_gate_up(w_gate, w_up))
+        else:
+            self.wq_gu, self.s_gu = quantize_per_channel_fp8(torch.cat([w_gate, w_up], dim=0).contiguous())
         self.wq_d, self.s_d = quantize_per_channel_fp8(w_down.contiguous())
         self._buf = {}
 
@@ -88,7 +127,9 @@ class QuantizedMLP:
             od = self.out_dtype.torch
             self._buf = {"T": T,
                          "xq": torch.empty((T, H), dtype=torch.float8_e4m3fn, device=device), "sx": torch.empty((T,), dtype=torch.float32, device=device),
-                         "gu": torch.empty((T, 2 * I), dtype=od, device=device),
+                         "gu": None if self.fused_swiglu else torch.empty((T, 2 * I), dtype=od, device=device),
+                         "act": torch.empty((T, I), dtype=od, device=device) if self.fused_swiglu else None,
+                         "amax": torch.empty((T,), dtype=torch.float32, device=device) if self.fused_swiglu else None,
                          "aq": torch.empty((T, I), dtype=torch.float8_e4m3fn, device=device), "sa": torch.empty((T,), dtype=torch.float32, device=device),
                          "y": torch.empty((T, H), dtype=od, device=device)}
             world = 1
@@ -104,7 +145,17 @@ class QuantizedMLP:
             # (1.37 ms per step against 1.23 add_all and 1.31 add_owner), so it serves where rows do not split
             # into owner blocks of 128, or on request.
             owner_ok, switch_ok = world >= 2 and T % (128 * world) == 0, world >= 2 and T % world == 0
-            if self._force == "scatter" and owner_ok:
+            # "switch_pipelined": the down projection runs slab by slab over the tokens into the local replica; as soon
+            # as a slab's partial results are out, a side stream does that slab's barrier and in-switch reduction
+            # while the main stream computes the next slab, so only the last slab's exchange is exposed.
+            slabs = self.slabs
+            while slabs > 1 and T % (slabs * world * 8) != 0:
+                slabs //= 2
+            pipe_ok = switch_ok and slabs > 1
+            self._buf["slabs"] = slabs
+            if self._force == "pipeline" and pipe_ok:
+                self._buf["protocol"] = "switch_pipelined"
+            elif self._force == "scatter" and owner_ok:
                 self._buf["protocol"] = "add_owner"
             elif self._force == "switch" and switch_ok:
                 self._buf["protocol"] = "switch_reduce"
@@ -131,10 +182,16 @@ class QuantizedMLP:
         rmsnorm_quant_fp8(x, self.eps, b["xq"], b["sx"])
 
     def stage_gate_up(self, b):
-        gemm_fp8(b["xq"], self.wq_gu, b["sx"], self.s_gu, out_dtype=self.out_dtype, out=b["gu"])
+        if self.fused_swiglu:
+            gemm_fp8_swiglu(b["xq"], self.wq_gu, b["sx"], self.s_gu, b["act"], b["amax"])
+        else:
+            gemm_fp8(b["xq"], self.wq_gu, b["sx"], self.s_gu, out_dtype=self.out_dtype, out=b["gu"])
 
     def stage_swiglu_quant(self, b):
-        swiglu_quant_fp8(b["gu"], b["aq"], b["sa"])
+        if self.fused_swiglu:
+            quantize_rows_fp8(b["act"], b["amax"], b["aq"], b["sa"])
+        else:
+            swiglu_quant_fp8(b["gu"], b["aq"], b["sa"])
 
     def stage_down(self, b):
         gemm_fp8(b["aq"], self.wq_d, b["sa"], self.s_d, out_dtype=self.out_dtype, out=b["y"])
@@ -178,6 +235,40 @@ class QuantizedMLP:
         rows = b["T"] // y.world
         y.reduce_rows(y.rank * rows, rows)
 
+    # the pipelined switch protocol: one slab of tokens at a time
+    def stage_down_slab(self, b, s):
+        rows = b["T"] // b["slabs"]
+        sl = slice(s * rows, (s + 1) * rows)
+        gemm_fp8(b["aq"][sl], self.wq_d, b["sa"][sl], self.s_d, out_dtype=self.out_dtype, out=b["y_peer"][self._step % 2].local[sl])
+
+    def stage_reduce_slab(self, b, s):
+        """Barrier (every rank's partial results of slab `s` are in its replica), then the in-switch sum of the
+        rows of the slab this rank owns, written to every replica.  Runs on the current stream."""
+        y = b["y_peer"][self._step % 2]
+        rows = b["T"] // b["slabs"]
+        mine = rows // y.world
+        y.barrier()
+        y.reduce_rows(s * rows + y.rank * mine, mine)
+
+    def comm_stream(self, device):
+        if self._comm is None:
+            self._comm = torch.cuda.Stream(device, priority=-1)
+        return self._comm
+
+    def _forward_pipelined(self, b, device):
+        main, comm = torch.cuda.current_stream(device), self.comm_stream(device)
+        for s in range(b["slabs"]):
+            self.stage_down_slab(b, s)
+            done = main.record_event()
+            with torch.cuda.stream(comm):
+                comm.wait_event(done)
+                self.stage_reduce_slab(b, s)
+        main.wait_stream(comm)
+        self.stage_barrier(b)               # every rank's rows of every slab have been written everywhere
+        y = b["y_peer"][self._step % 2].local
+        self._step += 1
+        return y
+
     def reset_peer_buffers(self):
         """Zero both output buffers on every rank (after anything that added into them out of turn)."""
         for t in self._buf.get("y_peer", []):
@@ -190,6 +281,8 @@ class QuantizedMLP:
         self.stage_norm_quant(x, b)
         self.stage_gate_up(b)
         self.stage_swiglu_quant(b)
+        if b["protocol"] == "switch_pipelined":
+            return self._forward_pipelined(b, x.device)
         if b["protocol"] == "switch_reduce":
             self.stage_down_local(b)
             self.stage_barrier(b)           # every rank's partial result is in its own replica

@@ -31,7 +31,7 @@ import torch
 
 from . import _lib
 from . import dtypes as dt
-from . import linear as _linear
+from .linear import linear as _linear_nt, linear_w4a16 as _linear_w4a16, linear_w8a16 as _linear_w8a16
 from . import ops
 from .tensor import Float4Tensor, Int4Tensor, current_stream, empty_quantized, ql_view
 
@@ -374,13 +374,13 @@ class Program:
                 slots[st.out] = y
             elif st.op == "linear_w8a16":
                 x, q, s = ins
-                slots[st.out] = _linear.linear_w8a16(x.contiguous(), q, s.contiguous())
+                slots[st.out] = _linear_w8a16(x.contiguous(), q, s.contiguous())
             elif st.op == "linear_w4a16":
                 x, q, s = ins
-                slots[st.out] = _linear.linear_w4a16(x.contiguous(), q, s.contiguous())
+                slots[st.out] = _linear_w4a16(x.contiguous(), q, s.contiguous())
             elif st.op == "matmul16":
                 x, w = ins
-                slots[st.out] = _linear.gemm_16(x.contiguous(), w.contiguous())
+                slots[st.out] = _linear_nt(x.contiguous(), w.contiguous())
         outs = [slots[i] for i in self.result_slots]
         return outs[0] if len(outs) == 1 else tuple(outs)
 

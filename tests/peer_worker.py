@@ -114,9 +114,11 @@ def main():
     want = plain(x).clone()
     scattered = ql.QuantizedMLP(wg, wu, wd, group=dist.group.WORLD, fused_all_reduce="scatter")
     switched = ql.QuantizedMLP(wg, wu, wd, group=dist.group.WORLD, fused_all_reduce="switch")
+    piped = ql.QuantizedMLP(wg, wu, wd, group=dist.group.WORLD, fused_all_reduce="pipeline")
+    assert piped.protocol(T, dev) == "switch_pipelined"
     assert fused.protocol(T, dev) == ("add_all" if world == 2 else "add_owner")
     assert scattered.protocol(T, dev) == "add_owner" and switched.protocol(T, dev) == "switch_reduce"
-    for name, mlp in (("auto", fused), ("add-owner", scattered), ("switch", switched)):
+    for name, mlp in (("auto", fused), ("add-owner", scattered), ("switch", switched), ("switch, pipelined over token slabs", piped)):
         for i in range(3):
             got = mlp(x)
             torch.cuda.synchronize()

@@ -21,6 +21,7 @@ def test_fused_collectives_all_gpus_of_the_box():
            "--master-port", "29571", os.path.join(ROOT, "tests", "peer_worker.py")]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     out = r.stdout + r.stderr
+    print(out[-2000:])   # kept in the test log: which ranks ran and what they reported
     assert r.returncode == 0, out[-3000:]
     if "PEER UNAVAILABLE" in out:
         pytest.skip("no NVSwitch replication on this box")

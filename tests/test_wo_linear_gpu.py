@@ -112,10 +112,15 @@ def test_w8a16_compute_bound_single_launch_path(xdtype, M, N, K, monkeypatch):
         want = orc.linear_w8(to_np(x[rows]), code_of(x), to_np(q[sl]), to_np(s[sl]), code_of(s), orc.F32, acc64=True)
         assert_close_rel(float_values(y[rows, sl]), want, ulp, f"single-launch w8a16 {M}x{N}x{K} channels {sl}")
     monkeypatch.setenv("QL_W8_TWO_KERNELS", "1")
-    c0 = ql.lib().ql_launch_count()
-    y_two = ql.linear_w8a16(x, q, s)
-    assert ql.lib().ql_launch_count() - c0 == 3
-    assert torch.equal(y, y_two)
+    ql.lib().ql_reload_tuning()   # the tuning variables are read once per process otherwise
+    try:
+        c0 = ql.lib().ql_launch_count()
+        y_two = ql.linear_w8a16(x, q, s)
+        assert ql.lib().ql_launch_count() - c0 == 3
+        assert torch.equal(y, y_two)
+    finally:
+        monkeypatch.delenv("QL_W8_TWO_KERNELS")
+        ql.lib().ql_reload_tuning()
 
 
 @pytest.mark.parametrize("M", [1, 8, 32])
