@@ -18,6 +18,7 @@
 // issuing work, drains what it issued and returns.
 #include <cuda.h>
 #include <cstdlib>
+#include <cstring>
 
 #include "ql_common.cuh"
 #include "ql_tc_common.cuh"
@@ -33,7 +34,7 @@ constexpr int STAGES = 4;
 
 // Tuning switches from the environment, read once per process (not on every launch).
 struct Tuning {
-  bool one_cta, two_kernels, not_cooperative;
+  bool one_cta, two_kernels, not_cooperative, direct_stores;
   int group_m;
 };
 Tuning read_tuning() {
@@ -41,6 +42,7 @@ Tuning read_tuning() {
   v.one_cta = getenv("QL_GEMM_ONE_CTA") != nullptr;
   v.two_kernels = getenv("QL_W8_TWO_KERNELS") != nullptr;
   v.not_cooperative = getenv("QL_W8_NOT_COOPERATIVE") != nullptr;
+  v.direct_stores = getenv("QL_GEMM_DIRECT_STORES") != nullptr; // results by per-lane stores instead of bulk stores
   const char *e = getenv("QL_GEMM_GROUP_M");
   v.group_m = e ? atoi(e) : 0;
   return v;
@@ -68,6 +70,7 @@ struct GemmArgs {
   int group_m;     // m-tiles per scheduling group (see tile_coords)
   int *status;
   float *row_amax; // non-null: SwiGLU epilogue (see swiglu_chunk); max|result| of every row is merged in here
+  int tma_store;   // the CTA-pair kernel writes Y with bulk tensor stores through shared memory (see StoreStage)
   int64_t ldy;     // elements between rows of Y (N, or the full width when Y is a column slice)
   int peer_mode;   // QL_PEER_*: how the epilogue writes Y
   int rows_per_rank;               // QL_PEER_ADD_OWNER: rows [r * rows_per_rank, ...) belong to rank r
@@ -276,6 +279,100 @@ __device__ __forceinline__ void swiglu_chunk(const GemmArgs &args, OutT *Y, bool
   }
 }
 
+// Results leave the CTA-pair kernel through shared memory.  In tensor memory a lane owns a row, so a direct store
+// sends 32 separate 16-byte pieces per instruction, half a sector each: the epilogue then takes longer than the
+// MMAs of a tile with K below about 4096 bytes and the kernel is bound by it.  Instead each epilogue warp parks
+// 32 rows x 128 bytes in its own staging buffer (laid out with the copy engine's 128-byte swizzle, which also keeps
+// the quarter-warp's 16-byte writes on distinct banks) and one lane issues a bulk tensor store that writes whole
+// 128-byte lines and clips rows and columns beyond the matrix.  Two buffers per warp, used in turn: a buffer is
+// rewritten once the store issued from it two steps earlier has read it.
+struct StoreStage {
+  uint8_t *base; // 2 x 4096 bytes, 1024-byte aligned
+  int buf;
+  __device__ __forceinline__ void begin(int lane) { // before the first write into the current buffer
+    if (lane == 0) bulk_wait_read<1>();
+    __syncwarp();
+  }
+  __device__ __forceinline__ void put(int lane, int piece, const uint4 &v) { // 16-byte piece `piece` (0..7) of row `lane`
+    *reinterpret_cast<uint4 *>(base + buf * 4096 + lane * 128 + ((piece ^ (lane & 7)) << 4)) = v;
+  }
+  __device__ __forceinline__ void send(const CUtensorMap *map, int lane, int x, int y) { // the buffer is complete
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(map, smem_u32(base + buf * 4096), x, y);
+      bulk_commit();
+    }
+    buf ^= 1;
+  }
+  __device__ __forceinline__ void finish(int lane) { // before the CTA's shared memory goes away
+    if (lane == 0) bulk_wait_all<0>();
+    __syncwarp();
+  }
+};
+
+// emit_chunk through the staging buffers: chunk `c` of the tile is columns n .. n+31 of rows m_base .. m_base+31.
+template <int KIND, typename OutT>
+__device__ __forceinline__ void emit_chunk_tma(const GemmArgs &args, const CUtensorMap *map_y, const uint32_t (&r)[32], int m_base, int n,
+                                               const float (&s)[32], StoreStage &st, int lane, int c) {
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; j++) {
+    float acc = (KIND == KIND_I8) ? (float)(int)r[j] : __uint_as_float(r[j]);
+    v[j] = acc * s[j];
+  }
+  if (args.bias) {
+#pragma unroll
+    for (int j = 0; j < 32; j++) v[j] += (n + j < args.N) ? load_scale(args.bias, args.bias_dtype, n + j) : 0.f;
+  }
+  if constexpr (sizeof(OutT) == 4) { // 32 columns fill the 128-byte row
+    st.begin(lane);
+#pragma unroll
+    for (int j = 0; j < 32; j += 4)
+      st.put(lane, j >> 2, make_uint4(__float_as_uint(v[j]), __float_as_uint(v[j + 1]), __float_as_uint(v[j + 2]), __float_as_uint(v[j + 3])));
+    st.send(map_y, lane, n, m_base);
+  } else { // two chunks fill the row
+    const int half = c & 1;
+    if (half == 0) st.begin(lane);
+#pragma unroll
+    for (int j = 0; j < 32; j += 8)
+      st.put(lane, half * 4 + (j >> 3), make_uint4(pack2<OutT>(v[j], v[j + 1]), pack2<OutT>(v[j + 2], v[j + 3]), pack2<OutT>(v[j + 4], v[j + 5]),
+                                                   pack2<OutT>(v[j + 6], v[j + 7])));
+    if (half == 1) st.send(map_y, lane, n - 32, m_base);
+  }
+}
+
+// swiglu_chunk through the staging buffers: pair `c` of the tile gives result columns (n >> 1) .. (n >> 1) + 31.
+template <typename OutT>
+__device__ __forceinline__ void swiglu_chunk_tma(const GemmArgs &args, const CUtensorMap *map_y, uint32_t taddr, int m_base, int n, float sa,
+                                                 float sb_scalar, float &rmax, StoreStage &st, int lane, int c) {
+  uint32_t r[32];
+  float s[32], g[32];
+  load_chunk_scales(args, n, sa, sb_scalar, s);
+  tmem_load_32(taddr, r);
+#pragma unroll
+  for (int j = 0; j < 32; j++) g[j] = __uint_as_float(r[j]) * s[j];
+  load_chunk_scales(args, n + 32, sa, sb_scalar, s);
+  tmem_load_32(taddr + 32, r);
+  const int half = c & 1;
+  const bool live = m_base + lane < args.M && n < args.N;
+  if (half == 0) st.begin(lane);
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int k = j + 2 * i;
+      const float a0 = silu_mul(g[k], __uint_as_float(r[k]) * s[k]), a1 = silu_mul(g[k + 1], __uint_as_float(r[k + 1]) * s[k + 1]);
+      w[i] = pack2<OutT>(a0, a1);
+      const OutT *h = reinterpret_cast<const OutT *>(&w[i]);
+      if (live) rmax = fmaxf(rmax, fmaxf(fabsf(FloatIO<OutT>::to_f32(h[0])), fabsf(FloatIO<OutT>::to_f32(h[1]))));
+    }
+    st.put(lane, half * 4 + (j >> 3), make_uint4(w[0], w[1], w[2], w[3]));
+  }
+  if (half == 1) st.send(map_y, lane, (n >> 1) - 32, m_base);
+}
+
 // The whole accumulator of one tile (BN columns from tensor-memory address taddr) through swiglu_chunk.
 template <int BN, typename OutT>
 __device__ __forceinline__ void swiglu_tile(const GemmArgs &args, OutT *Y, bool vec_ok, uint32_t taddr, int m, int n0, float sa, float sb_scalar) {
@@ -470,18 +567,21 @@ constexpr int BN2 = 256;
 constexpr int B2_STAGE_BYTES = (BN2 / 2) * BK_BYTES;
 constexpr int STAGE2_BYTES = A_STAGE_BYTES + B2_STAGE_BYTES;
 
-// PEER = the instantiation whose epilogue may write to peers: it gives one pipeline stage up for the
-// epilogue's staging rows.
+// Six pipeline stages of 32 KiB and 32 KiB of epilogue staging.  PEER = the instantiation whose epilogue may
+// write to peers (its staging rows lie in the same area).
 template <bool PEER> struct Smem2 {
-  static constexpr int kStages = PEER ? 6 : 7;
+  static constexpr int kStages = 6;
   static constexpr int kTiles = kStages * STAGE2_BYTES;
-  static constexpr int kBarriers = kTiles;                   // full[S], empty[S], tfull[2], tempty[2], drain
+  static constexpr int kStage = kTiles;                      // epilogue staging: 4 warps x 2 x 4096 bytes of StoreStage,
+  static constexpr int kStageBytes = 4 * 2 * 4096;           // or the peer-mode rows (kPeerStageBytes), which are smaller
+  static constexpr int kPeerStage = kStage;
+  static constexpr int kBarriers = kStage + kStageBytes;     // full[S], empty[S], tfull[2], tempty[2], drain
   static constexpr int kTmemPtr = kBarriers + (2 * kStages + 5) * 8;
   static constexpr int kAbort = kTmemPtr + 4;
-  static constexpr int kPeerStage = (kAbort + 4 + 15) & ~15;
-  static constexpr int kTotal = kPeerStage + (PEER ? kPeerStageBytes : 0);
+  static constexpr int kTotal = kAbort + 4;
   static constexpr int kDynamic = kTotal + 1024;
 };
+static_assert(kPeerStageBytes <= Smem2<true>::kStageBytes, "the peer-mode staging rows share the store staging area");
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -593,8 +693,8 @@ __device__ __forceinline__ bool wait_counter(const int *ctr, int need, volatile 
 // args.tiles_m counts 256-row tiles here; args.tiles_n counts 256-column tiles.
 template <int KIND, typename OutT, bool PEER, bool WIDEN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(WIDEN ? kGemmThreads + kWidenThreads : kGemmThreads, 1)
-gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs args,
-                const WidenArgs wargs) {
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ CUtensorMap map_y, const GemmArgs args, const WidenArgs wargs) {
   using L = Smem2<PEER>;
   constexpr int STAGES2 = L::kStages;
   constexpr uint32_t kTmemCols = 512; // two 256-column accumulators
@@ -744,6 +844,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int quad = warp & 3;
     OutT *Y = static_cast<OutT *>(args.Y);
     uint8_t *stage = PEER ? smem + L::kPeerStage + quad * kPeerStageWarp : nullptr;
+    StoreStage sst{smem + L::kStage + quad * 8192, 0};
+    const bool tma_out = !PEER && args.tma_store; // the same for every thread of the grid
     const bool vec_ok = (args.ldy % (16 / (int)sizeof(OutT)) == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
     int it = 0;
     bool ok = true;
@@ -754,7 +856,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const int m0 = mt * 256 + (int)rank * BM, n0 = nt * BN2;
       if (!mbar_wait(tfull_bar(buf), (it >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      const int m = m0 + quad * 32 + lane;
+      const int m_base = m0 + quad * 32, m = m_base + lane;
       float sa = 1.f;
       if (args.sa) sa = (args.sa_n == 1) ? __ldg(args.sa) : (m < args.M ? __ldg(args.sa + m) : 0.f);
       const float sb_scalar = (args.sb && args.sb_n == 1) ? load_scale(args.sb, args.sb_dtype, 0) : 1.f;
@@ -762,7 +864,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       bool fused = false;
       if constexpr (KIND == KIND_F8 && sizeof(OutT) == 2 && !PEER && !WIDEN) {
         if (args.row_amax) {
-          swiglu_tile<BN2, OutT>(args, Y, vec_ok, taddr, m, n0, sa, sb_scalar);
+          if (tma_out) {
+            float rmax = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < BN2 / 64; c++)
+              swiglu_chunk_tma<OutT>(args, &map_y, taddr + c * 64, m_base, n0 + c * 64, sa, sb_scalar, rmax, sst, lane, c);
+            if (m < args.M && rmax > 0.f) atomicMax(reinterpret_cast<int *>(args.row_amax) + m, __float_as_int(rmax));
+          } else {
+            swiglu_tile<BN2, OutT>(args, Y, vec_ok, taddr, m, n0, sa, sb_scalar);
+          }
           fused = true;
         }
       }
@@ -773,12 +883,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int n = n0 + c * 32;
         load_chunk_scales(args, n, sa, sb_scalar, sc);
         tmem_load_32(taddr + c * 32, r);
-        emit_chunk<KIND, OutT>(args, Y, vec_ok, r, m, n, sc, stage, lane, c, c == BN2 / 32 - 1);
+        if (tma_out) emit_chunk_tma<KIND, OutT>(args, &map_y, r, m_base, n, sc, sst, lane, c);
+        else emit_chunk<KIND, OutT>(args, Y, vec_ok, r, m, n, sc, stage, lane, c, c == BN2 / 32 - 1);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0)); // the leader owns the accumulator hand-over
     }
+    if (tma_out) sst.finish(lane);
     if (!ok && lane == 0) signal_partner_abort(smem_u32((const void *)abort_flag), rank);
   }
 
@@ -845,10 +957,18 @@ int max_resident_pairs() {
 
 template <int KIND, typename OutT, int V>
 int launch_gemm_pair(const void *A, const void *B, GemmArgs args, int64_t K, int pairs, cudaStream_t st, WidenArgs wargs = WidenArgs{}) {
-  CUtensorMap ma, mb;
+  CUtensorMap ma, mb, my;
   int rc;
   if ((rc = make_map(&ma, KIND, A, args.M, K, BM)) != QL_OK) return rc;
   if ((rc = make_map(&mb, KIND, B, args.N, K, BN2 / 2)) != QL_OK) return rc;
+  // results through shared memory and bulk stores wherever the copy engine can address them
+  args.tma_store = 0;
+  memset(&my, 0, sizeof(my));
+  if (V != PAIR_PEER && aligned16(args.Y) && (args.ldy * (int64_t)sizeof(OutT)) % 16 == 0 && !tuning().direct_stores) {
+    const int64_t cols = args.row_amax ? args.N / 2 : args.N;
+    if ((rc = make_map_out(&my, FloatIO<OutT>::kDtype, args.Y, args.M, cols, args.ldy)) != QL_OK) return rc;
+    args.tma_store = 1;
+  }
   constexpr int kTileN = BN2;
   args.tiles_m = (args.M + 255) / 256;
   args.tiles_n = (args.N + kTileN - 1) / kTileN;
@@ -870,13 +990,13 @@ int launch_gemm_pair(const void *A, const void *B, GemmArgs args, int64_t K, int
     attr.val.cooperative = tuning().not_cooperative ? 0 : 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, pair_kernel<KIND, OutT, V>(), ma, mb, args, wargs);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, pair_kernel<KIND, OutT, V>(), ma, mb, my, args, wargs);
     if (e != cudaSuccess) {
       cudaGetLastError();
       return QL_ERR_UNSUPPORTED; // the caller falls back to the two-kernel route
     }
   } else {
-    pair_kernel<KIND, OutT, V>()<<<2 * clusters, pair_threads<V>(), pair_smem<V>(), st>>>(ma, mb, args, wargs);
+    pair_kernel<KIND, OutT, V>()<<<2 * clusters, pair_threads<V>(), pair_smem<V>(), st>>>(ma, mb, my, args, wargs);
   }
   count_launches(1);
   QL_CUDA_TRY(cudaGetLastError());
@@ -1050,6 +1170,7 @@ int run_gemm(const char *op, const ql_tensor *a, const ql_tensor *b, const ql_te
   args.status = device_status_word();
   if (!args.status) return set_error(QL_ERR_CUDA, "%s: could not allocate the device status word", op);
   args.row_amax = row_amax;
+  args.tma_store = 0;
   if (row_amax) args.ldy = N / 2;
   cudaStream_t st = (cudaStream_t)stream;
   if (y->dtype == QL_BF16) return launch_gemm_kind<KIND, __nv_bfloat16>(a->data, b->data, args, K, st);
@@ -1103,6 +1224,7 @@ int gemm16_widen_t(const void *X, const void *Wraw, void *wide, int *counters, c
   for (int r = 0; r < QL_MAX_PEERS; r++) args.owner_y[r] = nullptr;
   args.status = device_status_word();
   args.row_amax = nullptr;
+  args.tma_store = 0;
   if (!args.status) return set_error(QL_ERR_CUDA, "linear_w8a16: could not allocate the device status word");
   WidenArgs w;
   w.raw = static_cast<const uint8_t *>(Wraw);

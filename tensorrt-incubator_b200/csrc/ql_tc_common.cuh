@@ -73,6 +73,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
                : "memory");
 }
 
+// Bulk tensor store of a [32 rows x 128 bytes] box from shared memory; completion is tracked per issuing thread in
+// bulk async-groups.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until at most N of this thread's bulk groups still have to read their shared-memory source
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -225,6 +237,47 @@ inline int make_map(CUtensorMap *map, int kind, const void *ptr, int64_t rows, i
   return QL_OK;
 }
 
+
+// Result matrix [rows, cols] of `esize`-byte elements with `ld` elements between rows, box = [32 rows, 128 bytes],
+// 128-byte swizzle: the epilogue parks 32 rows x 128 bytes in shared memory and one bulk store writes them out as
+// whole 128-byte lines (rows and columns beyond the matrix are clipped by the copy engine).
+inline int make_map_out(CUtensorMap *map, int dtype, const void *ptr, int64_t rows, int64_t cols, int64_t ld) {
+  struct Entry {
+    const void *ptr;
+    int64_t rows, cols, ld;
+    int dtype;
+    CUtensorMap map;
+  };
+  constexpr int kEntries = 16;
+  static thread_local Entry cache[kEntries] = {};
+  const uintptr_t h = reinterpret_cast<uintptr_t>(ptr) >> 8;
+  Entry &e = cache[(h ^ (h >> 7) ^ (uintptr_t)rows) % kEntries];
+  if (e.ptr == ptr && ptr != nullptr && e.rows == rows && e.cols == cols && e.ld == ld && e.dtype == dtype) {
+    *map = e.map;
+    return QL_OK;
+  }
+  EncodeTiledFn enc;
+  int rc = get_encode_fn(&enc);
+  if (rc != QL_OK) return rc;
+  const int esize = dtype == QL_F32 ? 4 : 2;
+  CUtensorMapDataType dt = dtype == QL_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                           : dtype == QL_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                              : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * esize};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / esize), 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(QL_ERR_CUDA, "cuTensorMapEncodeTiled (result) failed with code %d", (int)r);
+  e.ptr = ptr;
+  e.rows = rows;
+  e.cols = cols;
+  e.ld = ld;
+  e.dtype = dtype;
+  e.map = *map;
+  return QL_OK;
+}
 
 // [rows, K] row-major bytes, box = [box_rows, box_bytes], no swizzle (tiles read back by ordinary loads)
 inline int make_map_bytes(CUtensorMap *map, const void *ptr, int64_t rows, int64_t row_bytes, int box_bytes, int box_rows) {
