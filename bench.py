@@ -174,7 +174,7 @@ class W8A16Linear(Workload):
     def run_part(self, m):
         w = self.wq[self.turn % self.REPLICAS]
         self.turn += 1
-        self.ql.linear_w8a16(self.x[m], w, self.scale, out=self.y[m])
+        self.ql.linear_w8a16(self.x[m], w, self.scale, out=self.y[m], weights_constant=True)   # quantized once, in __init__
 
     def parts(self):
         return [(f"M={m}", (lambda m=m: self.run_part(m)), self.flops(m), self.bytes(m), "tensor" if m >= 512 else "hbm") for m in self.MS]
@@ -222,7 +222,7 @@ class W4A16Linear(Workload):
     def run_part(self, m):
         i = self.turn % self.REPLICAS
         self.turn += 1
-        self.ql.linear_w4a16(self.x[m], self.wq[i], self.scale[i], out=self.y[m])
+        self.ql.linear_w4a16(self.x[m], self.wq[i], self.scale[i], out=self.y[m], weights_constant=True)   # quantized once, in __init__
 
     def parts(self):
         return [(f"M={m}", (lambda m=m: self.run_part(m)), 2 * m * self.N * self.K,

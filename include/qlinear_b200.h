@@ -138,6 +138,15 @@ QL_API int ql_linear_w8a16(const ql_tensor *x, const ql_tensor *w, const ql_tens
                            ql_tensor *y, void *stream);
 QL_API int ql_linear_w4a16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *scale,
                            ql_tensor *y, void *stream);
+/* Either of the two, chosen by w->dtype, with flags.  QL_WEIGHTS_CONSTANT: w and scale were written before the
+ * kernel that precedes this call on the stream was launched -- true of the weights of a compiled program, which
+ * are constants (the reference requires constant scales, TensorRTOps.td:3113-3114, and Linear's weights are
+ * parameters).  With at most 64 rows of x the kernel is then launched so that it may start while its predecessor
+ * is still finishing (programmatic dependent launch): it fetches its first weights, waits for the predecessor to
+ * complete, and only then reads x and writes y.  Without the flag the launch is ordered like any other. */
+#define QL_WEIGHTS_CONSTANT 1u
+QL_API int ql_linear_weight_only(const ql_tensor *x, const ql_tensor *w, const ql_tensor *scale, ql_tensor *y,
+                                 uint32_t flags, void *stream);
 
 /* Quantized GEMMs on the tensor cores, Y[M,N] = (Xq[M,K] . Wq[N,K]^T) * sx * sw, f32 (fp8) or
  * s32 (int8) accumulation, scales applied in the epilogue, Y bf16, f16 or f32.

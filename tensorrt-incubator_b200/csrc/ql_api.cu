@@ -78,7 +78,7 @@ int launch_scale_from_amax(const float *amax, void *scale, int sdt, int64_t n, f
 
 // ql_wo_linear.cu
 int launch_wo_linear(int wbits, int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M,
-                     int N, int K, int block, cudaStream_t st);
+                     int N, int K, int block, bool weights_constant, cudaStream_t st);
 
 // ql_gemm_w8a16.cu
 int launch_w8a16_fused(int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M, int N, int K,
@@ -94,8 +94,11 @@ int gemm16_device(int dtype, const void *X, const void *W, const float *sb, int 
 // ql_nvfp4.cu
 int launch_f4_block_dequantize(const ql_tensor *q, const ql_tensor *scale, ql_tensor *y, cudaStream_t st);
 
-// Above this many rows of X the weight-only layers leave the streaming kernel for the tcgen05 GEMM.
+// Above this many rows of X the weight-only layers leave the streaming kernel for the tcgen05 GEMM.  The int8
+// layer has a tcgen05 kernel that widens the weights itself and takes over earlier: the streaming kernel walks
+// batches in slices of 32 rows (58 us for 64 rows of config 2 against 35 us for 128 rows on the tensor cores).
 constexpr int kWeightOnlyMaxRows = 64;
+constexpr int kWeightOnlyMaxRowsInt8 = 32;
 
 static bool same_shape(const ql_tensor *a, const ql_tensor *b) {
   if (a->rank != b->rank) return false;
@@ -342,7 +345,7 @@ static int check_linear_io(const char *op, const ql_tensor *x, const ql_tensor *
   return QL_OK;
 }
 
-int ql_linear_w8a16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *scale, ql_tensor *y, void *stream) {
+static int linear_w8a16_impl(const ql_tensor *x, const ql_tensor *w, const ql_tensor *scale, ql_tensor *y, uint32_t flags, void *stream) {
   const char *op = "linear_w8a16";
   int rc = check_linear_io(op, x, w, scale, y, QL_I8);
   if (rc != QL_OK) return rc;
@@ -359,14 +362,14 @@ int ql_linear_w8a16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *sca
   if (M > fused_max)
     return launch_w8a16_widen(x->dtype, x->data, w->data, scale->data, scale->dtype, y->data, (int)M, (int)N, (int)K,
                               (cudaStream_t)stream);
-  if (M > kWeightOnlyMaxRows)
+  if (M > kWeightOnlyMaxRowsInt8)
     return launch_w8a16_fused(x->dtype, x->data, w->data, scale->data, scale->dtype, y->data, (int)M, (int)N, (int)K,
                               (cudaStream_t)stream);
   return launch_wo_linear(8, x->dtype, x->data, w->data, scale->data, scale->dtype, y->data, (int)M, (int)N, (int)K, 0,
-                          (cudaStream_t)stream);
+                          (flags & QL_WEIGHTS_CONSTANT) != 0, (cudaStream_t)stream);
 }
 
-int ql_linear_w4a16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *scale, ql_tensor *y, void *stream) {
+static int linear_w4a16_impl(const ql_tensor *x, const ql_tensor *w, const ql_tensor *scale, ql_tensor *y, uint32_t flags, void *stream) {
   const char *op = "linear_w4a16";
   int rc = check_linear_io(op, x, w, scale, y, QL_I4);
   if (rc != QL_OK) return rc;
@@ -395,7 +398,23 @@ int ql_linear_w4a16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *sca
     return rc;
   }
   return launch_wo_linear(4, x->dtype, x->data, w->data, scale->data, scale->dtype, y->data, (int)M, (int)N, (int)K,
-                          (int)block, (cudaStream_t)stream);
+                          (int)block, (flags & QL_WEIGHTS_CONSTANT) != 0, (cudaStream_t)stream);
+}
+
+int ql_linear_w8a16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *scale, ql_tensor *y, void *stream) {
+  return linear_w8a16_impl(x, w, scale, y, 0, stream);
+}
+
+int ql_linear_w4a16(const ql_tensor *x, const ql_tensor *w, const ql_tensor *scale, ql_tensor *y, void *stream) {
+  return linear_w4a16_impl(x, w, scale, y, 0, stream);
+}
+
+int ql_linear_weight_only(const ql_tensor *x, const ql_tensor *w, const ql_tensor *scale, ql_tensor *y, uint32_t flags, void *stream) {
+  if (!w) return set_error(QL_ERR_INVALID_ARGUMENT, "linear_weight_only: w is null");
+  if (flags & ~(uint32_t)QL_WEIGHTS_CONSTANT) return set_error(QL_ERR_INVALID_ARGUMENT, "linear_weight_only: unknown flags 0x%x", flags);
+  if (w->dtype == QL_I8) return linear_w8a16_impl(x, w, scale, y, flags, stream);
+  if (w->dtype == QL_I4) return linear_w4a16_impl(x, w, scale, y, flags, stream);
+  return set_error(QL_ERR_INVALID_ARGUMENT, "linear_weight_only: weights must be int8 or int4");
 }
 
 } // extern "C"

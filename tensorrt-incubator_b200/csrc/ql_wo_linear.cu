@@ -9,7 +9,10 @@
 // extracts (elements e and e+4 of a word) are matched by permuting the X registers.
 //
 // One block owns 16 output channels; its 8 warps split K, keep several iterations' worth of 16-byte
-// weight loads in flight in registers, and reduce through shared memory.  (A shared-memory ring fed by
+// weight loads in flight in registers, and reduce through shared memory.  Where N / 16 blocks are too few to
+// keep every SM's load queues full (N = 4096 gives 256 blocks for 148 SMs), K is also split across the CTAs of
+// a thread-block cluster: each CTA takes a slice of K, writes its 16 x M partial sums into the leader's shared
+// memory (distributed shared memory) and the leader adds them up in a fixed order.  (A shared-memory ring fed by
 // TMA was measured slower here: blocks are short-lived, so the ring's set-up and the copy latency at the
 // start of every block cost more than the deeper prefetch gained.)
 // Reference composition this implements: tripy/nvtripy/frontend/module/linear.py:140-151
@@ -25,6 +28,23 @@ namespace {
 constexpr int kWarps = 8;
 constexpr int kThreadsWo = kWarps * 32;
 constexpr int kRowsPerBlock = 16;
+constexpr int kMaxKSplit = 8; // CTAs of a cluster that share one block of output channels
+
+__device__ __forceinline__ uint32_t wo_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void wo_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// f32 store into the same shared-memory variable of CTA `rank` of the cluster
+__device__ __forceinline__ void wo_store_remote(float *local_addr, uint32_t rank, float v) {
+  uint32_t a = (uint32_t)__cvta_generic_to_shared(local_addr), r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(r), "f"(v) : "memory");
+}
 
 template <typename XT>
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -85,10 +105,11 @@ template <int WBITS> struct WoTraits {
 template <typename XT, int WBITS, int NT, int U, int MINB>
 __global__ void __launch_bounds__(kThreadsWo, MINB)
 wo_linear_kernel(const XT *__restrict__ X, const uint8_t *__restrict__ W, const void *__restrict__ scale, int sdt,
-                 XT *__restrict__ Y, int M, int N, int K, int block) {
+                 XT *__restrict__ Y, int M, int N, int K, int block, int ksplit) {
   using T = WoTraits<WBITS>;
   constexpr int XV = T::kXWords;
   __shared__ float red[kWarps][kRowsPerBlock][NT * 8 + 1];
+  __shared__ float part[kMaxKSplit][kRowsPerBlock * NT * 8]; // leader only: one slot per CTA of the cluster
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -97,7 +118,10 @@ wo_linear_kernel(const XT *__restrict__ X, const uint8_t *__restrict__ W, const 
   const int64_t row_bytes = (int64_t)K * WBITS / 8;
   const uint8_t *wa_ptr = W + (int64_t)row_a * row_bytes + t * 16;
   const uint8_t *wb_ptr = W + (int64_t)row_b * row_bytes + t * 16;
-  const int n_iters = K / T::kStep;
+  // this CTA's slice of the k iterations (the cluster lies along grid.y)
+  const int kslice = ksplit > 1 ? (int)wo_cluster_rank() : 0;
+  const int all_iters = K / T::kStep, per_slice = (all_iters + ksplit - 1) / ksplit;
+  const int it_begin = kslice * per_slice, n_iters = min(all_iters, it_begin + per_slice);
   const int nb = (WBITS == 4) ? K / block : 0;
 
   float acc[NT][4];
@@ -105,9 +129,11 @@ wo_linear_kernel(const XT *__restrict__ X, const uint8_t *__restrict__ W, const 
   for (int i = 0; i < NT; i++)
 #pragma unroll
     for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+  // the kernel that follows on the stream may start being scheduled as this one's blocks retire
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-  for (int it0 = warp; it0 < n_iters; it0 += kWarps * U) {
-    // ---- issue every load of this group of iterations
+  for (int it0 = it_begin + warp; it0 < n_iters; it0 += kWarps * U) {
+    // ---- issue every load of this group of iterations: the weights first
     uint4 wa[U], wb[U], xv[U][NT][XV];
 #pragma unroll
     for (int u = 0; u < U; u++) {
@@ -115,6 +141,16 @@ wo_linear_kernel(const XT *__restrict__ X, const uint8_t *__restrict__ W, const 
       if (it < n_iters) {
         wa[u] = __ldcs(reinterpret_cast<const uint4 *>(wa_ptr + (int64_t)it * 64));
         wb[u] = __ldcs(reinterpret_cast<const uint4 *>(wb_ptr + (int64_t)it * 64));
+      }
+    }
+    // The activations may be the result of the kernel that precedes this one on the stream.  When the launch was
+    // allowed to start before that kernel has finished (see QL_WEIGHTS_CONSTANT), everything up to here overlapped
+    // with its tail; this waits until it is complete and its writes are visible (no effect otherwise).
+    if (it0 == it_begin + warp) asm volatile("griddepcontrol.wait;" ::: "memory");
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int it = it0 + u * kWarps;
+      if (it < n_iters) {
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
           const int m = nt * 8 + g;
@@ -190,6 +226,7 @@ wo_linear_kernel(const XT *__restrict__ X, const uint8_t *__restrict__ W, const 
     }
   }
 
+  asm volatile("griddepcontrol.wait;" ::: "memory"); // warps without a k step of their own; Y is written only after this
   // cross-warp reduction: red[warp][row][m]
 #pragma unroll
   for (int nt = 0; nt < NT; nt++) {
@@ -199,21 +236,57 @@ wo_linear_kernel(const XT *__restrict__ X, const uint8_t *__restrict__ W, const 
     red[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
   }
   __syncthreads();
+  if (ksplit > 1) {
+    // every CTA hands its partial sums to the leader; the leader adds the slices in rank order
+    for (int idx = threadIdx.x; idx < kRowsPerBlock * NT * 8; idx += kThreadsWo) {
+      const int r = idx % kRowsPerBlock, m = idx / kRowsPerBlock;
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; w++) s += red[w][r][m];
+      wo_store_remote(&part[kslice][idx], 0, s);
+    }
+    wo_cluster_sync();
+    if (kslice != 0) return;
+  }
   for (int idx = threadIdx.x; idx < kRowsPerBlock * NT * 8; idx += kThreadsWo) {
     const int r = idx % kRowsPerBlock, m = idx / kRowsPerBlock;
     const int n = n0 + r;
     if (m >= M || n >= N) continue;
     float s = 0.f;
+    if (ksplit > 1) {
+      for (int c = 0; c < ksplit; c++) s += part[c][idx];
+    } else {
 #pragma unroll
-    for (int w = 0; w < kWarps; w++) s += red[w][r][m];
+      for (int w = 0; w < kWarps; w++) s += red[w][r][m];
+    }
     if constexpr (WBITS == 8) s *= load_scale(scale, sdt, n);
     Y[(int64_t)m * N + n] = FloatIO<XT>::from_f32(s);
   }
 }
 
+// How many CTAs share one block of output channels.  Splitting pays while the blocks of an unsplit launch cannot
+// fill the resident-block slots of the device a few times over; every slice keeps at least one k step per warp.
+int read_forced_ksplit() {
+  const char *e = getenv("QL_WO_KSPLIT"); // tuning aid
+  return e ? atoi(e) : 0;
+}
+int g_forced_ksplit = read_forced_ksplit(); // read when the library is loaded and by ql_reload_tuning()
+
+int pick_ksplit(unsigned row_blocks, int n_iters, int resident_per_sm) {
+  const int forced = g_forced_ksplit;
+  // Measured on B200 (N = 4096 and 11008, K = 4096, M = 1 .. 64): every doubling of the split costs 1.5 - 4 us
+  // (cluster scheduling, the exchange and its barrier) and never pays for itself, so nothing is split unless asked.
+  (void)row_blocks;
+  (void)resident_per_sm;
+  int ks = forced > 0 ? forced : 1;
+  if (ks > kMaxKSplit) ks = kMaxKSplit;
+  while (ks > 1 && n_iters / ks < 1) ks /= 2;
+  return ks;
+}
+
 template <typename XT, int WBITS>
 int launch_wo_t(const void *X, const void *W, const void *scale, int sdt, void *Y, int M, int N, int K, int block,
-                cudaStream_t st) {
+                bool weights_constant, cudaStream_t st) {
   const unsigned grid = (unsigned)((N + kRowsPerBlock - 1) / kRowsPerBlock);
   const uint8_t *wp = static_cast<const uint8_t *>(W);
   // batches larger than 32 rows are walked in slices; the weights of the later slices come from L2
@@ -223,11 +296,32 @@ int launch_wo_t(const void *X, const void *W, const void *scale, int sdt, void *
     XT *yp = static_cast<XT *>(Y) + (int64_t)m0 * N;
     // (k-steps in flight per warp, minimum resident blocks) per batch width, from timing on B200: many
     // resident blocks with one step in flight each beat fewer blocks with deeper unrolling
-#define QL_WO_LAUNCH(NT_, U_, MB_) wo_linear_kernel<XT, WBITS, NT_, U_, MB_><<<grid, kThreadsWo, 0, st>>>(xp, wp, scale, sdt, yp, mc, N, K, block)
+#define QL_WO_LAUNCH(NT_, U_, MB_)                                                                                        \
+  do {                                                                                                                    \
+    const int ks = pick_ksplit(grid, K / WoTraits<WBITS>::kStep, MB_);                                                    \
+    cudaLaunchConfig_t cfg = {};                                                                                          \
+    cfg.gridDim = dim3(grid, ks, 1);                                                                                      \
+    cfg.blockDim = dim3(kThreadsWo, 1, 1);                                                                                \
+    cfg.stream = st;                                                                                                      \
+    cudaLaunchAttribute attr[2];                                                                                          \
+    attr[0].id = cudaLaunchAttributeClusterDimension;                                                                     \
+    attr[0].val.clusterDim.x = 1;                                                                                         \
+    attr[0].val.clusterDim.y = ks;                                                                                        \
+    attr[0].val.clusterDim.z = 1;                                                                                         \
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                                      \
+    attr[1].val.programmaticStreamSerializationAllowed = 1;                                                               \
+    cfg.attrs = attr;                                                                                                     \
+    cfg.numAttrs = (early_start && ks == 1) ? 2 : 1;                                                                      \
+    QL_CUDA_TRY(cudaLaunchKernelEx(&cfg, wo_linear_kernel<XT, WBITS, NT_, U_, MB_>, xp, wp, scale, sdt, yp, mc, N, K, block, ks)); \
+  } while (0)
     // (int4 keeps four X words per row and step alive instead of two: the int8 settings would spill.)  When the
     // grid cannot fill the SMs several times over, occupancy is not what limits the bytes in flight, so each warp
     // issues all of its few steps at once instead.
     const bool few_blocks = grid < 3u * (unsigned)sm_count();
+    // Starting before the preceding kernel has finished (only with constant weights, only for the first slice)
+    // hides the launch gap and the first loads' latency: 6.8 -> 5.2 us at N = K = 4096 int4, M = 1.  With a grid
+    // that fills the device and at most 8 rows the early blocks only get in the way (measured: 6 % slower).
+    const bool early_start = weights_constant && m0 == 0 && (few_blocks || mc > 8);
     if (mc <= 8) {
       if (few_blocks) QL_WO_LAUNCH(1, 4, 2);
       else if constexpr (WBITS == 8) QL_WO_LAUNCH(1, 1, 6);
@@ -248,15 +342,19 @@ int launch_wo_t(const void *X, const void *W, const void *scale, int sdt, void *
 
 } // namespace
 
+void wo_reload_tuning() { g_forced_ksplit = read_forced_ksplit(); }
+
+// weights_constant: W and scale were written before the kernel preceding this launch on the stream started, so the
+// kernel may begin fetching them while that kernel is still finishing.
 int launch_wo_linear(int wbits, int xdt, const void *X, const void *W, const void *scale, int sdt, void *Y, int M,
-                     int N, int K, int block, cudaStream_t st) {
+                     int N, int K, int block, bool weights_constant, cudaStream_t st) {
   if (M == 0 || N == 0) return QL_OK;
   if (wbits == 8) {
-    if (xdt == QL_F16) return launch_wo_t<__half, 8>(X, W, scale, sdt, Y, M, N, K, block, st);
-    return launch_wo_t<__nv_bfloat16, 8>(X, W, scale, sdt, Y, M, N, K, block, st);
+    if (xdt == QL_F16) return launch_wo_t<__half, 8>(X, W, scale, sdt, Y, M, N, K, block, weights_constant, st);
+    return launch_wo_t<__nv_bfloat16, 8>(X, W, scale, sdt, Y, M, N, K, block, weights_constant, st);
   }
-  if (xdt == QL_F16) return launch_wo_t<__half, 4>(X, W, scale, sdt, Y, M, N, K, block, st);
-  return launch_wo_t<__nv_bfloat16, 4>(X, W, scale, sdt, Y, M, N, K, block, st);
+  if (xdt == QL_F16) return launch_wo_t<__half, 4>(X, W, scale, sdt, Y, M, N, K, block, weights_constant, st);
+  return launch_wo_t<__nv_bfloat16, 4>(X, W, scale, sdt, Y, M, N, K, block, weights_constant, st);
 }
 
 } // namespace ql

@@ -40,6 +40,7 @@ class QlQdqAttrs(ctypes.Structure):
     _fields_ = [("has_axis", ctypes.c_int32), ("axis", ctypes.c_int32), ("fp8_mode", ctypes.c_int32)]
 
 
+WEIGHTS_CONSTANT = 1  # flag of ql_linear_weight_only
 PEER_NONE, PEER_STORE_ALL, PEER_ADD_ALL, PEER_ADD_OWNER = 0, 1, 2, 3  # ql_peer_mode
 QL_MAX_PEERS = 8
 
@@ -69,6 +70,7 @@ SIGNATURES = {
     "ql_dequantize_nvfp4": ([_T, _T, _T, _T, _S], ctypes.c_int),
     "ql_linear_w8a16": ([_T, _T, _T, _T, _S], ctypes.c_int),
     "ql_linear_w4a16": ([_T, _T, _T, _T, _S], ctypes.c_int),
+    "ql_linear_weight_only": ([_T, _T, _T, _T, ctypes.c_uint32, _S], ctypes.c_int),
     "ql_gemm_fp8": ([_T, _T, _T, _T, _T, _S], ctypes.c_int),
     "ql_gemm_fp8_peer": ([_T, _T, _T, _T, _P, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, _S], ctypes.c_int),
     "ql_peer_barrier": ([_P, _S], ctypes.c_int),

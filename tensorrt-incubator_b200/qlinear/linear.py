@@ -47,7 +47,15 @@ class Linear:
     def quantized_weight(self):
         if self._qweight is None:
             self._qweight = ops.quantize(self.weight, self.weight_scale, self.quant_dtype, self.weight_quant_dim)
+            self.__dict__["_qweight_fresh"] = True   # written by the kernel just launched: not yet "constant"
         return self._qweight
+
+    def _weights_constant(self) -> bool:
+        """False for the call that quantized the weights (its quantize kernel is the one preceding the linear kernel
+        on the stream), True afterwards."""
+        fresh = self.__dict__.get("_qweight_fresh", True)
+        self.__dict__["_qweight_fresh"] = False
+        return not fresh
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         return self.forward(x)
@@ -83,10 +91,10 @@ class Linear:
         # the weight-only kernels (16-bit activations, weights dequantized in registers); their bias is added after
         fast, out = self.dtype is not dt.float32, None
         if fast and self.quant_dtype is dt.int8 and self.weight_quant_dim == 0 and self.in_features % 64 == 0:
-            out = linear_w8a16(x2, qw, ws)
+            out = linear_w8a16(x2, qw, ws, weights_constant=self._weights_constant())
         elif fast and self.quant_dtype is dt.int4 and ws.dim() == 2 and ws.shape[0] == self.out_features \
                 and self.in_features % 128 == 0 and (self.in_features // ws.shape[1]) % 128 == 0:
-            out = linear_w4a16(x2, qw, ws)
+            out = linear_w4a16(x2, qw, ws, weights_constant=self._weights_constant())
         if out is not None:
             return out if self.bias is None else out + self.bias.unsqueeze(0)
         # remaining legal combinations: dequantize on the GPU, then the product in `dtype`
@@ -98,19 +106,20 @@ def _out(M, N, torch_dtype, device):
     return torch.empty((M, N), dtype=torch_dtype, device=device)
 
 
-def linear_w8a16(x: torch.Tensor, wq: torch.Tensor, scale: torch.Tensor, out=None) -> torch.Tensor:
-    """Y = X . (Wq * scale[:, None])^T, Wq int8 [N, K], X f16/bf16 [M, K]."""
+def linear_w8a16(x: torch.Tensor, wq: torch.Tensor, scale: torch.Tensor, out=None, weights_constant: bool = False) -> torch.Tensor:
+    """Y = X . (Wq * scale[:, None])^T, Wq int8 [N, K], X f16/bf16 [M, K].  `weights_constant`: Wq and scale were
+    written before the kernel preceding this call on the stream was launched (QL_WEIGHTS_CONSTANT)."""
     y = out if out is not None else _out(x.shape[0], wq.shape[0], x.dtype, x.device)
     tx, tw, ts, ty = ql_view(x), ql_view(wq), ql_view(scale), ql_view(y)
-    _lib.check(_lib.lib().ql_linear_w8a16(tx, tw, ts, ty, current_stream(x.device)))
+    _lib.check(_lib.lib().ql_linear_weight_only(tx, tw, ts, ty, _lib.WEIGHTS_CONSTANT if weights_constant else 0, current_stream(x.device)))
     return y
 
 
-def linear_w4a16(x: torch.Tensor, wq: Int4Tensor, scale: torch.Tensor, out=None) -> torch.Tensor:
-    """Y = X . dequantize(Wq)^T, Wq int4 [N, K] packed, scale [N, K / block]."""
+def linear_w4a16(x: torch.Tensor, wq: Int4Tensor, scale: torch.Tensor, out=None, weights_constant: bool = False) -> torch.Tensor:
+    """Y = X . dequantize(Wq)^T, Wq int4 [N, K] packed, scale [N, K / block]; `weights_constant` as in linear_w8a16."""
     y = out if out is not None else _out(x.shape[0], wq.shape[0], x.dtype, x.device)
     tx, tw, ts, ty = ql_view(x), ql_view(wq), ql_view(scale), ql_view(y)
-    _lib.check(_lib.lib().ql_linear_w4a16(tx, tw, ts, ty, current_stream(x.device)))
+    _lib.check(_lib.lib().ql_linear_weight_only(tx, tw, ts, ty, _lib.WEIGHTS_CONSTANT if weights_constant else 0, current_stream(x.device)))
     return y
 
 
