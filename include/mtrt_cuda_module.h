@@ -21,9 +21,13 @@
  *   ql:linear_w8a16;x=bf16;scale=f16;M=16;N=11008;K=4096                args: x, w, scale, y
  *   ql:linear_w4a16;x=f16;scale=f16;M=8;N=4096;K=4096;block=128         args: x, w, scale, y
  *   ql:gemm_fp8;out=bf16;M=8192;N=28672;K=8192;sx=1;sw=1                args: xq, wq, sx, sw, y
- * Arguments follow the reference's launch convention for statically shaped memrefs: args[i] points
- * to the i-th kernel parameter, each memref contributes its aligned base pointer only
- * (compiler/lib/Passes/1_Core/KernelToCUDA/KernelToCUDA.cpp:94-108, 163-175).
+ * Arguments follow the reference's launch convention (compiler/lib/Passes/1_Core/KernelToCUDA/KernelToCUDA.cpp:94-108,
+ * 163-175): args[i] points to the i-th kernel parameter; a memref contributes its aligned base pointer and then,
+ * only where they are not compile-time constants, its offset, dynamic sizes and dynamic strides as i64 values.  A
+ * dynamic dimension is written `?` in a spec (shape=?x4096, M=?): the kernel then reads that size (and the strides
+ * that depend on it, which must be the dense row-major ones) from the arguments after the memref's pointer:
+ *   ql:quantize;in=f32;out=i8;scale=f32;shape=?x4096        args: in, in.size0, scale, out, out.size0
+ *   ql:linear_w8a16;x=bf16;scale=f16;M=?;N=11008;K=4096     args: x, x.size0, w, scale, y, y.size0
  */
 #ifndef MTRT_CUDA_MODULE_H
 #define MTRT_CUDA_MODULE_H
@@ -74,6 +78,52 @@ MTRT_CAPI_EXPORTED int32_t mtrt_cuda_get_program_device(int32_t logicalId);
  * last failed mtrt_cuda_* call ("" if none), and the alias table described above. */
 MTRT_CAPI_EXPORTED const char *mtrt_cuda_last_error();
 MTRT_CAPI_EXPORTED int32_t ql_mtrt_bind_kernel(const char *kernel_name, const char *op_spec);
+
+/* Type-erased forms of the calls above, for host code generated through EmitC: that code passes every handle and
+ * buffer as `void *`, so each entry point has an inline `<name>_cwrapper` that casts and forwards (same names and
+ * parameter lists as mlir-tensorrt/executor/lib/Runtime/Backend/C/CUDAModule.h:130-205). */
+#define MTRT_CW static inline
+MTRT_CW void *mtrt_cuda_stream_create_cwrapper() { return (void *)mtrt_cuda_stream_create(); }
+MTRT_CW void mtrt_cuda_stream_destroy_cwrapper(void *stream) { mtrt_cuda_stream_destroy((CUstream)stream); }
+MTRT_CW void mtrt_cuda_stream_sync_cwrapper(void *stream) { mtrt_cuda_stream_sync((CUstream)stream); }
+MTRT_CW void *mtrt_cuda_event_create_cwrapper(int32_t device) { return (void *)mtrt_cuda_event_create(device); }
+MTRT_CW void mtrt_cuda_event_release_cwrapper(void *event) { mtrt_cuda_event_release((cudaEvent_t)event); }
+MTRT_CW void mtrt_cuda_stream_record_event_cwrapper(void *stream, void *event) {
+  mtrt_cuda_stream_record_event((CUstream)stream, (cudaEvent_t)event);
+}
+MTRT_CW void mtrt_cuda_stream_wait_event_cwrapper(void *stream, void *event) {
+  mtrt_cuda_stream_wait_event((CUstream)stream, (cudaEvent_t)event);
+}
+MTRT_CW void mtrt_cuda_event_sync_cwrapper(void *event) { mtrt_cuda_event_sync((cudaEvent_t)event); }
+MTRT_CW float mtrt_cuda_event_elapsed_msec_cwrapper(void *start, void *end) {
+  return mtrt_cuda_event_elapsed_msec((cudaEvent_t)start, (cudaEvent_t)end);
+}
+MTRT_CW void *mtrt_cuda_alloc_async_cwrapper(void *stream, int64_t size, int32_t alignment, int8_t isHostPinned, int8_t isManaged) {
+  return mtrt_cuda_alloc_async((CUstream)stream, size, alignment, isHostPinned, isManaged);
+}
+MTRT_CW void mtrt_cuda_memcpy_async_cwrapper(void *stream, void *src, void *dest, int64_t size) {
+  mtrt_cuda_memcpy_async((CUstream)stream, src, dest, size);
+}
+MTRT_CW void mtrt_cuda_free_cwrapper(void *stream, void *ptr, int8_t isHostPinned, int8_t isManaged) {
+  mtrt_cuda_free((CUstream)stream, ptr, isHostPinned, isManaged);
+}
+MTRT_CW void *mtrt_cuda_module_load_from_ptx_cwrapper(void *ptxData, size_t ptxLen) {
+  return (void *)mtrt_cuda_module_load_from_ptx((const char *)ptxData, ptxLen);
+}
+MTRT_CW void *mtrt_cuda_module_load_from_ptx_file_cwrapper(void *filename, size_t filenameLength) {
+  return (void *)mtrt_cuda_module_load_from_ptx_file((const char *)filename, filenameLength);
+}
+MTRT_CW void mtrt_cuda_module_unload_cwrapper(void *module) { mtrt_cuda_module_unload((CUmodule)module); }
+MTRT_CW void *mtrt_cuda_module_get_function_cwrapper(void *cumodule, void *name, int64_t length) {
+  return (void *)mtrt_cuda_module_get_function((CUmodule)cumodule, (const char *)name, length);
+}
+MTRT_CW void mtrt_cuda_launch_kernel_cwrapper(void *cudaFuncPtr, int32_t gridX, int32_t gridY, int32_t gridZ, int32_t blockX,
+                                              int32_t blockY, int32_t blockZ, int32_t dynamicSharedMemory, void *stream, void *args) {
+  mtrt_cuda_launch_kernel((CUfunction)cudaFuncPtr, gridX, gridY, gridZ, blockX, blockY, blockZ, dynamicSharedMemory, (CUstream)stream,
+                          (void **)args);
+}
+MTRT_CW int32_t mtrt_cuda_get_current_device_cwrapper() { return mtrt_cuda_get_current_device(); }
+#undef MTRT_CW
 
 #ifdef __cplusplus
 }

@@ -248,6 +248,32 @@ QL_API int ql_gemm_status(int32_t *code);
  * process; this makes it read them again (not thread-safe against GEMM calls in flight on other host threads). */
 QL_API int ql_reload_tuning(void);
 
+/* ---- Compiled executables (`.rtexe`).  The reference's translation step writes a FlatBuffers file
+ * (executor/include/mlir-executor/Runtime/API/Executable.fbs) whose data segments carry, among the program's
+ * constants, the PTX or cubin of each cuda.compiled_module; its runtime hands those bytes to __cuda_load_module
+ * (executor/lib/Runtime/Backend/Lua/Modules/CUDA/CUDAModule.cpp:287-300), i.e. to mtrt_cuda_module_load_from_ptx.
+ * These calls read the same segments without that runtime (host side only, no GPU needed); in addition
+ * mtrt_cuda_module_load_from_ptx_file accepts "path/program.rtexe#segment_name". */
+typedef struct ql_rtexe ql_rtexe;
+typedef enum { QL_RTEXE_DATA = 0, QL_RTEXE_PTX = 1, QL_RTEXE_CUBIN = 2, QL_RTEXE_FATBIN = 3 } ql_rtexe_kind;
+typedef struct {
+  const char *name;            /* the global's symbol name; valid until ql_rtexe_close */
+  const void *data;            /* the segment's bytes inside the opened file (null when it has none) */
+  uint64_t size;
+  uint64_t uninitialized_size; /* size of a segment that is only reserved, not filled */
+  uint32_t alignment;
+  int32_t constant;
+  int32_t address_space;       /* PointerType of the schema: 0 host, 1 pinned_host, 2 device, 3 unified, 4 unknown */
+  int32_t kind;                /* ql_rtexe_kind, guessed from the bytes */
+} ql_rtexe_segment_info;
+QL_API int ql_rtexe_open(const char *path, ql_rtexe **out);
+QL_API int ql_rtexe_open_memory(const void *bytes, uint64_t size, ql_rtexe **out); /* the bytes are copied */
+QL_API void ql_rtexe_close(ql_rtexe *exe);
+QL_API const char *ql_rtexe_name(const ql_rtexe *exe);
+QL_API int32_t ql_rtexe_num_segments(const ql_rtexe *exe);
+QL_API int ql_rtexe_segment(const ql_rtexe *exe, int32_t index, ql_rtexe_segment_info *info);
+QL_API int ql_rtexe_find_segment(const ql_rtexe *exe, const char *name); /* index, or -1 */
+
 #ifdef __cplusplus
 }
 #endif

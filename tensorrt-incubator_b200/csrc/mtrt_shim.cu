@@ -140,34 +140,69 @@ int dtype_of(const std::string &s) {
   return -1;
 }
 
-bool shape_of(const std::string &s, ql_tensor *t) {
+std::string get(const OpSpec &s, const char *k, const char *dflt = "") {
+  auto it = s.kv.find(k);
+  return it == s.kv.end() ? std::string(dflt) : it->second;
+}
+
+// args[i] points at the i-th kernel parameter.  A memref parameter arrives unpacked, as the compiler's launch
+// convention lays it out (compiler/lib/Passes/1_Core/KernelToCUDA/KernelToCUDA.cpp:94-108): the aligned base
+// pointer, then -- only where they are not compile-time constants -- the offset, every dynamic size and every
+// dynamic stride, each an `index` (i64).  In a kernel spec a dynamic dimension is written `?` (shape=?x4096,
+// M=?); for the dense row-major memrefs these kernels take, the offset is the constant 0 and stride i is dynamic
+// exactly when a dimension to its right is, so the cursor below knows how many values follow each pointer.
+struct ArgCursor {
+  void **args;
+  int next;
+  bool ok;
+  void *pointer() { return *reinterpret_cast<void **>(args[next++]); }
+  int64_t index() { return *reinterpret_cast<int64_t *>(args[next++]); }
+  // Fills t->data and resolves the `?` dimensions of t (marked by -1) from the arguments.
+  void memref(ql_tensor *t) {
+    t->data = pointer();
+    bool dynamic_right[QL_MAX_RANK + 1] = {false};
+    for (int i = t->rank - 1; i >= 0; i--) dynamic_right[i] = dynamic_right[i + 1] || t->shape[i] < 0;
+    for (int i = 0; i < t->rank; i++)
+      if (t->shape[i] < 0) {
+        t->shape[i] = index();
+        if (t->shape[i] < 0) ok = false;
+      }
+    // the dynamic strides follow the sizes, outermost first; each must be the dense one
+    int64_t expect[QL_MAX_RANK];
+    int64_t run = 1;
+    for (int i = t->rank - 1; i >= 0; i--) {
+      expect[i] = run;
+      run *= t->shape[i];
+    }
+    for (int i = 0; i < t->rank; i++)
+      if (dynamic_right[i + 1] && index() != expect[i]) ok = false;
+  }
+};
+
+bool shape_spec(const std::string &s, ql_tensor *t) { // "4096x4096", "?x4096" (`?` = -1, resolved from the arguments), "" = scalar
   t->rank = 0;
   if (s.empty() || s == "scalar") return true;
   std::stringstream ss(s);
   std::string d;
   while (std::getline(ss, d, 'x')) {
     if (t->rank >= QL_MAX_RANK) return false;
-    t->shape[t->rank++] = atoll(d.c_str());
+    t->shape[t->rank++] = (d == "?") ? -1 : atoll(d.c_str());
   }
   return true;
 }
 
-std::string get(const OpSpec &s, const char *k, const char *dflt = "") {
-  auto it = s.kv.find(k);
-  return it == s.kv.end() ? std::string(dflt) : it->second;
-}
-
-// args[i] points at the i-th kernel parameter; memref parameters are device pointers
-void *ptr_arg(void **args, int i) { return *reinterpret_cast<void **>(args[i]); }
+int64_t dim_spec(const std::string &v) { return v == "?" ? -1 : atoll(v.c_str()); }
 
 void launch_library_kernel(const OpSpec &s, CUstream stream, void **args) {
   int rc = QL_OK;
+  ArgCursor cur{args, 0, true};
+  const char *strided = "a memref argument is not dense row-major (dynamic stride differs from the dense one) or has a negative size";
   if (s.op == "quantize" || s.op == "dequantize") {
     ql_tensor in{}, sc{}, out{};
     in.dtype = dtype_of(get(s, "in"));
     out.dtype = dtype_of(get(s, "out"));
     sc.dtype = dtype_of(get(s, "scale", "f32"));
-    if (!shape_of(get(s, "shape"), &in)) return fail("bad shape in kernel spec");
+    if (!shape_spec(get(s, "shape"), &in)) return fail("bad shape in kernel spec");
     out.rank = in.rank;
     memcpy(out.shape, in.shape, sizeof(in.shape));
     ql_qdq_attrs at{};
@@ -177,34 +212,49 @@ void launch_library_kernel(const OpSpec &s, CUstream stream, void **args) {
       at.axis = atoi(axis.c_str());
       sc.rank = 1;
       sc.shape[0] = (at.axis >= 0 && at.axis < in.rank) ? in.shape[at.axis] : 0;
-    } else if (!shape_of(get(s, "scale_shape"), &sc)) {
+    } else if (!shape_spec(get(s, "scale_shape"), &sc)) {
       return fail("bad scale_shape in kernel spec");
     }
     std::string mode = get(s, "fp8_mode", "direct");
     at.fp8_mode = mode == "via_f16" ? QL_FP8_VIA_F16 : mode == "stablehlo" ? QL_FP8_STABLEHLO : QL_FP8_DIRECT;
-    in.data = ptr_arg(args, 0);
-    sc.data = ptr_arg(args, 1);
-    out.data = ptr_arg(args, 2);
+    cur.memref(&in);
+    cur.memref(&sc);
+    cur.memref(&out);
+    if (!cur.ok) return fail("%s", strided);
     rc = (s.op == "quantize") ? ql_quantize(&in, &sc, &out, &at, stream) : ql_dequantize(&in, &sc, &out, &at, stream);
   } else if (s.op == "linear_w8a16" || s.op == "linear_w4a16") {
-    const int64_t M = atoll(get(s, "M").c_str()), N = atoll(get(s, "N").c_str()), K = atoll(get(s, "K").c_str());
+    const int64_t M = dim_spec(get(s, "M")), N = atoll(get(s, "N").c_str()), K = atoll(get(s, "K").c_str());
     const int xd = dtype_of(get(s, "x", "bf16"));
-    ql_tensor x{ptr_arg(args, 0), xd, 2, {M, K}}, y{ptr_arg(args, 3), xd, 2, {M, N}};
+    ql_tensor x{nullptr, xd, 2, {M, K}}, y{nullptr, xd, 2, {M, N}}, w{nullptr, s.op == "linear_w8a16" ? QL_I8 : QL_I4, 2, {N, K}}, sc{};
+    sc.dtype = dtype_of(get(s, "scale", "f16"));
     if (s.op == "linear_w8a16") {
-      ql_tensor w{ptr_arg(args, 1), QL_I8, 2, {N, K}}, sc{ptr_arg(args, 2), dtype_of(get(s, "scale", "f16")), 1, {N}};
-      rc = ql_linear_w8a16(&x, &w, &sc, &y, stream);
+      sc.rank = 1;
+      sc.shape[0] = N;
     } else {
       const int64_t B = atoll(get(s, "block", "128").c_str());
-      ql_tensor w{ptr_arg(args, 1), QL_I4, 2, {N, K}}, sc{ptr_arg(args, 2), dtype_of(get(s, "scale", "f16")), 2, {N, B > 0 ? K / B : 0}};
-      rc = ql_linear_w4a16(&x, &w, &sc, &y, stream);
+      sc.rank = 2;
+      sc.shape[0] = N;
+      sc.shape[1] = B > 0 ? K / B : 0;
     }
+    cur.memref(&x);
+    cur.memref(&w);
+    cur.memref(&sc);
+    cur.memref(&y);
+    if (!cur.ok) return fail("%s", strided);
+    rc = s.op == "linear_w8a16" ? ql_linear_w8a16(&x, &w, &sc, &y, stream) : ql_linear_w4a16(&x, &w, &sc, &y, stream);
   } else if (s.op == "gemm_fp8" || s.op == "gemm_i8") {
-    const int64_t M = atoll(get(s, "M").c_str()), N = atoll(get(s, "N").c_str()), K = atoll(get(s, "K").c_str());
+    const int64_t M = dim_spec(get(s, "M")), N = atoll(get(s, "N").c_str()), K = atoll(get(s, "K").c_str());
     const int qd = s.op == "gemm_fp8" ? QL_F8E4M3 : QL_I8;
-    const int64_t nsx = atoll(get(s, "sx", "1").c_str()), nsw = atoll(get(s, "sw", "1").c_str());
-    ql_tensor x{ptr_arg(args, 0), qd, 2, {M, K}}, w{ptr_arg(args, 1), qd, 2, {N, K}};
-    ql_tensor sx{ptr_arg(args, 2), QL_F32, nsx == 1 ? 0 : 1, {nsx}}, sw{ptr_arg(args, 3), QL_F32, nsw == 1 ? 0 : 1, {nsw}};
-    ql_tensor y{ptr_arg(args, 4), dtype_of(get(s, "out", "bf16")), 2, {M, N}};
+    const int64_t nsx = dim_spec(get(s, "sx", "1")), nsw = atoll(get(s, "sw", "1").c_str());
+    ql_tensor x{nullptr, qd, 2, {M, K}}, w{nullptr, qd, 2, {N, K}};
+    ql_tensor sx{nullptr, QL_F32, nsx == 1 ? 0 : 1, {nsx}}, sw{nullptr, QL_F32, nsw == 1 ? 0 : 1, {nsw}};
+    ql_tensor y{nullptr, dtype_of(get(s, "out", "bf16")), 2, {M, N}};
+    cur.memref(&x);
+    cur.memref(&w);
+    cur.memref(&sx);
+    cur.memref(&sw);
+    cur.memref(&y);
+    if (!cur.ok) return fail("%s", strided);
     rc = s.op == "gemm_fp8" ? ql_gemm_fp8(&x, &w, &sx, &sw, &y, stream) : ql_gemm_i8(&x, &w, &sx, &sw, &y, stream);
   } else if (s.op == "dynamic_quantize") {
     // args: input, double_quant_scale (rank 0), result (f4), scales (f8)
@@ -213,17 +263,18 @@ void launch_library_kernel(const OpSpec &s, CUstream stream, void **args) {
     gs.dtype = dtype_of(get(s, "scale", "f32"));
     out.dtype = QL_F4E2M1;
     sc.dtype = QL_F8E4M3;
-    if (!shape_of(get(s, "shape"), &in) || in.rank < 1) return fail("bad shape in kernel spec");
+    if (!shape_spec(get(s, "shape"), &in) || in.rank < 1) return fail("bad shape in kernel spec");
     const int axis = atoi(get(s, "axis", "-1").c_str());
     const int ax = axis < 0 ? in.rank + axis : axis;
     out.rank = sc.rank = in.rank;
     memcpy(out.shape, in.shape, sizeof(in.shape));
     memcpy(sc.shape, in.shape, sizeof(in.shape));
-    if (ax >= 0 && ax < in.rank) sc.shape[ax] = in.shape[ax] / 16;
-    in.data = ptr_arg(args, 0);
-    gs.data = ptr_arg(args, 1);
-    out.data = ptr_arg(args, 2);
-    sc.data = ptr_arg(args, 3);
+    if (ax >= 0 && ax < in.rank && in.shape[ax] >= 0) sc.shape[ax] = in.shape[ax] / 16;
+    cur.memref(&in);
+    cur.memref(&gs);
+    cur.memref(&out);
+    cur.memref(&sc);
+    if (!cur.ok) return fail("%s", strided);
     rc = ql_dynamic_quantize(&in, &gs, ax, atoi(get(s, "block_size", "16").c_str()), &out, &sc, stream);
   } else {
     return fail("unknown library kernel '%s'", s.op.c_str());
@@ -343,6 +394,22 @@ CUmodule mtrt_cuda_module_load_from_ptx(const char *ptxData, size_t ptxLen) {
 
 CUmodule mtrt_cuda_module_load_from_ptx_file(const char *filename, size_t filenameLength) {
   std::string path(filename ? filename : "", filenameLength);
+  // "program.rtexe#segment": the module bytes are a data segment of a compiled executable
+  const size_t hash = path.rfind('#');
+  if (hash != std::string::npos && hash >= 6 && path.compare(hash - 6, 6, ".rtexe") == 0) {
+    ql_rtexe *exe = nullptr;
+    if (ql_rtexe_open(path.substr(0, hash).c_str(), &exe) != QL_OK) {
+      fail("could not open artifact '%s': %s", path.c_str(), ql_last_error());
+      return nullptr;
+    }
+    const int idx = ql_rtexe_find_segment(exe, path.substr(hash + 1).c_str());
+    ql_rtexe_segment_info info;
+    CUmodule mod = nullptr;
+    if (idx < 0 || ql_rtexe_segment(exe, idx, &info) != QL_OK) fail("executable '%s' has no data segment '%s'", path.substr(0, hash).c_str(), path.substr(hash + 1).c_str());
+    else mod = mtrt_cuda_module_load_from_ptx(static_cast<const char *>(info.data), (size_t)info.size);
+    ql_rtexe_close(exe);
+    return mod;
+  }
   std::ifstream f(path, std::ios::binary);
   if (!f) {
     fail("could not open artifact '%s'", path.c_str());

@@ -203,3 +203,23 @@ def test_linear_and_matmul_argument_rules():
         L.ql_matmul(_t(_lib.F32, [2, 1, 3, 4]), _t(_lib.F32, [2, 6, 4, 5]), _t(_lib.F32, [2, 6, 3, 5]), None))
     # empty products are no-ops even without a device
     assert L.ql_matmul(_t(_lib.F32, [0, 3, 4]), _t(_lib.F32, [0, 4, 5]), _t(_lib.F32, [0, 3, 5]), None) == 0
+
+
+def test_emitc_wrappers_compile_as_c_and_link(tmp_path):
+    """The `_cwrapper` inlines of the launch-ABI header (C/CUDAModule.h:130-205 of the reference), used from plain C
+    the way EmitC-generated host code uses them, compiled and linked against the library (never run)."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None or not os.path.exists("/usr/local/cuda/include/cuda.h"):
+        pytest.skip("needs gcc and the CUDA headers")
+    src = os.path.join(ROOT, "tests", "golden", "emitc_host_stub.c")
+    out = str(tmp_path / "libemitc_stub.so")
+    env = {k: v for k, v in os.environ.items() if k not in ("CC", "CXX")}
+    r = subprocess.run([gcc, "-std=c11", "-Wall", "-Werror", "-shared", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", "/usr/local/cuda/include",
+                        src, "-o", out, "-L", os.path.dirname(_lib.LIB_PATH), "-lqlinear_b200", "-Wl,--no-undefined", "-Wl,-rpath," + os.path.dirname(_lib.LIB_PATH)],
+                       capture_output=True, text=True, env=env)
+    assert r.returncode == 0, r.stderr
+    text = open(os.path.join(ROOT, "include", "mtrt_cuda_module.h")).read()
+    wrappers = set(re.findall(r"\b(mtrt_cuda_\w+)_cwrapper\s*\(", text))
+    assert len(wrappers) == 18 and wrappers <= set(_declared_symbols())

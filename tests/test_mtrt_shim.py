@@ -207,3 +207,51 @@ def test_nvfp4_through_the_launch_abi(rt):
     assert rt.mtrt_cuda_last_error() == b""
     assert np.array_equal(y.cpu().numpy(), orc.dequantize_nvfp4(want_q, want_s, 1.0, orc.F32))
     rt.mtrt_cuda_module_unload(mod)
+
+
+@pytest.mark.gpu
+def test_dynamic_shape_memrefs_through_the_launch_abi(rt):
+    """A program compiled with a dynamic batch dimension: each memref with a `?` dimension is followed in `args` by
+    that size (and by the strides that depend on it) as i64 values, the way the compiler unpacks memrefs
+    (compiler/lib/Passes/1_Core/KernelToCUDA/KernelToCUDA.cpp:94-108).  Same results as the static spelling."""
+    mod = rt.mtrt_cuda_module_load_from_ptx(b"", 0)
+    stream = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator(device="cpu").manual_seed(21)
+    i64, vp = ctypes.c_int64, ctypes.c_void_p
+    # quantize f32 [?, 256] -> i8 with rows = 48: args are in, in.size0, scale, out, out.size0
+    rows = 48
+    x = torch.randn((rows, 256), generator=g).cuda()
+    s = (x.abs().max() / 127).reshape(())
+    q = torch.empty((rows, 256), dtype=torch.int8, device="cuda")
+    name = b"ql:quantize;in=f32;out=i8;scale=f32;shape=?x256"
+    arr, keep = _args(vp(x.data_ptr()), i64(rows), vp(s.data_ptr()), vp(q.data_ptr()), i64(rows))
+    rt.mtrt_cuda_launch_kernel(rt.mtrt_cuda_module_get_function(mod, name, len(name)), 1, 1, 1, 1, 1, 1, 0, stream, arr)
+    torch.cuda.synchronize()
+    assert rt.mtrt_cuda_last_error() == b""
+    assert torch.equal(q, ql.quantize(x, s, ql.int8))
+    # a dynamic inner dimension makes the outer stride dynamic too: [4, ?] passes size1 and then stride0
+    x2 = x[:4].contiguous()
+    q2 = torch.empty((4, 256), dtype=torch.int8, device="cuda")
+    name = b"ql:quantize;in=f32;out=i8;scale=f32;shape=4x?"
+    arr, keep = _args(vp(x2.data_ptr()), i64(256), i64(256), vp(s.data_ptr()), vp(q2.data_ptr()), i64(256), i64(256))
+    rt.mtrt_cuda_launch_kernel(rt.mtrt_cuda_module_get_function(mod, name, len(name)), 1, 1, 1, 1, 1, 1, 0, stream, arr)
+    torch.cuda.synchronize()
+    assert rt.mtrt_cuda_last_error() == b"" and torch.equal(q2, q[:4])
+    # a stride that is not the dense one is refused, not misread
+    arr, keep = _args(vp(x2.data_ptr()), i64(256), i64(512), vp(s.data_ptr()), vp(q2.data_ptr()), i64(256), i64(256))
+    rt.mtrt_cuda_launch_kernel(rt.mtrt_cuda_module_get_function(mod, name, len(name)), 1, 1, 1, 1, 1, 1, 0, stream, arr)
+    assert b"not dense row-major" in rt.mtrt_cuda_last_error()
+    # W8A16 linear with a dynamic number of tokens: x, x.size0, w, scale, y, y.size0
+    w = (torch.randn((32, 128), generator=g) * 0.02).to(torch.float16).cuda()
+    ws = ql.amax_scale(w, ql.int8, dim=0)
+    wq = ql.quantize(w, ws, ql.int8, 0)
+    for m in (3, 20):
+        xa = torch.randn((m, 128), generator=g).to(torch.bfloat16).cuda()
+        y = torch.empty((m, 32), dtype=torch.bfloat16, device="cuda")
+        name = b"ql:linear_w8a16;x=bf16;scale=f16;M=?;N=32;K=128"
+        arr, keep = _args(vp(xa.data_ptr()), i64(m), vp(wq.data_ptr()), vp(ws.data_ptr()), vp(y.data_ptr()), i64(m))
+        rt.mtrt_cuda_launch_kernel(rt.mtrt_cuda_module_get_function(mod, name, len(name)), 1, 1, 1, 1, 1, 1, 0, stream, arr)
+        torch.cuda.synchronize()
+        assert rt.mtrt_cuda_last_error() == b""
+        assert torch.equal(y, ql.linear_w8a16(xa, wq, ws))
+    rt.mtrt_cuda_module_unload(mod)
