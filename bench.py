@@ -44,8 +44,10 @@ TRAFFIC = {
     "config2_w8a16_linear:M=2048": 198_069_248,               # includes the 16-bit scratch copy of the weights, written and read back
     "config3_w4a16_linear:M=1": 8_668_416, "config3_w4a16_linear:M=8": 8_726_016, "config3_w4a16_linear:M=32": 8_924_160,
     "config4_fp8_w8a8_gemm:fp8_gemm": 1_593_066_736,
-    "config5_fp8_mlp_block:rmsnorm_quant": 72_830_976, "config5_fp8_mlp_block:gate_up_gemm": 1_712_782_648,
-    "config5_fp8_mlp_block:swiglu_quant": 559_550_512, "config5_fp8_mlp_block:down_gemm": 1_070_384_104,
+    "config5_fp8_mlp_block:rmsnorm_quant": 72_518_400, "config5_fp8_mlp_block:gate_up_gemm": 1_712_782_648,
+    "config5_fp8_mlp_block:gate_up_gemm_swiglu": 1_246_894_040,   # weights streamed once per band of 2048 tokens (two bands)
+    "config5_fp8_mlp_block:quantize_rows": 314_609_664,           # part of the output still dirty in L2 when the kernel ends
+    "config5_fp8_mlp_block:swiglu_quant": 559_550_512, "config5_fp8_mlp_block:down_gemm": 1_051_541_624,
 }
 
 
@@ -717,7 +719,67 @@ class Nvfp4Qdq(Workload):
                 "l2": f"{self.REPLICAS} input/output replicas (876 MiB > 126 MiB L2) cycled per step", "seed": 1006}
 
 
-WORKLOADS = {"c1": QdqInt8, "c2": W8A16Linear, "c3": W4A16Linear, "c4": Fp8Gemm, "c5": Fp8Mlp, "nvfp4": Nvfp4Qdq}
+class Nvfp4Gemm(Workload):
+    """Not a BASELINE config: the block-scaled NVFP4 GEMM on config 4's shape.  X bf16 [8192,8192] ~ N(0,1) goes through
+    tensorrt.dynamic_quantize every step; W [28672,8192] ~ N(0,0.02) was quantized once; Y = dq(Xq) . dq(Wq)^T, bf16."""
+
+    name = "nvfp4_block_scaled_gemm"
+    metric = "quantized GEMM TFLOP/s (NVFP4 block-scaled GEMM, 8192x8192x28672, activations quantized every step)"
+    unit = "TFLOP/s"
+    dtype = "e2m1 x e2m1, e4m3 block scales -> f32 accumulate -> bf16"
+    M, K, N = 8192, 8192, 28672
+    use_graphs = False
+
+    def __init__(self, torch, ql, device, dist=None, seed=1007):
+        self.torch, self.ql, self.device = torch, ql, device
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        self.x_host = torch.randn((self.M, self.K), generator=g, dtype=torch.float32).to(torch.bfloat16).pin_memory()
+        self.x = self.x_host.to(device)
+        wq, ws = [], []
+        for r0 in range(0, self.N, 4096):
+            blk = (torch.randn((4096, self.K), generator=g, dtype=torch.float32) * 0.02).to(torch.bfloat16).to(device)
+            d, sc = ql.dynamic_quantize(blk, 1.0)
+            wq.append(d.packed)
+            ws.append(sc)
+        self.wq = ql.Float4Tensor(torch.cat(wq), (self.N, self.K))
+        self.ws = torch.cat(ws, dim=0).contiguous()
+        self.xq, self.xs = ql.dynamic_quantize(self.x, 1.0)
+        self.y = torch.empty((self.M, self.N), dtype=torch.bfloat16, device=device)
+        self.y_host = torch.empty((self.M, self.N), dtype=torch.bfloat16).pin_memory()
+        from qlinear import _lib
+        from qlinear.tensor import current_stream, ql_view
+        self._lib, self._view, self._stream = _lib, ql_view, current_stream
+        self.gs = torch.ones((), dtype=torch.float32, device=device)
+
+    def p_quant(self):
+        L = self._lib
+        L.check(L.lib().ql_dynamic_quantize(self._view(self.x), self._view(self.gs), 1, 16, self._view(self.xq), self._view(self.xs), self._stream(self.device)))
+
+    def p_gemm(self):
+        self.ql.gemm_nvfp4(self.xq, self.xs, self.wq, self.ws, out=self.y)
+
+    def parts(self):
+        M, K, N = self.M, self.K, self.N
+        n = M * K
+        return [("dynamic_quantize_x", self.p_quant, 0, 2 * n + n // 2 + n // 16, "hbm"),
+                ("nvfp4_gemm", self.p_gemm, 2 * M * N * K, (M + N) * (K // 2 + K // 16) + 2 * M * N, "tensor_fp4")]
+
+    def e2e_units(self, step):
+        def run():
+            self.p_quant()
+            self.p_gemm()
+        return [(("x", 0), ("y", 0), (lambda: self.x.copy_(self.x_host, non_blocking=True)), run,
+                 (lambda: self.y_host.copy_(self.y, non_blocking=True)))]
+
+    def e2e_bytes(self):
+        return 2 * self.M * self.K, 2 * self.M * self.N
+
+    def config(self):
+        return {"workload": self.name, "M": self.M, "K": self.K, "N": self.N, "block": 16, "double_quant_scale": 1.0,
+                "l2": "operands and output (>= 600 MiB) exceed the 126 MiB L2", "seed": 1007}
+
+
+WORKLOADS = {"nvfp4gemm": Nvfp4Gemm, "c1": QdqInt8, "c2": W8A16Linear, "c3": W4A16Linear, "c4": Fp8Gemm, "c5": Fp8Mlp, "nvfp4": Nvfp4Qdq}
 
 
 # ----------------------------------------------------------------------------------------------
@@ -825,6 +887,21 @@ def cpu_reference(workload: str, budget_s: float = 12.0):
         dt = time.perf_counter() - t0
         n = rows * K
         return (2 * n + n // 2 + n // 16) * 2.0 * reps / dt / 1e9, "GB/s", cores, f"{reps} x (dynamic_quantize + dequantize) of {rows} x {K} bf16 elements, {dt:.1f} s"
+    if workload == "nvfp4gemm":
+        K = 8192
+        def sample(mm, nn):
+            a = orc.from_f32(rng.standard_normal((mm, K)).astype(np.float32), orc.BF16)
+            b = orc.from_f32((rng.standard_normal((nn, K)) * 0.02).astype(np.float32), orc.BF16)
+            t0 = time.perf_counter()
+            qa, sa = orc.dynamic_quantize_nvfp4(a, orc.BF16, 1.0)
+            qb, sb = orc.dynamic_quantize_nvfp4(b, orc.BF16, 1.0)
+            orc.matmul(orc.dequantize_nvfp4(qa, sa, 1.0, orc.F32), np.ascontiguousarray(orc.dequantize_nvfp4(qb, sb, 1.0, orc.F32).T), orc.F32)
+            return time.perf_counter() - t0
+        t1 = sample(32, 64)
+        grow = (budget_s / max(t1, 1e-4)) ** 0.5
+        mm, nn = int(min(8192, max(32, 32 * grow))), int(min(28672, max(64, 64 * grow)))
+        dt = sample(mm, nn)
+        return 2.0 * mm * nn * K / dt / 1e12, "TFLOP/s", cores, f"{mm} of 8192 rows x {nn} of 28672 columns x K={K}: dynamic_quantize, dequantize, f32 product, {dt:.1f} s"
     raise SystemExit(f"no CPU restatement for workload {workload}")
 
 
@@ -945,6 +1022,8 @@ def peak_of(bound, peaks, lib_fp8=None):
         if lib_fp8:
             note += f"; cuBLASLt fp8 on the same operands in this process: {lib_fp8:.0f} TFLOP/s"
         return "tensor", 2 * peaks["bf16_tflops"], "TFLOP/s", note
+    if bound == "tensor_fp4":
+        return "tensor", 4 * peaks["bf16_tflops"], "TFLOP/s", "4 x measured cuBLAS bf16 burst (no fp4 peak is measured by the driver)"
     if bound == "nvlink":
         return "nvlink", 770.0, "GB/s", "peer copy per direction measured on this pool (900 nominal)"
     return "hbm", peaks["hbm_gbs"], "GB/s", "measured copy bandwidth"

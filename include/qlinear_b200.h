@@ -129,6 +129,16 @@ QL_API int ql_dynamic_quantize(const ql_tensor *input, const ql_tensor *double_q
 QL_API int ql_dequantize_nvfp4(const ql_tensor *data, const ql_tensor *scales, const ql_tensor *double_quant_scale,
                                ql_tensor *output, void *stream);
 
+/* Block-scaled NVFP4 GEMM: Y[M,N] = dq(a)[M,K] . dq(b)[N,K]^T with dq(x)[r,k] = e2m1 * e4m3 scale[r, k/16] * global, i.e.
+ * tensorrt.matrix_multiply of two operands that went through tensorrt.dynamic_quantize and its two dequantize steps
+ * (TensorRTOps.td:3279-3358, 1986-2080), with the dequantization done by the tensor core
+ * (tcgen05.mma kind::mxf4nvf4, block scales read from tensor memory; f32 accumulation).  a, b: QL_F4E2M1 [M,K], [N,K];
+ * *_scales: QL_F8E4M3 [rows, K/16] as ql_dynamic_quantize writes them; *_global: f32 scalar or null (= 1);
+ * y: f32 | f16 | bf16.  Needs K % 32 == 0 and 16-byte aligned data (QL_ERR_UNSUPPORTED otherwise: dequantize and
+ * use ql_linear).  Takes scratch for the re-ordered scales from the stream-ordered allocator. */
+QL_API int ql_gemm_nvfp4(const ql_tensor *a, const ql_tensor *a_scales, const ql_tensor *a_global, const ql_tensor *b,
+                         const ql_tensor *b_scales, const ql_tensor *b_global, ql_tensor *y, void *stream);
+
 /* Weight-only linear layers, Y[M,N] = X[M,K] . dequantize(W)[N,K]^T with f32 accumulation
  * (linear.py:140-151 with quant_dtype set and no input scale).
  *   w8: W int8 [N,K], scale [N] per output channel (weight_quant_dim = 0)

@@ -364,6 +364,15 @@ def dequantize_nvfp4(q, scales, double_quant_scale, y_code):
     return y
 
 
+def gemm_nvfp4(qa, sa, ga, qb, sb, gb):
+    """dequantize_nvfp4(a) @ dequantize_nvfp4(b)^T in f64 (the reference's documented use of dynamic_quantize:
+    dequantize twice, then matrix_multiply; TensorRTOps.td:3279-3358): qa [M, K/2] packed e2m1 bytes, sa [M, K/16] e4m3
+    bits, ga the double-quantization scale; likewise b [N, ...].  Returns float64 [M, N]."""
+    a = dequantize_nvfp4(qa, sa, ga, F32).astype(np.float64)
+    b = dequantize_nvfp4(qb, sb, gb, F32).astype(np.float64)
+    return a @ b.T
+
+
 def f8_to_f32(bits: np.ndarray) -> np.ndarray:
     """e4m3 bit patterns -> float32 values."""
     L = lib()

@@ -68,6 +68,7 @@ SIGNATURES = {
     "ql_amax_scale_noalloc": ([_T, _T, _A, ctypes.c_float, _S], ctypes.c_int),
     "ql_dynamic_quantize": ([_T, _T, ctypes.c_int32, ctypes.c_int32, _T, _T, _S], ctypes.c_int),
     "ql_dequantize_nvfp4": ([_T, _T, _T, _T, _S], ctypes.c_int),
+    "ql_gemm_nvfp4": ([_T, _T, _T, _T, _T, _T, _T, _S], ctypes.c_int),
     "ql_linear_w8a16": ([_T, _T, _T, _T, _S], ctypes.c_int),
     "ql_linear_w4a16": ([_T, _T, _T, _T, _S], ctypes.c_int),
     "ql_linear_weight_only": ([_T, _T, _T, _T, ctypes.c_uint32, _S], ctypes.c_int),

@@ -95,10 +95,10 @@ class QuantizedMLP:
         "auto" = over peer memory when the box supports it and the group has several ranks; "scatter" / "switch" /
         "pipeline" = a given protocol whatever the group size (see _buffers).
 
-        With a peer protocol the result is this rank's replica of an internal two-buffer set: it stays valid until
-        the call after next starts (the next call clears or overwrites the other buffer, the one after that this
-        one).  Copy it if it must live longer.  The NCCL path returns an internal buffer that the next call
-        overwrites."""
+        The result is an internal buffer, valid until the next call.  With a peer protocol it is this rank's
+        replica of one of two buffers used in turn: the add protocols clear it during the next call (it is the
+        buffer the call after next adds into); the switch protocols overwrite it one call later.  The NCCL path
+        returns a buffer that the next call overwrites.  Copy the result if it must live longer."""
         self.eps, self.group = eps, group
         self._force = fused_all_reduce if fused_all_reduce in ("scatter", "switch", "pipeline") else None   # a protocol on any group size
         self.slabs = 4        # token slabs of the pipelined protocol

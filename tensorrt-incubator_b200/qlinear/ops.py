@@ -214,5 +214,22 @@ def dequantize_nvfp4(data: Float4Tensor, scales: torch.Tensor, double_quant_scal
     require_cuda(data, "data")
     gs = _global_scale(double_quant_scale, data.device)
     y = torch.empty(data.shape, dtype=dtype.torch, device=data.device)
-    _lib.check(_lib.lib().ql_dequantize_nvfp4(ql_view(data), ql_view(scales.contiguous()), ql_view(gs), ql_view(y), current_stream(data.device)))
+    sc = scales.contiguous()   # kept alive across the call: a view only borrows the pointer
+    _lib.check(_lib.lib().ql_dequantize_nvfp4(ql_view(data), ql_view(sc), ql_view(gs), ql_view(y), current_stream(data.device)))
+    return y
+
+
+def gemm_nvfp4(a: Float4Tensor, a_scales: torch.Tensor, b: Float4Tensor, b_scales: torch.Tensor, a_global=None, b_global=None,
+               out_dtype: dt.dtype = dt.bfloat16, out=None) -> torch.Tensor:
+    """dequantize_nvfp4(a) @ dequantize_nvfp4(b)^T on the block-scaled tensor cores: a [M,K], b [N,K] and their e4m3
+    block scales as dynamic_quantize returns them; `a_global` / `b_global` the double-quantization scales (None = 1)."""
+    require_cuda(a, "a")
+    require_cuda(b, "b")
+    y = out if out is not None else torch.empty((a.shape[0], b.shape[0]), dtype=out_dtype.torch, device=a.device)
+    # the scale tensors must outlive the call: a view only borrows the pointer
+    ta = _global_scale(a_global, a.device) if a_global is not None else None
+    tb = _global_scale(b_global, b.device) if b_global is not None else None
+    sa, sb = a_scales.contiguous(), b_scales.contiguous()
+    _lib.check(_lib.lib().ql_gemm_nvfp4(ql_view(a), ql_view(sa), ql_view(ta) if ta is not None else None, ql_view(b), ql_view(sb),
+                                        ql_view(tb) if tb is not None else None, ql_view(y), current_stream(a.device)))
     return y

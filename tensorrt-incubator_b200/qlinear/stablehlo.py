@@ -369,7 +369,8 @@ class Program:
                 q, s = ins
                 q = q if isinstance(q, (Int4Tensor, Float4Tensor)) else q.contiguous()
                 y = torch.empty(tuple(q.shape), dtype=st.attrs["dtype"].torch, device=q.device)
-                _lib.check(_lib.lib().ql_dequantize(ql_view(q), ql_view(s.contiguous()), ql_view(y), _lib.make_attrs(st.attrs["axis"]),
+                s = s.contiguous()
+                _lib.check(_lib.lib().ql_dequantize(ql_view(q), ql_view(s), ql_view(y), _lib.make_attrs(st.attrs["axis"]),
                                                     current_stream(y.device)))
                 slots[st.out] = y
             elif st.op == "linear_w8a16":

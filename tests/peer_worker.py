@@ -125,6 +125,22 @@ def main():
             e = rel_err(got, want)
             assert e < 2e-2, f"rank {rank}: fused MLP ({name}) call {i} off by {e}"
             assert same_everywhere(got), f"fused MLP ({name}) call {i}: ranks disagree"
+    # Lifetime of the result of a peer protocol: it is this rank's replica of one of two internal buffers and is only
+    # promised until the next call.  The add protocols clear it during that call (the whole buffer with two ranks, the
+    # rows this rank owns otherwise); the switch protocols happen to leave it alone for one more call.
+    x2 = (torch.randn((T, H), generator=torch.Generator().manual_seed(6))).to(torch.bfloat16).to(dev)
+    for name, mlp in (("auto", fused), ("switch, pipelined over token slabs", piped)):
+        y1 = mlp(x)
+        keep = y1.clone()
+        y2 = mlp(x2)
+        torch.cuda.synchronize()
+        assert y2.data_ptr() != y1.data_ptr()
+        if name == "auto":
+            rows = T // world
+            mine = y1 if world == 2 else y1[rank * rows:(rank + 1) * rows]
+            assert float(mine.float().abs().max()) == 0.0, "the add protocols clear the previous result during the next call"
+        else:
+            assert torch.equal(y1, keep), f"fused MLP ({name}): the previous result was disturbed by the next call"
     assert ql.lib().ql_gemm_status(None) == 0
     dist.barrier()
     if rank == 0:

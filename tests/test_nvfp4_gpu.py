@@ -88,3 +88,40 @@ def test_f4_dequantize_with_float_block_scales(out, block):
     assert torch.equal(y, want)
     with pytest.raises(ql.QlError, match="multiple of 16"):
         ql.dequantize(data, torch.ones((33, 24), device="cuda"), ql.float32)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (64, 96, 64), (200, 136, 320), (512, 384, 1024), (1000, 1100, 2080)])
+@pytest.mark.parametrize("out", [torch.float32, torch.bfloat16])
+def test_block_scaled_gemm_matches_dequantize_then_matmul(M, N, K, out):
+    """tcgen05.mma kind::mxf4nvf4 with the block scales in tensor memory against the oracle's dequantize -> f64
+    product of the very same quantized operands (row, column and k tails; K not a multiple of the 256-element k step).
+    The tensor core multiplies exact e2m1 products by the block scales and accumulates in f32, so the result is held
+    to the f32 accumulation bound (and to the result type's rounding step)."""
+    a, b = randn((M, K), torch.float32, 950 + M, std=2.0), randn((N, K), torch.float32, 951 + N, std=0.5)
+    ga, gb = 0.5, 2.0
+    qa, sa = ql.dynamic_quantize(a, ga)
+    qb, sb = ql.dynamic_quantize(b, gb)
+    y = ql.gemm_nvfp4(qa, sa, qb, sb, ga, gb, out_dtype=ql.dtypes.from_torch(out))
+    assert ql.lib().ql_gemm_status(None) == 0
+    want = orc.gemm_nvfp4(qa.packed.cpu().numpy().reshape(M, K // 2), to_np(sa), ga, qb.packed.cpu().numpy().reshape(N, K // 2), to_np(sb), gb)
+    got = y.double().cpu().numpy()
+    scale = np.sqrt(np.mean(want * want))
+    tol = 2e-5 if out == torch.float32 else 2.0 ** -8
+    assert np.all(np.abs(got - want) <= tol * np.maximum(np.abs(want), scale)), float(np.abs(got - want).max() / scale)
+    # and it agrees with the library's own dequantize -> general product route within the benchmark's bound
+    ref = ql.linear(ql.dequantize_nvfp4(qa, sa, ga, ql.float32), ql.dequantize_nvfp4(qb, sb, gb, ql.float32))
+    assert float((y.float() - ref).abs().max() / ref.abs().max()) < 1e-2
+
+
+def test_block_scaled_gemm_argument_rules():
+    qa, sa = ql.dynamic_quantize(torch.ones((4, 48), device="cuda"))
+    qb, sb = ql.dynamic_quantize(torch.ones((8, 48), device="cuda"))
+    with pytest.raises(ql.QlError, match="multiple of 32"):
+        ql.gemm_nvfp4(qa, sa, qb, sb)
+    qc, sc = ql.dynamic_quantize(torch.ones((8, 64), device="cuda"))
+    qd, sd = ql.dynamic_quantize(torch.ones((4, 64), device="cuda"))
+    with pytest.raises(ql.QlError, match="one entry per block of 16"):
+        ql.gemm_nvfp4(qd, sc, qc, sc)
+    with pytest.raises(ql.QlError, match="inner dimensions differ"):
+        ql.gemm_nvfp4(qa, sa, qc, sc)
+    assert tuple(ql.gemm_nvfp4(qd, sd, qc, sc, out_dtype=ql.float32).shape) == (4, 8)

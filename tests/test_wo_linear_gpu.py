@@ -147,3 +147,85 @@ def test_linear_module_mirrors_tripy_linear():
     # weights above 127 saturate, exactly as quantize -> dequantize -> matmul does
     want = x.float() @ wt.float().clamp(-128, 127).cuda().T
     assert torch.allclose(out.float(), want, rtol=1e-3)
+
+
+def _w8_layer(N, K, seed):
+    w = randn((N, K), torch.float16, seed, std=0.02)
+    s = ql.amax_scale(w, ql.int8, dim=0)
+    return ql.quantize(w, s, ql.int8, 0), s
+
+
+def test_w8a16_scratch_is_per_call_graph_replay_after_a_larger_layer():
+    """The compute-bound route (more than 256 rows) widens the weights into scratch taken per call from the
+    stream-ordered allocator.  A graph captured for a small layer must still be right after a larger layer has run
+    (nothing it refers to may have been freed or moved), and again after the large layer's own graph."""
+    q1, s1 = _w8_layer(512, 256, 1301)
+    q2, s2 = _w8_layer(4096, 2048, 1302)
+    x1, x2 = randn((320, 256), torch.bfloat16, 1303), randn((1024, 2048), torch.bfloat16, 1304)
+    want1, want2 = ql.linear_w8a16(x1, q1, s1).clone(), ql.linear_w8a16(x2, q2, s2).clone()
+    y1 = torch.empty_like(want1)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        ql.linear_w8a16(x1, q1, s1, out=y1)   # warm-up on the capture stream
+    torch.cuda.current_stream().wait_stream(side)
+    g1 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g1):
+        ql.linear_w8a16(x1, q1, s1, out=y1)
+    y1.zero_()
+    g1.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(y1, want1)
+    for _ in range(2):
+        assert torch.equal(ql.linear_w8a16(x2, q2, s2), want2)   # the larger layer, eagerly
+        y1.zero_()
+        g1.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y1, want1)
+    assert ql.lib().ql_gemm_status(None) == 0
+
+
+def test_w8a16_calls_on_two_streams_do_not_share_scratch():
+    q1, s1 = _w8_layer(2048, 1024, 1311)
+    q2, s2 = _w8_layer(1024, 2048, 1312)
+    x1, x2 = randn((768, 1024), torch.bfloat16, 1313), randn((640, 2048), torch.float16, 1314)
+    want1, want2 = ql.linear_w8a16(x1, q1, s1).clone(), ql.linear_w8a16(x2, q2, s2).clone()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Stream(), torch.cuda.Stream()
+    outs = []
+    for i in range(6):
+        with torch.cuda.stream(a):
+            ya = ql.linear_w8a16(x1, q1, s1)
+        with torch.cuda.stream(b):
+            yb = ql.linear_w8a16(x2, q2, s2)
+        outs.append((ya, yb))
+    torch.cuda.synchronize()
+    for ya, yb in outs:
+        assert torch.equal(ya, want1) and torch.equal(yb, want2)
+    assert ql.lib().ql_gemm_status(None) == 0
+
+
+def test_weights_constant_flag_gives_the_same_result():
+    """QL_WEIGHTS_CONSTANT only changes when the kernel may start; back-to-back launches that overlap must each still
+    see their own, complete activations."""
+    q, s = _w8_layer(4096, 1024, 1321)
+    w4 = randn((4096, 1024), torch.float16, 1322, std=0.02)
+    s4 = ql.amax_scale(w4, ql.int4, block=(1, 128))
+    q4 = ql.quantize(w4, s4, ql.int4)
+    torch.cuda.synchronize()
+    for m in (1, 8, 24):
+        xs = [randn((m, 1024), torch.float16, 1330 + i) for i in range(4)]
+        plain = [ql.linear_w8a16(x, q, s) for x in xs]
+        plain4 = [ql.linear_w4a16(x, q4, s4) for x in xs]
+        torch.cuda.synchronize()
+        # a chain: each launch's input is rewritten by a kernel right before it
+        buf = torch.empty_like(xs[0])
+        got, got4 = [], []
+        for x in xs:
+            buf.copy_(x)
+            got.append(ql.linear_w8a16(buf, q, s, weights_constant=True).clone())
+            buf.copy_(x)
+            got4.append(ql.linear_w4a16(buf, q4, s4, weights_constant=True).clone())
+        torch.cuda.synchronize()
+        for a_, b_ in zip(plain + plain4, got + got4):
+            assert torch.equal(a_, b_)
