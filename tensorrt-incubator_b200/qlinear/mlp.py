@@ -95,10 +95,9 @@ class QuantizedMLP:
         "auto" = over peer memory when the box supports it and the group has several ranks; "scatter" / "switch" /
         "pipeline" = a given protocol whatever the group size (see _buffers).
 
-        The result is an internal buffer, valid until the next call.  With a peer protocol it is this rank's
-        replica of one of two buffers used in turn: the add protocols clear it during the next call (it is the
-        buffer the call after next adds into); the switch protocols overwrite it one call later.  The NCCL path
-        returns a buffer that the next call overwrites.  Copy the result if it must live longer."""
+        The result is an internal buffer (with a peer protocol this rank's replica of one of a few buffers used in
+        turn; otherwise one of two local buffers): it stays intact during the next call and is cleared or
+        overwritten by the call after that.  Copy it if it must live longer."""
         self.eps, self.group = eps, group
         self._force = fused_all_reduce if fused_all_reduce in ("scatter", "switch", "pipeline") else None   # a protocol on any group size
         self.slabs = 4        # token slabs of the pipelined protocol
@@ -131,7 +130,10 @@ class QuantizedMLP:
                          "act": torch.empty((T, I), dtype=od, device=device) if self.fused_swiglu else None,
                          "amax": torch.empty((T,), dtype=torch.float32, device=device) if self.fused_swiglu else None,
                          "aq": torch.empty((T, I), dtype=torch.float8_e4m3fn, device=device), "sa": torch.empty((T,), dtype=torch.float32, device=device),
-                         "y": torch.empty((T, H), dtype=od, device=device)}
+                         # two results used in turn (like the peer protocols' buffers): a caller may still be reading the
+                         # previous result, e.g. copying it to the host, while the next call runs
+                         "y2": [torch.empty((T, H), dtype=od, device=device) for _ in range(2)]}
+            self._buf["y"] = self._buf["y2"][0]
             world = 1
             if self.fused_all_reduce:
                 import torch.distributed as dist
@@ -170,7 +172,11 @@ class QuantizedMLP:
             if self._buf["protocol"] != "nccl":
                 # two output buffers, used in turn: while the ranks add into one, the other is cleared for
                 # the next call, and a barrier separates "all added" from "anyone reads"
-                self._buf["y_peer"] = [peer.PeerTensor((T, H), od, self.group) for _ in range(2)]
+                # The add protocols clear the buffer of the call after next while they run, so they rotate over three
+                # buffers and the one holding the previous result is left alone; the switch protocols need no
+                # clearing and rotate over two.  Either way a result stays intact during the next call.
+                n_out = 3 if self._buf["protocol"] in ("add_all", "add_owner") else 2
+                self._buf["y_peer"] = [peer.PeerTensor((T, H), od, self.group) for _ in range(n_out)]
         return self._buf
 
     def protocol(self, T, device) -> str:
@@ -206,12 +212,16 @@ class QuantizedMLP:
         """True when rows have owners (reduce-scatter + broadcast); False when every rank adds into every output."""
         return b["protocol"] == "add_owner"
 
+    def _out(self, b):
+        """The output buffer of the current call."""
+        return b["y_peer"][self._step % len(b["y_peer"])]
+
     def stage_down_add(self, b):
         mode = peer.ADD_OWNER if self._scatter(b) else peer.ADD_ALL
-        peer.gemm_fp8_peer(b["aq"], self.wq_d, b["sa"], self.s_d, b["y_peer"][self._step % 2], mode)
+        peer.gemm_fp8_peer(b["aq"], self.wq_d, b["sa"], self.s_d, self._out(b), mode)
 
     def stage_clear_next(self, b):
-        nxt = b["y_peer"][(self._step + 1) % 2]
+        nxt = b["y_peer"][(self._step + 1) % len(b["y_peer"])]
         if self._scatter(b):   # only the rows this rank owns are added into; the rest is overwritten by broadcasts
             rows = b["T"] // nxt.world
             nxt.local[nxt.rank * rows:(nxt.rank + 1) * rows].zero_()
@@ -219,19 +229,19 @@ class QuantizedMLP:
             nxt.local.zero_()
 
     def stage_barrier(self, b):
-        b["y_peer"][self._step % 2].barrier()
+        self._out(b).barrier()
 
     def stage_broadcast_owned(self, b):
-        y = b["y_peer"][self._step % 2]
+        y = self._out(b)
         rows = b["T"] // y.world
         y.broadcast_rows(y.rank * rows, rows)
 
     # the switch protocol: plain GEMM into the local replica, then the in-switch sum of the owned rows
     def stage_down_local(self, b):
-        gemm_fp8(b["aq"], self.wq_d, b["sa"], self.s_d, out_dtype=self.out_dtype, out=b["y_peer"][self._step % 2].local)
+        gemm_fp8(b["aq"], self.wq_d, b["sa"], self.s_d, out_dtype=self.out_dtype, out=self._out(b).local)
 
     def stage_switch_reduce_owned(self, b):
-        y = b["y_peer"][self._step % 2]
+        y = self._out(b)
         rows = b["T"] // y.world
         y.reduce_rows(y.rank * rows, rows)
 
@@ -239,12 +249,12 @@ class QuantizedMLP:
     def stage_down_slab(self, b, s):
         rows = b["T"] // b["slabs"]
         sl = slice(s * rows, (s + 1) * rows)
-        gemm_fp8(b["aq"][sl], self.wq_d, b["sa"][sl], self.s_d, out_dtype=self.out_dtype, out=b["y_peer"][self._step % 2].local[sl])
+        gemm_fp8(b["aq"][sl], self.wq_d, b["sa"][sl], self.s_d, out_dtype=self.out_dtype, out=self._out(b).local[sl])
 
     def stage_reduce_slab(self, b, s):
         """Barrier (every rank's partial results of slab `s` are in its replica), then the in-switch sum of the
         rows of the slab this rank owns, written to every replica.  Runs on the current stream."""
-        y = b["y_peer"][self._step % 2]
+        y = self._out(b)
         rows = b["T"] // b["slabs"]
         mine = rows // y.world
         y.barrier()
@@ -265,12 +275,12 @@ class QuantizedMLP:
                 self.stage_reduce_slab(b, s)
         main.wait_stream(comm)
         self.stage_barrier(b)               # every rank's rows of every slab have been written everywhere
-        y = b["y_peer"][self._step % 2].local
+        y = self._out(b).local
         self._step += 1
         return y
 
     def reset_peer_buffers(self):
-        """Zero both output buffers on every rank (after anything that added into them out of turn)."""
+        """Zero every output buffer on every rank (after anything that added into them out of turn)."""
         for t in self._buf.get("y_peer", []):
             t.barrier()
             t.local.zero_()
@@ -288,7 +298,7 @@ class QuantizedMLP:
             self.stage_barrier(b)           # every rank's partial result is in its own replica
             self.stage_switch_reduce_owned(b)
             self.stage_barrier(b)           # every rank's rows have been summed and written everywhere
-            y = b["y_peer"][self._step % 2].local
+            y = self._out(b).local
             self._step += 1
             return y
         if b["protocol"] != "nccl":
@@ -298,9 +308,11 @@ class QuantizedMLP:
             if self._scatter(b):
                 self.stage_broadcast_owned(b)
                 self.stage_barrier(b)       # every rank's rows have landed
-            y = b["y_peer"][self._step % 2].local
+            y = self._out(b).local
             self._step += 1
             return y
+        b["y"] = b["y2"][self._step % 2]
+        self._step += 1
         self.stage_down(b)
         self.stage_all_reduce(b)
         return b["y"]
