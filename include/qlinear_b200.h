@@ -50,7 +50,9 @@ typedef enum {
   QL_FP8_DIRECT = 0,
   QL_FP8_VIA_F16 = 1,   /* f32 -> f16 -> e4m3, as kernel/lib/Kernel/Transforms/NormalizeQuantizedConversions.cpp:43-80 lowers it */
   QL_FP8_STABLEHLO = 2  /* divide, round to integer, clamp, convert in the input type
-                           (compiler/lib/Dialect/StablehloExt/Transforms/StablehloRaiseQDQ.cpp:233-265) */
+                           (compiler/lib/Dialect/StablehloExt/Transforms/StablehloRaiseQDQ.cpp:233-265).  The one
+                           mode that also changes int8 and int4 results: for f16 / bf16 input the quotient is rounded
+                           to that type before the round to integer, where the operator itself divides in f32. */
 } ql_fp8_mode;
 
 typedef struct {

@@ -192,8 +192,10 @@ static inline int64_t scale_index(int mode, int64_t i, int64_t C, int64_t inner,
 }
 
 /* integer quantize core: clamp(round_half_even(x / (f32)scale), lo, hi); NaN -> 0 */
-static inline int quant_int(float x, float s, float lo, float hi) {
+static inline int quant_int(float x, float s, float lo, float hi, int x_dtype, int fp8_mode) {
   float q = x / s;
+  /* the StableHLO pattern divides in the input's element type */
+  if (fp8_mode == ORC_FP8_STABLEHLO) q = round_to(q, x_dtype);
   if (q != q) return 0;
   float r = nearbyintf(q); /* FE_TONEAREST: ties to even */
   if (r < lo) r = lo;
@@ -210,9 +212,9 @@ int orc_quantize(const void *x, int x_dtype, const void *scale, int s_dtype, voi
     float xv = load_as_f32(x, x_dtype, i);
     float sv = load_as_f32(scale, s_dtype, scale_index(mode, i, C, inner, block_dim, block));
     if (q_dtype == ORC_I8) {
-      ((int8_t *)q)[i] = (int8_t)quant_int(xv, sv, -128.0f, 127.0f);
+      ((int8_t *)q)[i] = (int8_t)quant_int(xv, sv, -128.0f, 127.0f, x_dtype, fp8_mode);
     } else if (q_dtype == ORC_I4) {
-      store_i4((uint8_t *)q, i, quant_int(xv, sv, -8.0f, 7.0f));
+      store_i4((uint8_t *)q, i, quant_int(xv, sv, -8.0f, 7.0f, x_dtype, fp8_mode));
     } else if (q_dtype == ORC_F8E4M3) {
       float quo = xv / sv;
       uint8_t b;

@@ -158,6 +158,14 @@ __device__ __forceinline__ float round_through(float v) {
   return FloatIO<InT>::to_f32(FloatIO<InT>::from_f32(v));
 }
 
+// The quotient an integer quantize rounds: the f32 quotient as the operator specifies it, or, under the StableHLO
+// pattern's arithmetic (divide, round, clamp and convert all in the input's element type), that quotient rounded to
+// the input type first.  An f32 quotient rounded again to f16/bf16 is the correctly rounded 16-bit quotient.
+template <typename InT>
+__device__ __forceinline__ float int_quotient(float q, int fp8_mode) {
+  return fp8_mode == QL_FP8_STABLEHLO ? round_through<InT>(q) : q;
+}
+
 // fp8 quantize of a pair of quotients under the selected semantics
 template <typename InT>
 __device__ __forceinline__ uint32_t quant_f8_pair(float q0, float q1, int fp8_mode) {

@@ -154,6 +154,22 @@ def test_fp8_modes_differ_where_documented(orc):
     assert _f8_decode(orc, orc.quantize(y, 0, s, 0, CODE["f8"], 0, fp8_mode=1)).tolist() == [1.0]
 
 
+def test_integer_quantize_in_the_input_type_against_numpy_half_arithmetic(orc):
+    """The StableHLO pattern (divide, round_nearest_even, clamp, convert, all on f16 tensors:
+    compiler/test/Dialect/StablehloExt/raise-qdq-per-tensor-quantize.mlir) restated with numpy's float16 operators,
+    which round every result to f16; the operator's own f32 division differs from it on a few inputs."""
+    x = np.arange(0, 1 << 16, dtype=np.uint16).view(np.float16)
+    x = x[np.isfinite(x) & (np.abs(x.astype(np.float32)) < 200.0)]
+    differ = 0
+    for scale in (1.0009765625, 0.3, 1.75):
+        s = np.array(scale, dtype=np.float16)
+        want = np.clip(np.rint(x / s), np.float16(-128), np.float16(127)).astype(np.int8)
+        got = orc.quantize(x, CODE["f16"], s, CODE["f16"], CODE["i8"], 0, fp8_mode=2)
+        assert np.array_equal(got, want)
+        differ += int((orc.quantize(x, CODE["f16"], s, CODE["f16"], CODE["i8"], 0) != want).sum())
+    assert differ > 0
+
+
 def test_nvfp4_dynamic_quantize_known_answer(orc, kat):
     """The reference's only NVFP4 execution test: quantize to e2m1 with e4m3 block-16 scales, dequantize back."""
     case = kat["nvfp4_dynamic_quantize"]

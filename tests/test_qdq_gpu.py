@@ -90,6 +90,25 @@ def test_fp8_modes(mode, in_dtype):
     _check_q(x, s, orc.F8E4M3, orc.PER_TENSOR, fp8_mode=mode)
 
 
+@pytest.mark.parametrize("in_dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("qcode", [orc.I8, orc.I4])
+def test_integer_quantize_in_the_input_type(in_dtype, qcode):
+    """The StableHLO pattern divides in the input's element type: the quotient is rounded to f16 / bf16 before the
+    round to integer, which moves values that sit just off a half.  All 16-bit patterns of a range, three scales,
+    per-tensor (vector path) and per-channel on a ragged shape (scalar path)."""
+    bits = torch.arange(0, 1 << 16, dtype=torch.int32).to(torch.int16).view(in_dtype)
+    x = bits[torch.isfinite(bits.float()) & (bits.float().abs() < 200.0)].cuda()
+    differ = 0
+    for scale in (1.0009765625, 0.3, 1.75):
+        s = torch.tensor(scale).to(in_dtype)
+        q = _check_q(x, s, qcode, orc.PER_TENSOR, fp8_mode="stablehlo")
+        differ += int((to_np(q) != to_np(ql.quantize(x, s, QL_OF_CODE[qcode]))).sum())
+    assert differ > 0   # the two arithmetics are not the same function
+    xr = x[: 37 * 129].reshape(37, 129).contiguous()
+    sc = (torch.rand(129, generator=torch.Generator().manual_seed(3)) + 0.25).to(in_dtype).cuda()
+    _check_q(xr, sc, qcode, orc.PER_CHANNEL, 1, fp8_mode="stablehlo")
+
+
 def test_fp8_every_tie_and_boundary():
     """All e4m3 rounding boundaries and their f32 neighbours, both signs, scale 1."""
     exps = np.arange(-12, 11)
