@@ -10,6 +10,16 @@
 //
 // Warps: 0 TMA producer (W), 1 TMEM owner + MMA issuer, 2-5 epilogue, 6-13 converters, 14 TMA producer (X).
 // All waits bounded.
+//
+// One row tile (M <= 128) is not bound by the tensor cores but by shared-memory bandwidth: per weight one raw byte
+// is written and read and two widened bytes are written and read, and every CTA also stages all of X for its part
+// of K (written by TMA, read by the MMA).  With one CTA per column tile and the whole of K the X traffic is as large
+// as the weights' (2 MiB against 2 MiB per SM at 128 x 11008 x 4096).  The KS > 1 instantiations give a column tile
+// KS times as wide to a cluster of KS CTAs that split K between them (each stages 1/KS of X) and add the KS partial
+// accumulators through distributed shared memory: CTA r of the cluster owns columns [r BN/KS, (r+1) BN/KS) of the
+// tile, gathers every CTA's partial sums for them in the (by then idle) pipeline buffers, adds them in rank order,
+// scales and stores.  Measured at that shape: 31 us against 36 (the main loop 44 000 cycles against 59 000, which is
+// the ratio of the shared-memory bytes, 3.0 MB against 4.0 MB per SM).
 #include <cuda/std/type_traits>
 #include <cstdlib>
 
@@ -19,22 +29,28 @@
 namespace ql {
 namespace {
 
-constexpr int kConvWarps = 8;
-constexpr int kConvThreads = kConvWarps * 32;
-constexpr int kW8Threads = (6 + kConvWarps + 1) * 32; // TMA(W), MMA, 4 epilogue, converters, TMA(X)
-constexpr int kWarpXProducer = 6 + kConvWarps;
+// Warp roles: TMA(W), MMA, 4 epilogue, converters, TMA(X).  The K-split kernels run twice the converter warps: one
+// row tile leaves the tensor cores nearly idle and the widening, a chain of dependent integer operations per weight,
+// is what bounds the main loop, so it needs the extra warps to overlap its latencies.
+template <int KS> struct W8Warps {
+  static constexpr int kConv = (KS > 1) ? 16 : 8;
+  static constexpr int kConvThreads = kConv * 32;
+  static constexpr int kThreads = (6 + kConv + 1) * 32;
+  static constexpr int kXProducer = 6 + kConv;
+};
 constexpr int BKE = 64; // k elements per stage: 128 bytes of X, 64 bytes of int8 W
 
 // Three rings, so that each resource is held only as long as it is needed: the small raw int8 tiles
 // sit in a deep ring (their HBM latency is the one to hide), X tiles in a 4-deep ring released by the
 // MMA, and the widened tiles in a 2- or 3-deep ring between the converters and the MMA.
-template <int BN> struct W8Smem {
+template <int BN, int KS> struct W8Smem {
   static constexpr int kA = BM * BK_BYTES;
   static constexpr int kConv = BN * BK_BYTES;
   static constexpr int kRaw = BN * BKE;
-  static constexpr int NA = (BN <= 128) ? 6 : 4;
+  static constexpr int kBudget = (KS > 1 ? 216 : 200) * 1024;
+  static constexpr int NA = (KS > 1) ? 3 : (BN <= 128) ? 6 : 4;
   static constexpr int NC = (BN >= 256) ? 2 : 3;
-  static constexpr int kRawFit = (200 * 1024 - NA * kA - NC * kConv) / kRaw;
+  static constexpr int kRawFit = (kBudget - NA * kA - NC * kConv) / kRaw;
   static constexpr int NR = kRawFit > 16 ? 16 : kRawFit;
   static constexpr int kOffA = 0;
   static constexpr int kOffConv = NA * kA;
@@ -43,9 +59,16 @@ template <int BN> struct W8Smem {
   static constexpr int kNumBarriers = 2 * NR + 2 * NA + 2 * NC + 5;
   static constexpr int kTmemPtr = kBarriers + kNumBarriers * 8;
   static constexpr int kAbort = kTmemPtr + 4;
-  static constexpr int kTotal = kAbort + 4;
+  static constexpr int kScales = (kAbort + 4 + 15) & ~15; // f32 scales of the columns this CTA stores (K split only), 16-byte aligned
+  static constexpr int kTotal = kScales + ((KS > 1) ? (BN / KS) * 4 : 0);
   static constexpr int kDynamic = kTotal + 1024;
+  // K split: columns owned by one CTA of the cluster, and the partial sums it gathers for them (one slot per CTA of
+  // the cluster, its own included: [128 rows][kOwn f32], rows padded by 16 bytes against bank conflicts)
+  static constexpr int kOwn = BN / KS;
+  static constexpr int kSlotRow = kOwn * 4 + 16;
+  static constexpr int kSlot = BM * kSlotRow;
   static_assert(NR >= 2, "raw ring too shallow");
+  static_assert(KS == 1 || (kOwn % 16 == 0 && KS * kSlot <= kBarriers && kScales % 16 == 0), "partial sums must fit the idle rings");
 };
 
 struct W8Args {
@@ -83,12 +106,28 @@ __device__ __forceinline__ uint32_t widen_pair(uint32_t w) {
   }
 }
 
-// Every CTA walks the k-blocks in the same cyclic order but starts at a different one, so that the CTAs
+// Every CTA walks its k-blocks in the same cyclic order but starts at a different one, so that the CTAs
 // which share an X tile (all of them, when M fits one row tile) do not ask L2 for the same lines at the
 // same moment.  The sum over k does not depend on the order beyond f32 rounding.
-__device__ __forceinline__ int rotated_kb(int kb, int num_kb) {
-  const int v = kb + (int)((blockIdx.x * 7u) % (unsigned)num_kb);
+__device__ __forceinline__ int rotated_kb(int kb, int num_kb, int who) {
+  const int v = kb + (int)(((unsigned)who * 7u) % (unsigned)num_kb);
   return v >= num_kb ? v - num_kb : v;
+}
+
+__device__ __forceinline__ uint32_t w8_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void w8_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// 16 bytes into the shared memory of CTA `rank` of the cluster, at the address `local` has in this CTA
+__device__ __forceinline__ void w8_store_remote(uint32_t local, uint32_t rank, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(r), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
 struct Ring {
@@ -99,13 +138,19 @@ struct Ring {
   }
 };
 
-template <typename XT, int BN>
-__global__ void __launch_bounds__(kW8Threads, 1)
+template <typename XT, int BN, int KS>
+__global__ void __launch_bounds__(W8Warps<KS>::kThreads, 1)
 gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const W8Args args) {
-  using L = W8Smem<BN>;
+  using L = W8Smem<BN, KS>;
   constexpr int NR = L::NR, NA = L::NA, NC = L::NC;
+  constexpr int kConvWarps = W8Warps<KS>::kConv, kConvThreads = W8Warps<KS>::kConvThreads, kWarpXProducer = W8Warps<KS>::kXProducer;
   constexpr int KIND = cuda::std::is_same<XT, __half>::value ? KIND_F16 : KIND_BF16;
-  constexpr uint32_t kTmemCols = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
+  // a column tile wider than one MMA's N (256) is two MMAs per k-step over the halves of the widened tile
+  constexpr int NMMA = BN > 256 ? 2 : 1;
+  constexpr int BNM = BN / NMMA;
+  constexpr int kAccCols = (KS > 1) ? BN : 2 * BN; // the K-split CTAs compute one tile each: a single accumulator
+  constexpr uint32_t kTmemCols = (kAccCols <= 32) ? 32 : (kAccCols <= 64) ? 64 : (kAccCols <= 128) ? 128 : (kAccCols <= 256) ? 256 : 512;
+  static_assert(BNM % 16 == 0 && BNM <= 256 && kAccCols <= 512, "tile shape");
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_u32(smem);
@@ -124,6 +169,12 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_tiles = args.tiles_m * args.tiles_n;
+  // K split: the cluster's CTAs share one tile and take consecutive ranges of the k-blocks; otherwise every CTA
+  // walks the tiles with stride gridDim.x over the whole of K
+  const int krank = (KS > 1) ? (int)w8_cluster_rank() : 0;
+  const int tile_begin = (KS > 1) ? (int)blockIdx.x / KS : (int)blockIdx.x;
+  const int tile_step = (KS > 1) ? num_tiles : (int)gridDim.x;
+  const int nkb = args.num_kb / KS, kb_first = krank * nkb;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NR; s++) {
@@ -160,13 +211,16 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     if (lane == 0) {
       Ring r;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = tile_begin; tile < num_tiles && ok; tile += tile_step) {
         int mt, nt;
         w8_tile_coords(args, tile, &mt, &nt);
-        for (int kb = 0; kb < args.num_kb; kb++) {
+        for (int kb = 0; kb < nkb; kb++) {
           if (!mbar_wait(raw_empty(r.stage), r.phase ^ 1, abort_flag, args.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           mbar_expect_tx(raw_full(r.stage), L::kRaw);
-          tma_load_2d(smem_base + L::kOffRaw + r.stage * L::kRaw, &map_w, raw_full(r.stage), rotated_kb(kb, args.num_kb) * BKE, nt * BN);
+          const int k0 = (kb_first + rotated_kb(kb, nkb, tile)) * BKE;
+#pragma unroll
+          for (int h = 0; h < NMMA; h++)
+            tma_load_2d(smem_base + L::kOffRaw + r.stage * L::kRaw + h * BNM * BKE, &map_w, raw_full(r.stage), k0, nt * BN + h * BNM);
           r.advance(NR);
         }
       }
@@ -176,13 +230,13 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     if (lane == 0) {
       Ring r;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = tile_begin; tile < num_tiles && ok; tile += tile_step) {
         int mt, nt;
         w8_tile_coords(args, tile, &mt, &nt);
-        for (int kb = 0; kb < args.num_kb; kb++) {
+        for (int kb = 0; kb < nkb; kb++) {
           if (!mbar_wait(a_empty(r.stage), r.phase ^ 1, abort_flag, args.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           mbar_expect_tx(a_full(r.stage), L::kA);
-          tma_load_2d(smem_base + L::kOffA + r.stage * L::kA, &map_x, a_full(r.stage), rotated_kb(kb, args.num_kb) * BKE, mt * BM);
+          tma_load_2d(smem_base + L::kOffA + r.stage * L::kA, &map_x, a_full(r.stage), (kb_first + rotated_kb(kb, nkb, tile)) * BKE, mt * BM);
           r.advance(NA);
         }
       }
@@ -190,24 +244,27 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = make_instr_desc<KIND, BN>();
+      const uint32_t idesc = make_instr_desc<KIND, BNM>();
       Ring ra, rc;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, it++) {
+      for (int tile = tile_begin; tile < num_tiles && ok; tile += tile_step, it++) {
         const int buf = it & 1;
         if (!mbar_wait(tempty_bar(buf), ((it >> 1) & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-        for (int kb = 0; kb < args.num_kb; kb++) {
+        for (int kb = 0; kb < nkb; kb++) {
           if (!mbar_wait(a_full(ra.stage), ra.phase, abort_flag, args.status, ST_TIMEOUT_FULL)) { ok = false; break; }
           if (!mbar_wait(conv_ready(rc.stage), rc.phase, abort_flag, args.status, ST_TIMEOUT_READY)) { ok = false; break; }
           tc_fence_after();
           const uint64_t adesc = make_smem_desc(smem_base + L::kOffA + ra.stage * L::kA);
-          const uint64_t bdesc = make_smem_desc(smem_base + L::kOffConv + rc.stage * L::kConv);
 #pragma unroll
-          for (int k = 0; k < BK_BYTES / 32; k++)
-            tc_mma<KIND>(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int h = 0; h < NMMA; h++) {
+            const uint64_t bdesc = make_smem_desc(smem_base + L::kOffConv + rc.stage * L::kConv + h * BNM * BK_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK_BYTES / 32; k++)
+              tc_mma<KIND>(tmem_d + (uint32_t)(h * BNM), adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
           tc_commit(a_empty(ra.stage));
           tc_commit(conv_empty(rc.stage));
           ra.advance(NA);
@@ -226,8 +283,8 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     const int ctid = threadIdx.x - 6 * 32;
     Ring rr, rc;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      for (int kb = 0; kb < args.num_kb; kb++) {
+    for (int tile = tile_begin; tile < num_tiles && ok; tile += tile_step) {
+      for (int kb = 0; kb < nkb; kb++) {
         if (!mbar_wait(raw_full(rr.stage), rr.phase, abort_flag, args.status, ST_TIMEOUT_FULL)) { ok = false; break; }
         if (!mbar_wait(conv_empty(rc.stage), rc.phase ^ 1, abort_flag, args.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
         const uint8_t *raw = smem + L::kOffRaw + rr.stage * L::kRaw;
@@ -253,14 +310,14 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         rc.advance(NC);
       }
     }
-  } else {
+  } else if constexpr (KS == 1) {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quad = warp & 3;
     XT *Y = static_cast<XT *>(args.Y);
     const bool vec_ok = (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
     int it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, it++) {
+    for (int tile = tile_begin; tile < num_tiles && ok; tile += tile_step, it++) {
       const int buf = it & 1;
       int mt, nt;
       w8_tile_coords(args, tile, &mt, &nt);
@@ -293,6 +350,79 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     }
   }
 
+  if constexpr (KS > 1) {
+    // ------------------------------------------------------------------ the cluster adds its partial sums
+    // Every warp but the three single-thread roles (the epilogue warps and the converters, now idle): five warps for
+    // each quadrant of the accumulator's 128 lanes, sharing the 16-column chunks between them.
+    const bool worker = warp >= 2 && warp != kWarpXProducer;
+    const int quad = warp & 3, share = (warp - 2) >> 2;
+    constexpr int kShares = (4 + kConvWarps) / 4;
+    constexpr int kChunks = L::kOwn / 16;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    float *sc = reinterpret_cast<float *>(smem + L::kScales);
+    int mt, nt;
+    w8_tile_coords(args, tile_begin, &mt, &nt);
+    const int n_own = nt * BN + krank * L::kOwn; // first of the columns this CTA adds up and stores
+    if (worker) {
+      for (int j = threadIdx.x - 64; j < L::kOwn; j += (4 + kConvWarps) * 32) // (the X producer's threads sit past the end)
+        sc[j] = (n_own + j < args.N) ? load_scale(args.scale, args.sdt, n_own + j) : 0.f;
+      mbar_wait(tfull_bar(0), 0, abort_flag, args.status, ST_TIMEOUT_TMEM_FULL);
+    }
+    tc_fence_after();
+    __syncthreads();
+    // every CTA of the cluster has finished its k range (its MMAs are complete: the issuer waited for them), so the
+    // pipeline buffers are idle everywhere and may take the partial sums
+    w8_cluster_sync();
+    if (worker) {
+      // slot `krank` of every owner (this CTA included) receives this CTA's partial sums for the owner's columns
+      int item = 0;
+      for (int o = 0; o < KS; o++) {
+        const uint32_t owner = (uint32_t)((krank + o) % KS);
+#pragma unroll 1
+        for (int c = 0; c < kChunks; c++, item++) {
+          if (item % kShares != share) continue;
+          uint32_t r[16];
+          tmem_load_16(lane_base + owner * L::kOwn + c * 16, r);
+          const uint32_t dst = smem_base + krank * L::kSlot + row * L::kSlotRow + c * 64;
+#pragma unroll
+          for (int q = 0; q < 4; q++) w8_store_remote(dst + q * 16, owner, r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+        }
+      }
+    }
+    w8_cluster_sync(); // release / acquire: the partial sums written into this CTA are visible
+    if (worker) {
+      // one item = eight adjacent columns of one row: added in rank order (whichever CTA does the adding), scaled,
+      // rounded and stored as 16 bytes; consecutive threads take consecutive items, so a row's bytes leave together
+      XT *Y = static_cast<XT *>(args.Y);
+      const bool vec_ok = (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
+      constexpr int kPerRow = L::kOwn / 8;
+      const int wid = (warp < kWarpXProducer ? warp - 2 : warp - 3) * 32 + lane;
+      for (int item = wid; item < BM * kPerRow; item += (4 + kConvWarps) * 32) {
+        const int r = item / kPerRow, g8 = item % kPerRow;
+        const int m = mt * BM + r, n = n_own + g8 * 8;
+        if (m >= args.M || n >= args.N) continue;
+        float v[8];
+#pragma unroll
+        for (int src = 0; src < KS; src++) {
+          const float4 *sp = reinterpret_cast<const float4 *>(smem + src * L::kSlot + r * L::kSlotRow + g8 * 32);
+          const float4 lo = sp[0], hi = sp[1];
+          const float p[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+          for (int j = 0; j < 8; j++) v[j] = (src == 0) ? p[j] : v[j] + p[j];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[j] *= sc[g8 * 8 + j];
+        XT *out = Y + (size_t)m * args.N + n;
+        if (vec_ok && n + 8 <= args.N) {
+          __stcs(reinterpret_cast<uint4 *>(out), make_uint4(pack2<XT>(v[0], v[1]), pack2<XT>(v[2], v[3]), pack2<XT>(v[4], v[5]), pack2<XT>(v[6], v[7])));
+        } else {
+          for (int j = 0; j < 8 && n + j < args.N; j++) out[j] = FloatIO<XT>::from_f32(v[j]);
+        }
+      }
+    }
+  }
+
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -301,24 +431,66 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   }
 }
 
-template <typename XT, int BN>
-int launch_w8_bn(const CUtensorMap &mx, const CUtensorMap &mw, W8Args args, cudaStream_t st) {
-  using L = W8Smem<BN>;
-  auto kern = gemm_w8a16_kernel<XT, BN>;
+template <typename XT, int BN, int KS>
+int configure_w8(int *max_clusters) {
+  using L = W8Smem<BN, KS>;
+  auto kern = gemm_w8a16_kernel<XT, BN, KS>;
   static bool configured[64] = {false};
+  static int clusters[64] = {0};
   int dev = 0;
   QL_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
+  if (dev < 0 || dev >= 64) return set_error(QL_ERR_UNSUPPORTED, "linear_w8a16: device index %d", dev);
+  if (!configured[dev]) {
     QL_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic));
+    if (KS > 1) {
+      // how many clusters of this shape the device can hold at once (GPC sizes decide; it is not sms / KS)
+      cudaLaunchConfig_t cfg = {};
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = KS, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+      cfg.gridDim = dim3(KS * sm_count()), cfg.blockDim = dim3(W8Warps<KS>::kThreads), cfg.dynamicSmemBytes = L::kDynamic;
+      cfg.attrs = attr, cfg.numAttrs = 1;
+      int n = 0;
+      QL_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+      clusters[dev] = n;
+    }
     configured[dev] = true;
   }
+  if (max_clusters) *max_clusters = clusters[dev];
+  return QL_OK;
+}
+
+template <typename XT, int BN, int KS>
+int launch_w8_bn(const CUtensorMap &mx, const CUtensorMap &mw, W8Args args, cudaStream_t st) {
+  using L = W8Smem<BN, KS>;
+  auto kern = gemm_w8a16_kernel<XT, BN, KS>;
+  int rc = configure_w8<XT, BN, KS>(nullptr);
+  if (rc != QL_OK) return rc;
   const int tiles = args.tiles_m * args.tiles_n;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, kW8Threads, L::kDynamic, st>>>(mx, mw, args);
+  if (KS > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = KS, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+    cfg.gridDim = dim3(tiles * KS), cfg.blockDim = dim3(W8Warps<KS>::kThreads), cfg.dynamicSmemBytes = L::kDynamic, cfg.stream = st;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    QL_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, mx, mw, args));
+  } else {
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    kern<<<grid, W8Warps<KS>::kThreads, L::kDynamic, st>>>(mx, mw, args);
+  }
   count_launches(1);
   QL_CUDA_TRY(cudaGetLastError());
   return QL_OK;
 }
+
+// QL_W8_KSPLIT: 1 = never split K over a cluster, 2 = wherever the shape allows; unset = choose
+int read_w8_ksplit() {
+  const char *e = getenv("QL_W8_KSPLIT");
+  return e ? atoi(e) : 0;
+}
+int g_w8_ksplit = read_w8_ksplit();
+int w8_ksplit_setting() { return g_w8_ksplit; }
 
 template <typename XT>
 int launch_w8_t(const void *X, const void *W, const void *scale, int sdt, void *Y, int M, int N, int K, cudaStream_t st) {
@@ -333,6 +505,24 @@ int launch_w8_t(const void *X, const void *W, const void *scale, int sdt, void *
   args.tiles_m = (M + BM - 1) / BM;
   args.status = device_status_word();
   if (!args.status) return set_error(QL_ERR_CUDA, "linear_w8a16: could not allocate the device status word");
+  CUtensorMap mx, mw;
+  int rc;
+  if ((rc = make_map(&mx, KIND, X, M, K, BM)) != QL_OK) return rc;
+  // One row tile: K split over a cluster of two, where every cluster of the grid can be resident at once, the grid
+  // covers most of the device and each CTA still has a pipeline's worth of k-blocks.  (A four-way split over tiles of
+  // 320 or 384 columns has fewer, fatter CTAs: the device holds 33 clusters of four at this size, and what bounds the
+  // kernel, the shared-memory traffic of widening per SM, grows when the weights are spread over fewer SMs.)
+  const int want = w8_ksplit_setting(); // 0 = choose, 1 = never, 2 = whenever the shape allows
+  if (args.tiles_m == 1 && want != 1 && args.num_kb % 2 == 0 && args.num_kb / 2 >= (want == 0 ? 8 : 1)) {
+    int room = 0;
+    if ((rc = configure_w8<XT, 160, 2>(&room)) != QL_OK) return rc;
+    args.tiles_n = (N + 159) / 160;
+    args.group_m = 1;
+    if (args.tiles_n <= room && (want == 2 || args.tiles_n * 2 > sm_count() / 2)) {
+      if ((rc = make_map_bytes(&mw, W, N, K, BKE, 160)) != QL_OK) return rc;
+      return launch_w8_bn<XT, 160, 2>(mx, mw, args, st);
+    }
+  }
   // pick the column-tile width: waves of tiles over the SMs times the bytes a tile pulls per k-block
   const int sms = sm_count();
   int best_bn = 256;
@@ -349,18 +539,15 @@ int launch_w8_t(const void *X, const void *W, const void *scale, int sdt, void *
     args.group_m = (int)(band < 4 ? 4 : band);
     if (args.group_m > args.tiles_m) args.group_m = args.tiles_m;
   }
-  CUtensorMap mx, mw;
-  int rc;
-  if ((rc = make_map(&mx, KIND, X, M, K, BM)) != QL_OK) return rc;
   if ((rc = make_map_bytes(&mw, W, N, K, BKE, best_bn)) != QL_OK) return rc;
   switch (best_bn) {
-  case 256: return launch_w8_bn<XT, 256>(mx, mw, args, st);
-  case 128: return launch_w8_bn<XT, 128>(mx, mw, args, st);
-  case 96: return launch_w8_bn<XT, 96>(mx, mw, args, st);
-  case 80: return launch_w8_bn<XT, 80>(mx, mw, args, st);
-  case 64: return launch_w8_bn<XT, 64>(mx, mw, args, st);
-  case 48: return launch_w8_bn<XT, 48>(mx, mw, args, st);
-  default: return launch_w8_bn<XT, 32>(mx, mw, args, st);
+  case 256: return launch_w8_bn<XT, 256, 1>(mx, mw, args, st);
+  case 128: return launch_w8_bn<XT, 128, 1>(mx, mw, args, st);
+  case 96: return launch_w8_bn<XT, 96, 1>(mx, mw, args, st);
+  case 80: return launch_w8_bn<XT, 80, 1>(mx, mw, args, st);
+  case 64: return launch_w8_bn<XT, 64, 1>(mx, mw, args, st);
+  case 48: return launch_w8_bn<XT, 48, 1>(mx, mw, args, st);
+  default: return launch_w8_bn<XT, 32, 1>(mx, mw, args, st);
   }
 }
 
@@ -383,6 +570,8 @@ __global__ void __launch_bounds__(256) scale_to_f32_kernel(const void *__restric
 constexpr int kWidenCounters = 1024; // tile counters of the single-launch route (ceil(N / 256) + 1 are used)
 
 } // namespace
+
+void w8_reload_tuning() { g_w8_ksplit = read_w8_ksplit(); }
 
 int gemm16_device(int dtype, const void *X, const void *W, const float *sb, int sb_n, void *Y, int M, int N, int K,
                   cudaStream_t st);

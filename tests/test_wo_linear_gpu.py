@@ -60,6 +60,41 @@ def test_w8a16_large_batch_fused_tensor_core_path(xdtype, M, N, K):
     assert_close_rel(float_values(y), want, ulp, f"fused w8a16 {M}x{N}x{K}")
 
 
+@pytest.mark.parametrize("xdtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K", [(128, 11008, 4096), (70, 1000, 2048), (33, 320, 512), (128, 4100, 1024)])
+def test_w8a16_one_row_tile_splits_k_over_a_cluster(xdtype, M, N, K, monkeypatch, ksplit=2):
+    """M <= 128: a cluster of two CTAs shares a column tile, each takes half of K and the partial sums are
+    added through distributed shared memory in rank order.  Every channel against the oracle (ragged last tile
+    included), the status word clean, and the result identical from call to call (the order of the sum is fixed)."""
+    import ctypes
+    x, q, s = _w8_case(M, N, K, xdtype, 760 + M + ksplit)
+    monkeypatch.setenv("QL_W8_KSPLIT", str(ksplit))
+    ql.lib().ql_reload_tuning()
+    try:
+        y = torch.full((M, N), float("nan"), dtype=xdtype, device="cuda")
+        y.copy_(ql.linear_w8a16(x, q, s))
+        again = ql.linear_w8a16(x, q, s)
+    finally:
+        monkeypatch.delenv("QL_W8_KSPLIT")
+        ql.lib().ql_reload_tuning()
+    code = ctypes.c_int32(0)
+    assert ql.lib().ql_gemm_status(ctypes.byref(code)) == 0 and code.value == 0
+    assert torch.equal(y, again)
+    cols = slice(0, N) if N <= 1000 else slice(N - 700, N)
+    want = orc.linear_w8(to_np(x), code_of(x), to_np(q[cols]), to_np(s[cols]), code_of(s), orc.F32, acc64=True)
+    ulp = 2.0 ** -8 if xdtype == torch.bfloat16 else 2.0 ** -10
+    assert_close_rel(float_values(y[:, cols]), want, ulp, f"k split {ksplit}: {M}x{N}x{K}")
+    if N > 1000:   # the other channels against the unsplit kernel, which the oracle covers elsewhere
+        monkeypatch.setenv("QL_W8_KSPLIT", "1")
+        ql.lib().ql_reload_tuning()
+        try:
+            whole = ql.linear_w8a16(x, q, s)
+        finally:
+            monkeypatch.delenv("QL_W8_KSPLIT")
+            ql.lib().ql_reload_tuning()
+        assert_close_rel(float_values(y), float_values(whole).astype(np.float64), 2 * ulp, "split against unsplit")
+
+
 def test_w8a16_small_and_large_batch_paths_agree():
     """The same rows through the streaming kernel (M <= 64) and the tensor-core kernel (M > 64)."""
     x, q, s = _w8_case(192, 512, 1024, torch.bfloat16, 710)
