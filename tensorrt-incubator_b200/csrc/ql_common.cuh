@@ -158,6 +158,36 @@ __device__ __forceinline__ float round_through(float v) {
   return FloatIO<InT>::to_f32(FloatIO<InT>::from_f32(v));
 }
 
+// Division by a divisor that many numerators share, with the result of the IEEE division (round to nearest even)
+// wherever a quantize step can tell the difference.  y = RN(1/s) once; per numerator q0 = RN(v y), then twice
+// r = v - s q (exact in an FMA), q = RN(q + r y).  After the first correction q is within an ulp of v/s, and for
+// such a q and a correctly rounded reciprocal the second correction returns RN(v/s) (Markstein's theorem on
+// FMA-based division), five dependent-free-of-special-cases instructions against about ten for the general
+// division.  Guards: a divisor outside [2^-40, 2^40] (or NaN) and numerators above 2^80, infinite or NaN take the
+// general division; numerators below 2^-90, zeros included, return q0, whose quotient is below 2^-50 in magnitude
+// with the right sign (the residuals could underflow there): every quantized type rounds that to a zero of that
+// sign, as it does the exact quotient.
+struct SharedDivisor {
+  float s, y;
+  bool fast;
+  __device__ __forceinline__ explicit SharedDivisor(float s_) {
+    s = s_;
+    y = __frcp_rn(s_);
+    const float a = fabsf(s_);
+    fast = a >= 0x1p-40f && a <= 0x1p40f;
+  }
+  __device__ __forceinline__ float operator()(float v) const {
+    const float av = fabsf(v);
+    if (!fast || !(av <= 0x1p80f)) return __fdiv_rn(v, s);
+    const float q0 = __fmul_rn(v, y);
+    float r = __fmaf_rn(-s, q0, v);
+    float q = __fmaf_rn(r, y, q0);
+    r = __fmaf_rn(-s, q, v);
+    q = __fmaf_rn(r, y, q);
+    return av < 0x1p-90f ? q0 : q;
+  }
+};
+
 // The quotient an integer quantize rounds: the f32 quotient as the operator specifies it, or, under the StableHLO
 // pattern's arithmetic (divide, round, clamp and convert all in the input's element type), that quotient rounded to
 // the input type first.  An f32 quotient rounded again to f16/bf16 is the correctly rounded 16-bit quotient.

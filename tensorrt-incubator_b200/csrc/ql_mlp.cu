@@ -67,7 +67,8 @@ rmsnorm_quant_fp8_kernel(const XT *__restrict__ X, uint8_t *__restrict__ Q, floa
     S[row] = s;
   }
   __syncthreads();
-  const float rinv = s_rinv, s = s_scale;
+  const float rinv = s_rinv;
+  const SharedDivisor by_s(s_scale);
   // second pass: the row is still in L1/L2; 16 values -> one 16-byte store
   const int n_chunks = H / 16;
   for (int c = threadIdx.x; c < n_chunks; c += kRowThreads) {
@@ -76,10 +77,87 @@ rmsnorm_quant_fp8_kernel(const XT *__restrict__ X, uint8_t *__restrict__ Q, floa
     uint32_t w[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int j = 0; j < 16; j += 2) {
-      const float a = __fdiv_rn(__fmul_rn(v[j], rinv), s), b = __fdiv_rn(__fmul_rn(v[j + 1], rinv), s);
+      const float a = by_s(__fmul_rn(v[j], rinv)), b = by_s(__fmul_rn(v[j + 1], rinv));
       w[j >> 2] |= (f32x2_to_e4m3x2(a, b) & 0xFFFFu) << (8 * (j & 3));
     }
     __stcs(reinterpret_cast<uint4 *>(q) + c, make_uint4(w[0], w[1], w[2], w[3]));
+  }
+}
+
+// The same for rows of at most 16 * P * 256 values, read from HBM once: every thread keeps its P groups of 16 values
+// (two 16-byte words of 16-bit data) in registers between the reduction and the quantize pass, and all of its loads
+// are in flight together.
+template <typename XT, int P>
+__global__ void __launch_bounds__(kRowThreads)
+rmsnorm_quant_fp8_regs_kernel(const XT *__restrict__ X, uint8_t *__restrict__ Q, float *__restrict__ S, int H, float eps) {
+  static_assert(sizeof(XT) == 2, "two 16-byte words per group of 16 values");
+  const int64_t row = blockIdx.x;
+  const uint4 *x = reinterpret_cast<const uint4 *>(X + row * H);
+  uint4 *q = reinterpret_cast<uint4 *>(Q + row * H);
+  const int n_groups = H / 16;
+  uint4 raw[P][2];
+#pragma unroll
+  for (int i = 0; i < P; i++) {
+    const int g = threadIdx.x + i * kRowThreads;
+    if (g < n_groups) {
+      raw[i][0] = __ldcs(x + 2 * g);
+      raw[i][1] = __ldcs(x + 2 * g + 1);
+    } else {
+      raw[i][0] = raw[i][1] = make_uint4(0, 0, 0, 0);
+    }
+  }
+  double ss = 0.0;
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < P; i++) {
+    const XT *e = reinterpret_cast<const XT *>(&raw[i][0]);
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      const float v = FloatIO<XT>::to_f32(e[j]);
+      ss += (double)v * (double)v;
+      amax = fmaxf(amax, fabsf(v));
+    }
+  }
+  __shared__ double part_ss[kRowThreads / 32];
+  __shared__ float part_mx[kRowThreads / 32];
+  __shared__ float s_rinv, s_scale;
+  ss = warp_sum_f64(ss);
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) {
+    part_ss[threadIdx.x >> 5] = ss;
+    part_mx[threadIdx.x >> 5] = amax;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    float m = 0.f;
+    for (int i = 0; i < kRowThreads / 32; i++) {
+      t += part_ss[i];
+      m = fmaxf(m, part_mx[i]);
+    }
+    const float rinv = (float)(1.0 / sqrt(t / (double)H + (double)eps));
+    float s = __fdiv_rn(__fmul_rn(m, rinv), 448.f);
+    if (s == 0.f) s = 1.f;
+    s_rinv = rinv;
+    s_scale = s;
+    S[row] = s;
+  }
+  __syncthreads();
+  const float rinv = s_rinv;
+  const SharedDivisor by_s(s_scale);
+#pragma unroll
+  for (int i = 0; i < P; i++) {
+    const int g = threadIdx.x + i * kRowThreads;
+    if (g >= n_groups) break;
+    const XT *e = reinterpret_cast<const XT *>(&raw[i][0]);
+    uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; j += 2) {
+      const float a = by_s(__fmul_rn(FloatIO<XT>::to_f32(e[j]), rinv));
+      const float b = by_s(__fmul_rn(FloatIO<XT>::to_f32(e[j + 1]), rinv));
+      w[j >> 2] |= (f32x2_to_e4m3x2(a, b) & 0xFFFFu) << (8 * (j & 3));
+    }
+    __stcs(q + g, make_uint4(w[0], w[1], w[2], w[3]));
   }
 }
 
@@ -124,7 +202,7 @@ swiglu_quant_fp8_kernel(const XT *__restrict__ GU, uint8_t *__restrict__ Q, floa
     S[row] = s;
   }
   __syncthreads();
-  const float s = s_scale;
+  const SharedDivisor by_s(s_scale);
   for (int c = threadIdx.x; c < n_chunks; c += kRowThreads) {
     float av[16];
     if constexpr (kCache) {
@@ -143,7 +221,7 @@ swiglu_quant_fp8_kernel(const XT *__restrict__ GU, uint8_t *__restrict__ Q, floa
     uint32_t w[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int j = 0; j < 16; j += 2)
-      w[j >> 2] |= (f32x2_to_e4m3x2(__fdiv_rn(av[j], s), __fdiv_rn(av[j + 1], s)) & 0xFFFFu) << (8 * (j & 3));
+      w[j >> 2] |= (f32x2_to_e4m3x2(by_s(av[j]), by_s(av[j + 1])) & 0xFFFFu) << (8 * (j & 3));
     __stcs(reinterpret_cast<uint4 *>(q) + c, make_uint4(w[0], w[1], w[2], w[3]));
   }
 }
@@ -167,6 +245,45 @@ __global__ void __launch_bounds__(256) quantize_rows_fp8_kernel(const XT *__rest
     for (int j = 0; j < 16; j += 2)
       w[j >> 2] |= (f32x2_to_e4m3x2(__fdiv_rn(v[j], s), __fdiv_rn(v[j + 1], s)) & 0xFFFFu) << (8 * (j & 3));
     __stcs(reinterpret_cast<uint4 *>(Q) + c, make_uint4(w[0], w[1], w[2], w[3]));
+  }
+}
+
+// The same for long rows: a block takes a segment of one row, so the scale is formed once per thread and no index is
+// divided per chunk; each trip issues kQU chunks' loads before converting any of them.
+constexpr int kQU = 4;
+template <typename XT>
+__global__ void __launch_bounds__(256) quantize_rows_fp8_seg_kernel(const XT *__restrict__ A, const float *__restrict__ amax, uint8_t *__restrict__ Q,
+                                                                    float *__restrict__ S, int chunks_per_row, int segs, int per_seg) {
+  static_assert(sizeof(XT) == 2, "two 16-byte words per chunk of 16 values");
+  const int row = blockIdx.x / segs, seg = blockIdx.x - row * segs;
+  float s = __fdiv_rn(__ldg(amax + row), 448.f);
+  if (s == 0.f) s = 1.f;
+  if (seg == 0 && threadIdx.x == 0) S[row] = s;
+  const SharedDivisor by_s(s);
+  const int c_end = min(chunks_per_row, (seg + 1) * per_seg);
+  const uint4 *a = reinterpret_cast<const uint4 *>(A) + (int64_t)row * chunks_per_row * 2;
+  uint4 *q = reinterpret_cast<uint4 *>(Q) + (int64_t)row * chunks_per_row;
+  for (int c0 = seg * per_seg + threadIdx.x; c0 < c_end; c0 += 256 * kQU) {
+    uint4 raw[kQU][2];
+#pragma unroll
+    for (int u = 0; u < kQU; u++) {
+      const int c = c0 + u * 256;
+      if (c < c_end) {
+        raw[u][0] = __ldcs(a + 2 * c);
+        raw[u][1] = __ldcs(a + 2 * c + 1);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kQU; u++) {
+      const int c = c0 + u * 256;
+      if (c >= c_end) break;
+      const XT *e = reinterpret_cast<const XT *>(&raw[u][0]);
+      uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+      for (int j = 0; j < 16; j += 2)
+        w[j >> 2] |= (f32x2_to_e4m3x2(by_s(FloatIO<XT>::to_f32(e[j])), by_s(FloatIO<XT>::to_f32(e[j + 1]))) & 0xFFFFu) << (8 * (j & 3));
+      __stcs(q + c, make_uint4(w[0], w[1], w[2], w[3]));
+    }
   }
 }
 
@@ -220,10 +337,19 @@ int ql_rmsnorm_quant_fp8(const ql_tensor *x, float eps, ql_tensor *q, ql_tensor 
   const int64_t T = x->shape[0], H = x->shape[1];
   if (T == 0) return QL_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  if (x->dtype == QL_BF16)
-    rmsnorm_quant_fp8_kernel<__nv_bfloat16><<<(unsigned)T, kRowThreads, 0, st>>>(static_cast<const __nv_bfloat16 *>(x->data), static_cast<uint8_t *>(q->data), static_cast<float *>(scale->data), (int)H, eps);
-  else
-    rmsnorm_quant_fp8_kernel<__half><<<(unsigned)T, kRowThreads, 0, st>>>(static_cast<const __half *>(x->data), static_cast<uint8_t *>(q->data), static_cast<float *>(scale->data), (int)H, eps);
+  uint8_t *qp = static_cast<uint8_t *>(q->data);
+  float *sp = static_cast<float *>(scale->data);
+  const int groups = (int)(H / 16);
+#define QL_RMS(XT)                                                                                                             \
+  do {                                                                                                                         \
+    const XT *xp = static_cast<const XT *>(x->data);                                                                           \
+    if (groups <= kRowThreads) rmsnorm_quant_fp8_regs_kernel<XT, 1><<<(unsigned)T, kRowThreads, 0, st>>>(xp, qp, sp, (int)H, eps); \
+    else if (groups <= 2 * kRowThreads) rmsnorm_quant_fp8_regs_kernel<XT, 2><<<(unsigned)T, kRowThreads, 0, st>>>(xp, qp, sp, (int)H, eps); \
+    else rmsnorm_quant_fp8_kernel<XT><<<(unsigned)T, kRowThreads, 0, st>>>(xp, qp, sp, (int)H, eps);                            \
+  } while (0)
+  if (x->dtype == QL_BF16) QL_RMS(__nv_bfloat16);
+  else QL_RMS(__half);
+#undef QL_RMS
   count_launches(1);
   QL_CUDA_TRY(cudaGetLastError());
   return QL_OK;
@@ -239,16 +365,27 @@ int ql_quantize_rows_fp8(const ql_tensor *a, const ql_tensor *row_amax, ql_tenso
   const int64_t T = a->shape[0], I = a->shape[1];
   if (T == 0 || I == 0) return QL_OK;
   const int64_t n_chunks = T * (I / 16);
-  int64_t blocks = (n_chunks + 255) / 256;
-  const int64_t cap = (int64_t)sm_count() * 16;
-  if (blocks > cap) blocks = cap;
   cudaStream_t st = (cudaStream_t)stream;
-  if (a->dtype == QL_BF16)
-    quantize_rows_fp8_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(a->data), static_cast<const float *>(row_amax->data),
-                                                                            static_cast<uint8_t *>(q->data), static_cast<float *>(scale->data), n_chunks, (int)(I / 16));
-  else
-    quantize_rows_fp8_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const __half *>(a->data), static_cast<const float *>(row_amax->data),
-                                                                     static_cast<uint8_t *>(q->data), static_cast<float *>(scale->data), n_chunks, (int)(I / 16));
+  const float *am = static_cast<const float *>(row_amax->data);
+  uint8_t *qp = static_cast<uint8_t *>(q->data);
+  float *sp = static_cast<float *>(scale->data);
+  const int cpr = (int)(I / 16);
+  if (cpr >= 256 && T * ((cpr + 1023) / 1024) <= INT32_MAX) {
+    // long rows: one block per row segment of at most 1024 chunks
+    const int segs = (cpr + 1023) / 1024, per_seg = (cpr + segs - 1) / segs;
+    if (a->dtype == QL_BF16)
+      quantize_rows_fp8_seg_kernel<__nv_bfloat16><<<(unsigned)(T * segs), 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(a->data), am, qp, sp, cpr, segs, per_seg);
+    else
+      quantize_rows_fp8_seg_kernel<__half><<<(unsigned)(T * segs), 256, 0, st>>>(static_cast<const __half *>(a->data), am, qp, sp, cpr, segs, per_seg);
+  } else {
+    int64_t blocks = (n_chunks + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    if (a->dtype == QL_BF16)
+      quantize_rows_fp8_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(a->data), am, qp, sp, n_chunks, cpr);
+    else
+      quantize_rows_fp8_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const __half *>(a->data), am, qp, sp, n_chunks, cpr);
+  }
   count_launches(1);
   QL_CUDA_TRY(cudaGetLastError());
   return QL_OK;

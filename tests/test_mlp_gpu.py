@@ -20,7 +20,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("dtype,code", [(torch.bfloat16, orc.BF16), (torch.float16, orc.F16)])
-@pytest.mark.parametrize("T,H", [(7, 256), (64, 8192), (33, 1040)])
+@pytest.mark.parametrize("T,H", [(7, 256), (64, 8192), (33, 1040), (5, 4096), (3, 12288), (4, 8208)])
 def test_rmsnorm_quant_matches_oracle(dtype, code, T, H):
     x = randn((T, H), dtype, 600 + T)
     q, s = ql.rmsnorm_quant_fp8(x, 1e-5)
@@ -84,6 +84,19 @@ def test_gate_up_projection_with_swiglu_epilogue(dtype, code, M, I, K):
     q, s = ql.quantize_rows_fp8(act, amax)
     wq_rows, ws = orc.quantize_rows_fp8(to_np(act), code, amax.cpu().numpy())
     assert np.array_equal(to_np(s), ws) and np.array_equal(to_np(q), wq_rows)
+
+
+@pytest.mark.parametrize("dtype,code", [(torch.bfloat16, orc.BF16), (torch.float16, orc.F16)])
+@pytest.mark.parametrize("T,I", [(5, 4096), (3, 28672), (2, 16400), (6, 4112), (9, 240)])
+def test_row_quantize_matches_oracle(dtype, code, T, I):
+    """Long rows take the kernel that walks one row segment per block (a ragged last segment and a row length that
+    is not a multiple of the block's stride among the cases), short rows the flat one: bit for bit."""
+    act = randn((T, I), dtype, 650 + T, std=1.5)
+    act[1, :] = 0
+    amax = act.float().abs().amax(dim=1)
+    q, s = ql.quantize_rows_fp8(act, amax)
+    wq, ws = orc.quantize_rows_fp8(to_np(act), code, amax.cpu().numpy())
+    assert np.array_equal(to_np(s), ws) and np.array_equal(to_np(q), wq)
 
 
 def test_row_quantize_handles_zero_rows():

@@ -109,6 +109,35 @@ def test_integer_quantize_in_the_input_type(in_dtype, qcode):
     _check_q(xr, sc, qcode, orc.PER_CHANNEL, 1, fp8_mode="stablehlo")
 
 
+@pytest.mark.parametrize("qcode", QUANTS)
+@pytest.mark.parametrize("in_dtype", [torch.float16, torch.bfloat16])
+def test_every_16_bit_input_over_a_range_of_scales(in_dtype, qcode):
+    """The kernels divide by a scale that many values share through its reciprocal and two FMA corrections; the
+    result must be the IEEE quotient's.  Every bit pattern of the input type (signed zeros, subnormals, infinities
+    and NaNs included) against scales from 1e-30 to 1e30 (the ends take the general division), per tensor and, for
+    the chunked kernel, per channel."""
+    x = torch.arange(0, 1 << 16, dtype=torch.int32).to(torch.int16).view(in_dtype).cuda()
+    for scale in (1e-30, 2.0 ** -41, 2.0 ** -40, 1.1e-5, 0.0123, 1.0 / 3.0, 1.0, 1.0009765625, 3.0, 448.0, 1000.7, 2.0 ** 40, 1e30):
+        s = torch.tensor(scale, dtype=torch.float32).to(in_dtype)
+        if not torch.isfinite(s) or float(s) == 0.0:
+            continue
+        _check_q(x, s, qcode, orc.PER_TENSOR)
+    xc = x.reshape(64, 1024).contiguous()
+    sc = torch.logspace(-12, 12, 64, base=2.0).to(in_dtype).cuda()
+    _check_q(xc, sc, qcode, orc.PER_CHANNEL, 0)
+
+
+def test_f32_inputs_of_every_magnitude_divide_exactly():
+    """f32 numerators from the subnormals to the largest finite value, both signs, scales across the guarded range."""
+    g = torch.Generator(device="cpu").manual_seed(77)
+    bits = torch.randint(0, 2 ** 31 - 1, (1 << 20,), generator=g, dtype=torch.int32)
+    bits = bits | (torch.randint(0, 2, (1 << 20,), generator=g, dtype=torch.int32) << 31)
+    x = bits.view(torch.float32).cuda()
+    for scale in (2.0 ** -45, 2.0 ** -39, 7.3e-4, 0.77, 5.0, 2.0 ** 39, 2.0 ** 45):
+        for qcode in QUANTS:
+            _check_q(x, torch.tensor(scale), qcode, orc.PER_TENSOR)
+
+
 def test_fp8_every_tie_and_boundary():
     """All e4m3 rounding boundaries and their f32 neighbours, both signs, scale 1."""
     exps = np.arange(-12, 11)
