@@ -286,6 +286,42 @@ QL_API int32_t ql_rtexe_num_segments(const ql_rtexe *exe);
 QL_API int ql_rtexe_segment(const ql_rtexe *exe, int32_t index, ql_rtexe_segment_info *info);
 QL_API int ql_rtexe_find_segment(const ql_rtexe *exe, const char *name); /* index, or -1 */
 
+/* ---- NCCL communicators and collectives, as the executor runtime's NCCL module offers them to compiled programs
+ * (executor/lib/Runtime/Backend/Lua/Modules/NCCL/NCCLModule.cpp:233-385: __nccl_comm_init_rank, __nccl_comm_split,
+ * __nccl_comm_rank / _num_ranks, __nccl_all_reduce_<op>_<type>, __nccl_reduce_scatter_<op>_<type>,
+ * __nccl_all_gather, __nccl_all_to_all, __nccl_permute).  Same conventions: communicators are non-blocking, and
+ * every call ends by polling ncclCommGetAsyncError until the communicator has left ncclInProgress or `timeout_ms`
+ * (5000 when <= 0, the reference's value; NCCLModule.cpp:88-106) has passed, returning QL_ERR_DEVICE_TIMEOUT then.
+ * NCCL itself is bound at run time (libnccl.so.2); without it these return QL_ERR_UNSUPPORTED and the rest of the
+ * library is unaffected.  Buffers are device pointers; `stream` is a cudaStream_t.  The fused GEMM + collective
+ * entry points above do not go through NCCL. */
+#define QL_NCCL_UNIQUE_ID_BYTES 128
+typedef struct ql_nccl_comm ql_nccl_comm;
+typedef enum { QL_NCCL_SUM = 0, QL_NCCL_PROD = 1, QL_NCCL_MIN = 2, QL_NCCL_MAX = 3, QL_NCCL_AVG = 4 } ql_nccl_op;
+QL_API int ql_nccl_version(int32_t *version);
+/* 128 bytes that rank 0 makes and every rank of the new communicator must be given (the runtime's _get_nccl_unique_id) */
+QL_API int ql_nccl_unique_id(void *id);
+/* makes `device` current, as __nccl_comm_init_rank does */
+QL_API int ql_nccl_comm_init_rank(int32_t rank, int32_t num_ranks, int32_t device, const void *id, int64_t timeout_ms,
+                                  ql_nccl_comm **out);
+/* *out is null for a rank that passes color -1 (no new communicator) */
+QL_API int ql_nccl_comm_split(ql_nccl_comm *parent, int32_t color, int32_t key, ql_nccl_comm **out);
+QL_API int ql_nccl_comm_rank(const ql_nccl_comm *comm, int32_t *rank, int32_t *num_ranks);
+/* finalizes a healthy communicator, aborts one that is in error or still busy after its time limit */
+QL_API int ql_nccl_comm_destroy(ql_nccl_comm *comm);
+/* dtype: QL_F32, QL_F16, QL_BF16 or QL_I8; op: ql_nccl_op */
+QL_API int ql_nccl_all_reduce(ql_nccl_comm *comm, const void *send, void *recv, uint64_t count, int32_t dtype, int32_t op,
+                              void *stream);
+QL_API int ql_nccl_reduce_scatter(ql_nccl_comm *comm, const void *send, void *recv, uint64_t recv_count, int32_t dtype,
+                                  int32_t op, void *stream);
+/* bytes: recv holds num_ranks * send_bytes */
+QL_API int ql_nccl_all_gather(ql_nccl_comm *comm, const void *send, void *recv, uint64_t send_bytes, void *stream);
+/* total_bytes / num_ranks bytes go to, and come from, every rank */
+QL_API int ql_nccl_all_to_all(ql_nccl_comm *comm, const void *send, void *recv, uint64_t total_bytes, void *stream);
+/* send to `send_to` and receive from `recv_from`; -1 = no send / no receive (the receive buffer is then zeroed) */
+QL_API int ql_nccl_permute(ql_nccl_comm *comm, const void *send, void *recv, int32_t send_to, int32_t recv_from,
+                           uint64_t bytes, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -162,11 +162,11 @@ __device__ __forceinline__ float round_through(float v) {
 // wherever a quantize step can tell the difference.  y = RN(1/s) once; per numerator q0 = RN(v y), then twice
 // r = v - s q (exact in an FMA), q = RN(q + r y).  After the first correction q is within an ulp of v/s, and for
 // such a q and a correctly rounded reciprocal the second correction returns RN(v/s) (Markstein's theorem on
-// FMA-based division), five dependent-free-of-special-cases instructions against about ten for the general
-// division.  Guards: a divisor outside [2^-40, 2^40] (or NaN) and numerators above 2^80, infinite or NaN take the
-// general division; numerators below 2^-90, zeros included, return q0, whose quotient is below 2^-50 in magnitude
-// with the right sign (the residuals could underflow there): every quantized type rounds that to a zero of that
-// sign, as it does the exact quotient.
+// FMA-based division): five instructions and a branch-free select against about a dozen, with a call, for the
+// general division.  The corrected value is taken where 2^-50 <= |q0| < inf; elsewhere q0 itself is returned: a
+// signed zero, a quotient below 2^-50 (its residuals could underflow; every quantized type rounds it to a zero of
+// that sign, as it does the exact quotient), an infinity (v infinite or v/s beyond the largest float: saturates
+// either way) or a NaN.  A divisor outside [2^-40, 2^40], or NaN, takes the general division throughout.
 struct SharedDivisor {
   float s, y;
   bool fast;
@@ -176,15 +176,26 @@ struct SharedDivisor {
     const float a = fabsf(s_);
     fast = a >= 0x1p-40f && a <= 0x1p40f;
   }
-  __device__ __forceinline__ float operator()(float v) const {
-    const float av = fabsf(v);
-    if (!fast || !(av <= 0x1p80f)) return __fdiv_rn(v, s);
+  // requires `fast`
+  __device__ __forceinline__ float quick(float v) const {
     const float q0 = __fmul_rn(v, y);
     float r = __fmaf_rn(-s, q0, v);
     float q = __fmaf_rn(r, y, q0);
     r = __fmaf_rn(-s, q, v);
     q = __fmaf_rn(r, y, q);
-    return av < 0x1p-90f ? q0 : q;
+    const float a0 = fabsf(q0);
+    return (a0 >= 0x1p-50f && a0 < __int_as_float(0x7f800000)) ? q : q0;
+  }
+  __device__ __forceinline__ float operator()(float v) const { return fast ? quick(v) : __fdiv_rn(v, s); }
+  // v[j] /= s for a group of values: one uniform branch for the group
+  template <int N> __device__ __forceinline__ void divide(float (&v)[N]) const {
+    if (fast) {
+#pragma unroll
+      for (int j = 0; j < N; j++) v[j] = quick(v[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < N; j++) v[j] = __fdiv_rn(v[j], s);
+    }
   }
 };
 

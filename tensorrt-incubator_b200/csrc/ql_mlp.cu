@@ -76,10 +76,10 @@ rmsnorm_quant_fp8_kernel(const XT *__restrict__ X, uint8_t *__restrict__ Q, floa
     load_vec_f32<XT, 16>(x + c * 16, v);
     uint32_t w[4] = {0, 0, 0, 0};
 #pragma unroll
-    for (int j = 0; j < 16; j += 2) {
-      const float a = by_s(__fmul_rn(v[j], rinv)), b = by_s(__fmul_rn(v[j + 1], rinv));
-      w[j >> 2] |= (f32x2_to_e4m3x2(a, b) & 0xFFFFu) << (8 * (j & 3));
-    }
+    for (int j = 0; j < 16; j++) v[j] = __fmul_rn(v[j], rinv);
+    by_s.divide(v);
+#pragma unroll
+    for (int j = 0; j < 16; j += 2) w[j >> 2] |= (f32x2_to_e4m3x2(v[j], v[j + 1]) & 0xFFFFu) << (8 * (j & 3));
     __stcs(reinterpret_cast<uint4 *>(q) + c, make_uint4(w[0], w[1], w[2], w[3]));
   }
 }
@@ -151,12 +151,12 @@ rmsnorm_quant_fp8_regs_kernel(const XT *__restrict__ X, uint8_t *__restrict__ Q,
     if (g >= n_groups) break;
     const XT *e = reinterpret_cast<const XT *>(&raw[i][0]);
     uint32_t w[4] = {0, 0, 0, 0};
+    float v[16];
 #pragma unroll
-    for (int j = 0; j < 16; j += 2) {
-      const float a = by_s(__fmul_rn(FloatIO<XT>::to_f32(e[j]), rinv));
-      const float b = by_s(__fmul_rn(FloatIO<XT>::to_f32(e[j + 1]), rinv));
-      w[j >> 2] |= (f32x2_to_e4m3x2(a, b) & 0xFFFFu) << (8 * (j & 3));
-    }
+    for (int j = 0; j < 16; j++) v[j] = __fmul_rn(FloatIO<XT>::to_f32(e[j]), rinv);
+    by_s.divide(v);
+#pragma unroll
+    for (int j = 0; j < 16; j += 2) w[j >> 2] |= (f32x2_to_e4m3x2(v[j], v[j + 1]) & 0xFFFFu) << (8 * (j & 3));
     __stcs(q + g, make_uint4(w[0], w[1], w[2], w[3]));
   }
 }
@@ -218,10 +218,11 @@ swiglu_quant_fp8_kernel(const XT *__restrict__ GU, uint8_t *__restrict__ Q, floa
 #pragma unroll
       for (int j = 0; j < 16; j++) av[j] = silu_mul(gv[j], uv[j]);
     }
+    by_s.divide(av);
     uint32_t w[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int j = 0; j < 16; j += 2)
-      w[j >> 2] |= (f32x2_to_e4m3x2(by_s(av[j]), by_s(av[j + 1])) & 0xFFFFu) << (8 * (j & 3));
+      w[j >> 2] |= (f32x2_to_e4m3x2(av[j], av[j + 1]) & 0xFFFFu) << (8 * (j & 3));
     __stcs(reinterpret_cast<uint4 *>(q) + c, make_uint4(w[0], w[1], w[2], w[3]));
   }
 }
@@ -248,22 +249,21 @@ __global__ void __launch_bounds__(256) quantize_rows_fp8_kernel(const XT *__rest
   }
 }
 
-// The same for long rows: a block takes a segment of one row, so the scale is formed once per thread and no index is
-// divided per chunk; each trip issues kQU chunks' loads before converting any of them.
+// The same for long rows.  A work item is a segment of at most 256 * kQU chunks of one row, so the scale is formed once
+// per thread and item and no index is divided per chunk; the blocks stay resident and walk the items with the grid's
+// stride, and in every item a thread issues all of its loads before it reads the row maximum, so that the latency of
+// that dependent load is hidden behind them.
 constexpr int kQU = 4;
 template <typename XT>
 __global__ void __launch_bounds__(256) quantize_rows_fp8_seg_kernel(const XT *__restrict__ A, const float *__restrict__ amax, uint8_t *__restrict__ Q,
-                                                                    float *__restrict__ S, int chunks_per_row, int segs, int per_seg) {
+                                                                    float *__restrict__ S, int chunks_per_row, int segs, int per_seg, int n_items) {
   static_assert(sizeof(XT) == 2, "two 16-byte words per chunk of 16 values");
-  const int row = blockIdx.x / segs, seg = blockIdx.x - row * segs;
-  float s = __fdiv_rn(__ldg(amax + row), 448.f);
-  if (s == 0.f) s = 1.f;
-  if (seg == 0 && threadIdx.x == 0) S[row] = s;
-  const SharedDivisor by_s(s);
-  const int c_end = min(chunks_per_row, (seg + 1) * per_seg);
-  const uint4 *a = reinterpret_cast<const uint4 *>(A) + (int64_t)row * chunks_per_row * 2;
-  uint4 *q = reinterpret_cast<uint4 *>(Q) + (int64_t)row * chunks_per_row;
-  for (int c0 = seg * per_seg + threadIdx.x; c0 < c_end; c0 += 256 * kQU) {
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int row = item / segs, seg = item - row * segs;
+    const int c_end = min(chunks_per_row, (seg + 1) * per_seg); // per_seg <= 256 * kQU: one trip per item
+    const int c0 = seg * per_seg + threadIdx.x;
+    const uint4 *a = reinterpret_cast<const uint4 *>(A) + (int64_t)row * chunks_per_row * 2;
+    uint4 *q = reinterpret_cast<uint4 *>(Q) + (int64_t)row * chunks_per_row;
     uint4 raw[kQU][2];
 #pragma unroll
     for (int u = 0; u < kQU; u++) {
@@ -273,15 +273,22 @@ __global__ void __launch_bounds__(256) quantize_rows_fp8_seg_kernel(const XT *__
         raw[u][1] = __ldcs(a + 2 * c + 1);
       }
     }
+    float s = __fdiv_rn(__ldg(amax + row), 448.f);
+    if (s == 0.f) s = 1.f;
+    if (seg == 0 && threadIdx.x == 0) S[row] = s;
+    const SharedDivisor by_s(s);
 #pragma unroll
     for (int u = 0; u < kQU; u++) {
       const int c = c0 + u * 256;
       if (c >= c_end) break;
       const XT *e = reinterpret_cast<const XT *>(&raw[u][0]);
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; j++) v[j] = FloatIO<XT>::to_f32(e[j]);
+      by_s.divide(v);
       uint32_t w[4] = {0, 0, 0, 0};
 #pragma unroll
-      for (int j = 0; j < 16; j += 2)
-        w[j >> 2] |= (f32x2_to_e4m3x2(by_s(FloatIO<XT>::to_f32(e[j])), by_s(FloatIO<XT>::to_f32(e[j + 1]))) & 0xFFFFu) << (8 * (j & 3));
+      for (int j = 0; j < 16; j += 2) w[j >> 2] |= (f32x2_to_e4m3x2(v[j], v[j + 1]) & 0xFFFFu) << (8 * (j & 3));
       __stcs(q + c, make_uint4(w[0], w[1], w[2], w[3]));
     }
   }
@@ -371,12 +378,14 @@ int ql_quantize_rows_fp8(const ql_tensor *a, const ql_tensor *row_amax, ql_tenso
   float *sp = static_cast<float *>(scale->data);
   const int cpr = (int)(I / 16);
   if (cpr >= 256 && T * ((cpr + 1023) / 1024) <= INT32_MAX) {
-    // long rows: one block per row segment of at most 1024 chunks
+    // long rows: work items of one row segment of at most 1024 chunks, walked by a resident grid
     const int segs = (cpr + 1023) / 1024, per_seg = (cpr + segs - 1) / segs;
+    const int n_items = (int)(T * segs);
+    const int grid = n_items < sm_count() * 4 ? n_items : sm_count() * 4;
     if (a->dtype == QL_BF16)
-      quantize_rows_fp8_seg_kernel<__nv_bfloat16><<<(unsigned)(T * segs), 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(a->data), am, qp, sp, cpr, segs, per_seg);
+      quantize_rows_fp8_seg_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(a->data), am, qp, sp, cpr, segs, per_seg, n_items);
     else
-      quantize_rows_fp8_seg_kernel<__half><<<(unsigned)(T * segs), 256, 0, st>>>(static_cast<const __half *>(a->data), am, qp, sp, cpr, segs, per_seg);
+      quantize_rows_fp8_seg_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half *>(a->data), am, qp, sp, cpr, segs, per_seg, n_items);
   } else {
     int64_t blocks = (n_chunks + 255) / 256;
     const int64_t cap = (int64_t)sm_count() * 16;

@@ -48,8 +48,9 @@ nvfp4_quantize_kernel(const InT *__restrict__ x, const void *__restrict__ gs, in
     uint32_t w[2] = {0u, 0u};
     if (s != 0.f) { // a block whose scale rounds to zero quantizes to zeros
       const SharedDivisor by_s(s);
+      by_s.divide(v);
 #pragma unroll
-      for (int i = 0; i < 16; i += 2) w[i >> 3] |= f32x2_to_e2m1x2(by_s(v[i]), by_s(v[i + 1])) << (4 * (i & 7));
+      for (int i = 0; i < 16; i += 2) w[i >> 3] |= f32x2_to_e2m1x2(v[i], v[i + 1]) << (4 * (i & 7));
     }
     *reinterpret_cast<uint2 *>(q + b * 8) = make_uint2(w[0], w[1]);
     scales[b] = (uint8_t)sq;

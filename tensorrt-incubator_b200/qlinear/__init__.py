@@ -8,4 +8,4 @@ from .ops import (QuantizeError, amax_scale, cast, dequantize, dequantize_nvfp4,
 from .tensor import Float4Tensor, Int4Tensor  # noqa: F401
 from .mlp import (QuantizedMLP, gemm_fp8_swiglu, interleave_gate_up, quantize_per_channel_fp8, quantize_rows_fp8, rmsnorm_quant_fp8,  # noqa: F401
                   shard_range, swiglu_quant_fp8)  # noqa: F401
-from . import peer, stablehlo  # noqa: F401,E402
+from . import nccl, peer, stablehlo  # noqa: F401,E402

@@ -88,6 +88,18 @@ SIGNATURES = {
     "ql_quantize_rows_fp8": ([_T, _T, _T, _T, _S], ctypes.c_int),
     "ql_reload_tuning": ([], ctypes.c_int),
     "ql_gemm_status": ([ctypes.POINTER(ctypes.c_int32)], ctypes.c_int),
+    "ql_nccl_version": ([ctypes.POINTER(ctypes.c_int32)], ctypes.c_int),
+    "ql_nccl_unique_id": ([ctypes.c_void_p], ctypes.c_int),
+    "ql_nccl_comm_init_rank": ([ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64,
+                                ctypes.POINTER(ctypes.c_void_p)], ctypes.c_int),
+    "ql_nccl_comm_split": ([ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(ctypes.c_void_p)], ctypes.c_int),
+    "ql_nccl_comm_rank": ([ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)], ctypes.c_int),
+    "ql_nccl_comm_destroy": ([ctypes.c_void_p], ctypes.c_int),
+    "ql_nccl_all_reduce": ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64, ctypes.c_int32, ctypes.c_int32, _S], ctypes.c_int),
+    "ql_nccl_reduce_scatter": ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64, ctypes.c_int32, ctypes.c_int32, _S], ctypes.c_int),
+    "ql_nccl_all_gather": ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64, _S], ctypes.c_int),
+    "ql_nccl_all_to_all": ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64, _S], ctypes.c_int),
+    "ql_nccl_permute": ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64, _S], ctypes.c_int),
 }
 
 _lib = None

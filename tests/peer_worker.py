@@ -33,11 +33,60 @@ def same_everywhere(t):
     return int(lo) == int(hi)
 
 
+def check_nccl_entry_points(rank, world, dev):
+    """The `ql_nccl_*` collectives of the C ABI between all ranks: the unique id travels over the process group, the
+    results are compared with what each collective is defined to return."""
+    from qlinear import nccl
+    box = [nccl.unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    comm = nccl.Communicator(rank, world, dev.index, box[0])
+    assert (comm.rank, comm.num_ranks) == (rank, world)
+    n = 4096
+    mine = (torch.arange(n, device=dev) % 7 + rank).float()
+    total = sum((torch.arange(n, device=dev) % 7 + r).float() for r in range(world))
+    for dtype in (torch.float32, torch.bfloat16):
+        out = torch.empty(n, dtype=dtype, device=dev)
+        comm.all_reduce(mine.to(dtype), out)
+        torch.cuda.synchronize()
+        assert torch.equal(out.float(), total), f"rank {rank}: all_reduce {dtype}"
+    out = torch.empty(n, device=dev)
+    comm.all_reduce(mine, out, "max")
+    torch.cuda.synchronize()
+    assert torch.equal(out, (torch.arange(n, device=dev) % 7 + world - 1).float())
+    part = torch.empty(n // world, device=dev)
+    comm.reduce_scatter(mine, part)
+    gathered = torch.empty(n * world, dtype=torch.int8, device=dev)
+    comm.all_gather(torch.full((n,), rank, dtype=torch.int8, device=dev), gathered)
+    sent = torch.arange(world, device=dev, dtype=torch.int32).repeat_interleave(16) + 100 * rank   # block p goes to rank p
+    got = torch.empty_like(sent)
+    comm.all_to_all(sent, got)
+    ring = torch.empty(8, dtype=torch.int32, device=dev)
+    comm.permute(torch.full((8,), rank, dtype=torch.int32, device=dev), ring, (rank + 1) % world, (rank - 1) % world)
+    torch.cuda.synchronize()
+    assert torch.equal(part, total[rank * (n // world):(rank + 1) * (n // world)])
+    assert torch.equal(gathered.view(world, n)[:, 0].cpu(), torch.arange(world, dtype=torch.int8))
+    assert torch.equal(got.view(world, 16)[:, 0].cpu(), torch.arange(world, dtype=torch.int32) * 100 + rank)
+    assert int(ring[0]) == (rank - 1) % world
+    half = comm.split(rank % 2, rank)      # even and odd ranks
+    members = len(range(rank % 2, world, 2))
+    assert half.num_ranks == members and half.rank == rank // 2
+    s = torch.ones(4, device=dev)
+    half.all_reduce(s, s)
+    torch.cuda.synchronize()
+    assert float(s[0]) == members
+    half.destroy()
+    comm.destroy()
+    dist.barrier()
+    if rank == 0:
+        print("NCCL ABI OK")
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dev = torch.device("cuda", torch.cuda.current_device())
     dist.init_process_group("nccl", device_id=dev)
+    check_nccl_entry_points(rank, world, dev)
     if not peer.available():
         if rank == 0:
             print("PEER UNAVAILABLE")

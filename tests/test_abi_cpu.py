@@ -140,6 +140,24 @@ def test_peer_entry_points_validate_before_touching_a_device():
     assert "no replication address" in _err(L.ql_peer_reduce(_peer(with_all=False), _lib.BF16, 0, 64, None))
 
 
+def test_nccl_entry_points_validate_their_arguments():
+    """The NCCL module of the C ABI (executor/lib/Runtime/Backend/Lua/Modules/NCCL/NCCLModule.cpp:233-385): argument
+    rules that need neither a GPU nor a communicator."""
+    import ctypes
+    L = _lib.lib()
+    none = ctypes.c_void_p()
+    assert "not a communicator" in _err(L.ql_nccl_all_reduce(None, None, None, 4, _lib.F32, 0, None))
+    assert "not a communicator" in _err(L.ql_nccl_all_gather(None, None, None, 4, None))
+    assert "not a communicator" in _err(L.ql_nccl_comm_split(None, 0, 0, ctypes.byref(none)))
+    assert "not a communicator" in _err(L.ql_nccl_comm_rank(None, None, None))
+    assert L.ql_nccl_comm_destroy(None) == 0           # destroying nothing is not an error
+    uid = ctypes.create_string_buffer(128)
+    rc = L.ql_nccl_comm_init_rank(3, 2, 0, uid, 0, ctypes.byref(none))
+    assert "rank 3 of 2" in _err(rc)
+    assert "null argument" in _err(L.ql_nccl_comm_init_rank(0, 1, 0, None, 0, ctypes.byref(none)))
+    assert "null argument" in _err(L.ql_nccl_unique_id(None))
+
+
 def _missing_replica():
     b = _peer(world=2)
     b.replica[1] = None

@@ -23,6 +23,7 @@ def test_fused_collectives_all_gpus_of_the_box():
     out = r.stdout + r.stderr
     print(out[-2000:])   # kept in the test log: which ranks ran and what they reported
     assert r.returncode == 0, out[-3000:]
+    assert "NCCL ABI OK" in out, out[-3000:]
     if "PEER UNAVAILABLE" in out:
         pytest.skip("no NVSwitch replication on this box")
     assert "PEER OK" in out, out[-3000:]
