@@ -95,7 +95,9 @@ NcclApi &api() {
   return a;
 }
 
-int no_nccl() { return set_error(QL_ERR_UNSUPPORTED, "nccl: libnccl.so.2 could not be loaded (%s)", dlerror() ? dlerror() : "missing symbols"); }
+int no_nccl() {
+  return set_error(QL_ERR_UNSUPPORTED, "nccl: %s", api().handle ? "libnccl.so.2 lacks an entry point this module binds" : "libnccl.so.2 could not be loaded");
+}
 
 int nccl_error(ncclResult_t r, const char *what) {
   return set_error(QL_ERR_CUDA, "nccl: %s failed: %s", what, api().GetErrorString ? api().GetErrorString(r) : "?");
