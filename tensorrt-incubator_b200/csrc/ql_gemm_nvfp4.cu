@@ -7,15 +7,21 @@
 // the tensor core itself: `tcgen05.mma.kind::mxf4nvf4.block_scale` multiplies every 16-element partial dot product
 // by the two block scales, which it reads from tensor memory.  The tensor scales gA * gB are applied in the epilogue.
 //
-// One persistent CTA per SM, 6 warps, 128 x 128 output tiles:
-//   warp 0   one lane issues, per k step of 256 elements, the TMA loads of the [128 x 128 B] A and B tiles (128-byte
-//            swizzle) and two bulk copies of 2 KiB of block scales each, all completing on the stage's barrier
+// One persistent CTA per SM, 6 warps, 128 x 224 output tiles.  At fp4 rates an MMA reads its operands from shared
+// memory faster than anything else in the SM can: M = 128, N = 128 needs 128 bytes per cycle, all the port has, which is
+// what bounded the first version of this kernel (128 x 128 tiles, 1.81 ms on 8192 x 28672 x 8192).  N = 224 needs 98 and
+// is the widest tile whose two accumulators (448 columns) still leave tensor memory room for one k step of scales (48).
+//   warp 0   one lane issues, per k step of 256 elements, the TMA loads of the [128 x 128 B] A and [224 x 128 B] B tiles
+//            (128-byte swizzle) and two bulk copies of block scales (2 KiB for A, 4 KiB for B), all completing on the
+//            stage's barrier
 //   warp 1   allocates tensor memory; per stage one lane copies the scales from shared to tensor memory
-//            (tcgen05.cp 32x128b.warpx4) and issues four MMAs (M=128, N=128, K=64)
+//            (tcgen05.cp 32x128b.warpx4) and issues four MMAs (M=128, N=224, K=64)
 //   warps 2-5 epilogue on a double-buffered accumulator
 // The tensor core wants the scales of 128 rows x 4 blocks as one 512-byte chunk, laid out as 32 rows of 16 bytes:
-// byte 16 * (r % 32) + 4 * (r / 32) + b holds the scale of row r, block b.  The operator's scale tensors are
-// row-major [rows, K/16], so a small kernel rewrites both into that order (scratch of the call) before the GEMM.
+// byte 16 * (r % 32) + 4 * (r / 32) + b holds the scale of row r, block b; in tensor memory that is 4 columns, row r in
+// column r / 32, and an operand of more than 128 rows continues in the next 4 columns.  The operator's scale tensors are
+// row-major [rows, K/16], so a small kernel rewrites both into that order, tile by tile (scratch of the call), before
+// the GEMM.
 // Every wait is bounded, as in the other tensor-core kernels.
 #include <cuda.h>
 
@@ -25,12 +31,15 @@
 namespace ql {
 namespace {
 
-constexpr int FBN = 128;                      // tile width
-constexpr int FSTAGES = 6;
+constexpr int FBN = 224;                      // tile width: two accumulators of 224 columns and the scales fill tensor memory
+constexpr int FSTAGES = 4;
 constexpr int kF4Threads = 192;
-constexpr int F_TILE_BYTES = BM * BK_BYTES;   // 16 KiB: 128 rows x 256 e2m1
+constexpr int F_TILE_BYTES = BM * BK_BYTES;   // 16 KiB: 128 rows x 256 e2m1 (the A tile)
+constexpr int F_TILE_B_BYTES = FBN * BK_BYTES; // 28 KiB: the B tile
 constexpr int F_SF_BYTES = 2048;              // scales of 128 rows x 16 blocks
-constexpr int F_STAGE_BYTES = 2 * F_TILE_BYTES + 2 * F_SF_BYTES;
+constexpr int F_SFB_GROUPS = (FBN + 127) / 128; // groups of 128 rows of B, the last one padded
+constexpr int F_STAGE_BYTES = F_TILE_BYTES + F_TILE_B_BYTES + (1 + F_SFB_GROUPS) * F_SF_BYTES;
+static_assert(F_STAGE_BYTES % 1024 == 0 && FBN % 32 == 0 && 2 * FBN + 16 + 16 * F_SFB_GROUPS <= 512, "tile shape");
 
 struct F4Smem {
   static constexpr int kTiles = FSTAGES * F_STAGE_BYTES;
@@ -43,7 +52,7 @@ struct F4Smem {
 
 struct F4Args {
   void *Y;
-  const uint8_t *sfa, *sfb; // scales in chunk order: [row group][k step][2048 bytes]
+  const uint8_t *sfa, *sfb; // scales in chunk order: [tile][k step][128-row group of the tile][2048 bytes]
   const float *ga, *gb;     // tensor scales (device scalars; null = 1)
   int y_dtype;
   int M, N;
@@ -52,20 +61,24 @@ struct F4Args {
   int *status;
 };
 
-// Row-major scales [rows, kb] (one byte per block of 16) -> chunk order, zero-padded to whole chunks.
+// Row-major scales [rows, kb] (one byte per block of 16) -> chunk order, zero-padded to whole chunks.  A tile of
+// `tile_rows` rows is cut into `groups` groups of 128 rows (the last one padded); per tile and k step the groups'
+// 2048-byte chunks follow one another.
 __global__ void __launch_bounds__(256) sf_reorder_kernel(const uint8_t *__restrict__ in, uint32_t *__restrict__ out, int rows, int kb, int num_ks,
-                                                         int64_t n_words) {
+                                                         int tile_rows, int groups, int64_t n_words) {
   const int64_t w = (int64_t)blockIdx.x * 256 + threadIdx.x;
   if (w >= n_words) return;
-  const int64_t per_group = (int64_t)num_ks * 512;
-  const int g = (int)(w / per_group);
-  const int rem = (int)(w % per_group);
-  const int s = rem / 512, v = rem % 512;
+  const int64_t per_tile = (int64_t)num_ks * groups * 512;
+  const int tile = (int)(w / per_tile);
+  const int rem = (int)(w % per_tile);
+  const int s = rem / (groups * 512), v2 = rem % (groups * 512);
+  const int sub = v2 / 512, v = v2 % 512;
   const int j = v / 128, cw = v % 128;
-  const int row = g * 128 + (cw % 4) * 32 + cw / 4;
+  const int local = sub * 128 + (cw % 4) * 32 + cw / 4;
+  const int row = tile * tile_rows + local;
   const int b0 = (s * 4 + j) * 4;
   uint32_t word = 0;
-  if (row < rows) {
+  if (local < tile_rows && row < rows) {
 #pragma unroll
     for (int i = 0; i < 4; i++)
       if (b0 + i < kb) word |= (uint32_t)in[(int64_t)row * kb + b0 + i] << (8 * i);
@@ -112,7 +125,7 @@ __device__ __forceinline__ uint32_t make_f4_idesc() {
 __global__ void __launch_bounds__(kF4Threads, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const F4Args args) {
   using L = F4Smem;
-  constexpr uint32_t kTmemCols = 512;           // 2 x 128 accumulator columns, then 32 scale columns per stage
+  constexpr uint32_t kTmemCols = 512;           // 2 x 224 accumulator columns, then one k step's scales: 16 columns of A's, 32 of B's
   constexpr uint32_t kSfCol0 = 2 * FBN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -161,15 +174,15 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int mt = tile % args.tiles_m, nt = tile / args.tiles_m; // row tiles of one column tile run side by side: B stays in L2
         const uint8_t *sfa = args.sfa + (size_t)mt * args.num_ks * F_SF_BYTES;
-        const uint8_t *sfb = args.sfb + (size_t)nt * args.num_ks * F_SF_BYTES;
+        const uint8_t *sfb = args.sfb + (size_t)nt * args.num_ks * (F_SFB_GROUPS * F_SF_BYTES);
         for (int ks = 0; ks < args.num_ks; ks++) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
-          const uint32_t a_dst = smem_base + stage * F_STAGE_BYTES, b_dst = a_dst + F_TILE_BYTES, s_dst = b_dst + F_TILE_BYTES;
+          const uint32_t a_dst = smem_base + stage * F_STAGE_BYTES, b_dst = a_dst + F_TILE_BYTES, s_dst = b_dst + F_TILE_B_BYTES;
           mbar_expect_tx(full_bar(stage), F_STAGE_BYTES);
           tma_load_2d(a_dst, &map_a, full_bar(stage), ks * BK_BYTES, mt * BM);   // coordinates in bytes of packed e2m1
           tma_load_2d(b_dst, &map_b, full_bar(stage), ks * BK_BYTES, nt * FBN);
           bulk_load(s_dst, sfa + (size_t)ks * F_SF_BYTES, F_SF_BYTES, full_bar(stage));
-          bulk_load(s_dst + F_SF_BYTES, sfb + (size_t)ks * F_SF_BYTES, F_SF_BYTES, full_bar(stage));
+          bulk_load(s_dst + F_SF_BYTES, sfb + (size_t)ks * (F_SFB_GROUPS * F_SF_BYTES), F_SFB_GROUPS * F_SF_BYTES, full_bar(stage));
           issued++;
           if (++stage == FSTAGES) { stage = 0; phase ^= 1; }
         }
@@ -200,17 +213,22 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (int ks = 0; ks < args.num_ks; ks++) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, ST_TIMEOUT_FULL)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = smem_base + stage * F_STAGE_BYTES, s_addr = a_addr + 2 * F_TILE_BYTES;
-          const uint32_t t_sfa = tmem_base + kSfCol0 + (uint32_t)stage * 32, t_sfb = t_sfa + 16;
+          const uint32_t a_addr = smem_base + stage * F_STAGE_BYTES, s_addr = a_addr + F_TILE_BYTES + F_TILE_B_BYTES;
+          // One slot of scale columns, rewritten every k step: the copies and the MMAs of one thread run in issue order,
+          // so a copy cannot overtake the MMAs that still read the slot.  A's scales: 4 columns per MMA (rows r of the
+          // tile in column r / 32); B's: 4 columns per group of 128 rows, the groups side by side.
+          const uint32_t t_sfa = tmem_base + kSfCol0, t_sfb = t_sfa + 16;
 #pragma unroll
           for (int j = 0; j < 4; j++) { // one 512-byte chunk = the scales of 128 rows for one MMA (4 blocks of 16)
             tc_copy_sf(t_sfa + 4 * j, make_sf_desc(s_addr + 512 * j));
-            tc_copy_sf(t_sfb + 4 * j, make_sf_desc(s_addr + F_SF_BYTES + 512 * j));
+#pragma unroll
+            for (int gI = 0; gI < F_SFB_GROUPS; gI++)
+              tc_copy_sf(t_sfb + 4 * (F_SFB_GROUPS * j + gI), make_sf_desc(s_addr + F_SF_BYTES * (1 + gI) + 512 * j));
           }
           const uint64_t adesc = make_smem_desc(a_addr), bdesc = make_smem_desc(a_addr + F_TILE_BYTES);
 #pragma unroll
           for (int j = 0; j < 4; j++) // each MMA consumes 64 elements = 32 bytes of K; +2 in the address field
-            tc_mma_f4(tmem_d, adesc + 2 * j, bdesc + 2 * j, idesc, t_sfa + 4 * j, t_sfb + 4 * j, (ks | j) != 0 ? 1u : 0u);
+            tc_mma_f4(tmem_d, adesc + 2 * j, bdesc + 2 * j, idesc, t_sfa + 4 * j, t_sfb + 4 * F_SFB_GROUPS * j, (ks | j) != 0 ? 1u : 0u);
           tc_commit(empty_bar(stage));
           if (++stage == FSTAGES) { stage = 0; phase ^= 1; }
         }
@@ -336,7 +354,7 @@ extern "C" int ql_gemm_nvfp4(const ql_tensor *a, const ql_tensor *a_scales, cons
   if (!args.status) return set_error(QL_ERR_CUDA, "%s: could not allocate the device status word", op);
 
   // both operands' block scales in the order the tensor core reads them, in scratch of this call
-  const size_t sfa_bytes = (size_t)args.tiles_m * args.num_ks * F_SF_BYTES, sfb_bytes = (size_t)args.tiles_n * args.num_ks * F_SF_BYTES;
+  const size_t sfa_bytes = (size_t)args.tiles_m * args.num_ks * F_SF_BYTES, sfb_bytes = (size_t)args.tiles_n * args.num_ks * F_SFB_GROUPS * F_SF_BYTES;
   uint8_t *scratch = nullptr;
   keep_scratch_pool_warm();
   QL_CUDA_TRY(cudaMallocAsync(&scratch, sfa_bytes + sfb_bytes, st));
@@ -344,9 +362,9 @@ extern "C" int ql_gemm_nvfp4(const ql_tensor *a, const ql_tensor *a_scales, cons
   args.sfb = scratch + sfa_bytes;
   const int64_t wa = (int64_t)(sfa_bytes / 4), wb = (int64_t)(sfb_bytes / 4);
   sf_reorder_kernel<<<(unsigned)((wa + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t *>(a_scales->data), reinterpret_cast<uint32_t *>(scratch), (int)M,
-                                                                  (int)(K / 16), args.num_ks, wa);
+                                                                  (int)(K / 16), args.num_ks, BM, 1, wa);
   sf_reorder_kernel<<<(unsigned)((wb + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t *>(b_scales->data),
-                                                                  reinterpret_cast<uint32_t *>(scratch + sfa_bytes), (int)N, (int)(K / 16), args.num_ks, wb);
+                                                                  reinterpret_cast<uint32_t *>(scratch + sfa_bytes), (int)N, (int)(K / 16), args.num_ks, FBN, F_SFB_GROUPS, wb);
   count_launches(2);
   rc = QL_OK;
   CUtensorMap ma, mb;
