@@ -7,10 +7,10 @@
 // the tensor core itself: `tcgen05.mma.kind::mxf4nvf4.block_scale` multiplies every 16-element partial dot product
 // by the two block scales, which it reads from tensor memory.  The tensor scales gA * gB are applied in the epilogue.
 //
-// One persistent CTA per SM, 6 warps, 128 x 224 output tiles.  At fp4 rates an MMA reads its operands from shared
-// memory faster than anything else in the SM can: M = 128, N = 128 needs 128 bytes per cycle, all the port has, which is
-// what bounded the first version of this kernel (128 x 128 tiles, 1.81 ms on 8192 x 28672 x 8192).  N = 224 needs 98 and
-// is the widest tile whose two accumulators (448 columns) still leave tensor memory room for one k step of scales (48).
+// One persistent CTA per SM, 6 warps, 128 x 224 output tiles: the widest tile whose two accumulators (448 columns)
+// still leave tensor memory room for one k step of scales (48), and wide tiles matter because per MMA the scales of
+// 128 + N rows have to be copied into tensor memory, which is what bounds this kernel (128 x 128 tiles: 1.81 ms on
+// 8192 x 28672 x 8192; these: 1.39 ms).
 //   warp 0   one lane issues, per k step of 256 elements, the TMA loads of the [128 x 128 B] A and [224 x 128 B] B tiles
 //            (128-byte swizzle) and two bulk copies of block scales (2 KiB for A, 4 KiB for B), all completing on the
 //            stage's barrier
@@ -24,6 +24,7 @@
 // the GEMM.
 // Every wait is bounded, as in the other tensor-core kernels.
 #include <cuda.h>
+#include <cstdlib>
 
 #include "ql_common.cuh"
 #include "ql_tc_common.cuh"
@@ -120,6 +121,41 @@ __device__ __forceinline__ uint32_t make_f4_idesc() {
   d |= (uint32_t)(FBN >> 3) << 17;
   d |= (uint32_t)(BM >> 4) << 24;
   return d;
+}
+
+// 32 columns of one accumulator row, times the tensor scales, rounded to y's type and stored
+__device__ __forceinline__ void f4_store_chunk(const F4Args &args, const uint32_t (&r)[32], int m, int n, float g) {
+  const size_t o = (size_t)m * (size_t)args.N + n;
+  const int cols = min(32, args.N - n);
+  if (args.y_dtype == QL_F32) {
+    float *y = static_cast<float *>(args.Y) + o;
+    for (int j = 0; j < cols; j++) y[j] = __uint_as_float(r[j]) * g;
+  } else if (args.y_dtype == QL_F16) {
+    __half *y = static_cast<__half *>(args.Y) + o;
+    if (cols == 32 && (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(args.Y) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8)
+        __stcs(reinterpret_cast<uint4 *>(y + j), make_uint4(pack2<__half>(__uint_as_float(r[j]) * g, __uint_as_float(r[j + 1]) * g),
+                                                            pack2<__half>(__uint_as_float(r[j + 2]) * g, __uint_as_float(r[j + 3]) * g),
+                                                            pack2<__half>(__uint_as_float(r[j + 4]) * g, __uint_as_float(r[j + 5]) * g),
+                                                            pack2<__half>(__uint_as_float(r[j + 6]) * g, __uint_as_float(r[j + 7]) * g)));
+    } else {
+      for (int j = 0; j < cols; j++) y[j] = __float2half_rn(__uint_as_float(r[j]) * g);
+    }
+  } else {
+    __nv_bfloat16 *y = static_cast<__nv_bfloat16 *>(args.Y) + o;
+    if (cols == 32 && (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(args.Y) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8)
+        __stcs(reinterpret_cast<uint4 *>(y + j),
+               make_uint4(pack2<__nv_bfloat16>(__uint_as_float(r[j]) * g, __uint_as_float(r[j + 1]) * g),
+                          pack2<__nv_bfloat16>(__uint_as_float(r[j + 2]) * g, __uint_as_float(r[j + 3]) * g),
+                          pack2<__nv_bfloat16>(__uint_as_float(r[j + 4]) * g, __uint_as_float(r[j + 5]) * g),
+                          pack2<__nv_bfloat16>(__uint_as_float(r[j + 6]) * g, __uint_as_float(r[j + 7]) * g)));
+    } else {
+      for (int j = 0; j < cols; j++) y[j] = __float2bfloat16_rn(__uint_as_float(r[j]) * g);
+    }
+  }
 }
 
 __global__ void __launch_bounds__(kF4Threads, 1)
@@ -258,39 +294,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         uint32_t r[32];
         tmem_load_32(taddr + c * 32, r);
         const int n = nt * FBN + c * 32;
-        if (m < args.M && n < args.N) {
-          const size_t o = (size_t)m * (size_t)args.N + n;
-          const int cols = min(32, args.N - n);
-          if (args.y_dtype == QL_F32) {
-            float *y = static_cast<float *>(args.Y) + o;
-            for (int j = 0; j < cols; j++) y[j] = __uint_as_float(r[j]) * g;
-          } else if (args.y_dtype == QL_F16) {
-            __half *y = static_cast<__half *>(args.Y) + o;
-            if (cols == 32 && (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(args.Y) & 15) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8)
-                __stcs(reinterpret_cast<uint4 *>(y + j), make_uint4(pack2<__half>(__uint_as_float(r[j]) * g, __uint_as_float(r[j + 1]) * g),
-                                                                    pack2<__half>(__uint_as_float(r[j + 2]) * g, __uint_as_float(r[j + 3]) * g),
-                                                                    pack2<__half>(__uint_as_float(r[j + 4]) * g, __uint_as_float(r[j + 5]) * g),
-                                                                    pack2<__half>(__uint_as_float(r[j + 6]) * g, __uint_as_float(r[j + 7]) * g)));
-            } else {
-              for (int j = 0; j < cols; j++) y[j] = __float2half_rn(__uint_as_float(r[j]) * g);
-            }
-          } else {
-            __nv_bfloat16 *y = static_cast<__nv_bfloat16 *>(args.Y) + o;
-            if (cols == 32 && (args.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(args.Y) & 15) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8)
-                __stcs(reinterpret_cast<uint4 *>(y + j),
-                       make_uint4(pack2<__nv_bfloat16>(__uint_as_float(r[j]) * g, __uint_as_float(r[j + 1]) * g),
-                                  pack2<__nv_bfloat16>(__uint_as_float(r[j + 2]) * g, __uint_as_float(r[j + 3]) * g),
-                                  pack2<__nv_bfloat16>(__uint_as_float(r[j + 4]) * g, __uint_as_float(r[j + 5]) * g),
-                                  pack2<__nv_bfloat16>(__uint_as_float(r[j + 6]) * g, __uint_as_float(r[j + 7]) * g)));
-            } else {
-              for (int j = 0; j < cols; j++) y[j] = __float2bfloat16_rn(__uint_as_float(r[j]) * g);
-            }
-          }
-        }
+        if (m < args.M && n < args.N) f4_store_chunk(args, r, m, n, g);
       }
       tc_fence_before();
       __syncwarp();
@@ -306,6 +310,236 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// The same product on CTA pairs: 256 x 224 tiles, `tcgen05.mma.cta_group::2` (M = 256) issued by the pair's leader.
+// Each CTA loads its own 128 rows of A, its own half of the B tile (112 rows), the scales of its A rows and the scales of
+// the whole B tile (each CTA's tensor core multiplies its rows by all 224 columns, so it needs them all), every copy a
+// TMA tile load that completes on the leader's barrier.  Per MMA a CTA then reads 128 + 112 rows of operands from its
+// shared memory instead of 128 + 224: 64 bytes per cycle at the fp4 rate, where the one-CTA tile needs 98.
+// Same bits as the one-CTA kernel (tests), but not faster (1.44 against 1.38 ms on 8192 x 28672 x 8192), and it is not
+// selected unless asked for: timing runs with the MMAs or the scale copies left out showed that both kernels are bound by
+// the scale copies (the copies alone take as long as the whole kernel, the MMAs alone two thirds of it; 12 copies of
+// 512 bytes per k step at about 120 cycles each, one 32-bit cell per cycle and lane quadrant), and a pair issues as many
+// copies per k step as a single CTA does.
+constexpr int PSTAGES = 5;
+constexpr int P_B_ROWS = FBN / 2;                                   // rows of the B tile one CTA holds
+constexpr int P_TILE_B_BYTES = P_B_ROWS * BK_BYTES;                 // 14 KiB
+constexpr int P_STAGE_BYTES = F_TILE_BYTES + P_TILE_B_BYTES + (1 + F_SFB_GROUPS) * F_SF_BYTES; // 36 KiB
+static_assert(P_STAGE_BYTES % 1024 == 0 && P_B_ROWS % 8 == 0, "pair stage layout");
+
+struct P4Smem {
+  static constexpr int kTiles = PSTAGES * P_STAGE_BYTES;
+  static constexpr int kBarriers = kTiles; // full[S], empty[S], tfull[2], tempty[2], drain
+  static constexpr int kTmemPtr = kBarriers + (2 * PSTAGES + 5) * 8;
+  static constexpr int kAbort = kTmemPtr + 4;
+  static constexpr int kTotal = kAbort + 4;
+  static constexpr int kDynamic = kTotal + 1024;
+};
+
+__device__ __forceinline__ uint32_t f4_cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t f4_map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void f4_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void f4_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void f4_tma_pair(uint32_t dst, const CUtensorMap *map, uint32_t leader_bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void f4_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void f4_copy_sf_pair(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void f4_mma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                            uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+               : "memory");
+}
+
+// args.tiles_m counts 256-row tiles here.  map_sfa / map_sfb see the re-ordered scales as rows of 256 bytes.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kF4Threads, 1)
+gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb, const F4Args args) {
+  using L = P4Smem;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kSfCol0 = 2 * FBN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::kBarriers;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (PSTAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * PSTAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * PSTAGES + 2 + b); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * PSTAGES + 4);
+  volatile uint32_t *tmem_ptr_smem = reinterpret_cast<volatile uint32_t *>(smem + L::kTmemPtr);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = f4_cluster_ctarank();
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  const int num_tiles = args.tiles_m * args.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PSTAGES; s++) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 8); // four epilogue warps in each CTA of the pair
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_ptr_smem)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  f4_cluster_sync(); // the partner's barriers exist before anything is signalled across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        const int mt = tile % args.tiles_m, nt = tile / args.tiles_m;
+        const int m0 = mt * 256 + (int)rank * BM, n0 = nt * FBN + (int)rank * P_B_ROWS;
+        // rows of 256 bytes in the re-ordered scales: A's by 128-row tile, B's by 224-column tile
+        const int sfa_row0 = (2 * mt + (int)rank) * args.num_ks * (F_SF_BYTES / 256);
+        const int sfb_row0 = nt * args.num_ks * (F_SFB_GROUPS * F_SF_BYTES / 256);
+        for (int ks = 0; ks < args.num_ks; ks++) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          const uint32_t a_dst = smem_base + stage * P_STAGE_BYTES, b_dst = a_dst + F_TILE_BYTES, s_dst = b_dst + P_TILE_B_BYTES;
+          const uint32_t leader_full = f4_map_to_cta(full_bar(stage), 0);
+          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * P_STAGE_BYTES); // both CTAs' bytes land on the leader's barrier
+          f4_tma_pair(a_dst, &map_a, leader_full, ks * BK_BYTES, m0);
+          f4_tma_pair(b_dst, &map_b, leader_full, ks * BK_BYTES, n0);
+          f4_tma_pair(s_dst, &map_sfa, leader_full, 0, sfa_row0 + ks * (F_SF_BYTES / 256));
+          f4_tma_pair(s_dst + F_SF_BYTES, &map_sfb, leader_full, 0, sfb_row0 + ks * (F_SFB_GROUPS * F_SF_BYTES / 256));
+          issued++;
+          if (++stage == PSTAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(f4_map_to_cta(smem_u32((const void *)abort_flag), rank ^ 1u)), "r"(1u) : "memory");
+        if (rank == 0) { // both CTAs' loads complete on the leader's barriers: let the ones in flight land
+          const long long pending = issued < PSTAGES ? issued : PSTAGES;
+          for (long long i = 0; i < pending; i++) {
+            stage = (stage == 0) ? PSTAGES - 1 : stage - 1;
+            if (stage == PSTAGES - 1) phase ^= 1;
+            const long long t0 = clock64();
+            while (!mbar_try_wait(full_bar(stage), phase) && clock64() - t0 < kWaitLimitCycles) {}
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ scale copies + MMA issue (leader only)
+    if (lane == 0 && rank == 0) {
+      uint32_t idesc = make_f4_idesc();
+      idesc &= ~(0x1Fu << 24);
+      idesc |= (uint32_t)(256 >> 4) << 24; // M = 256 over the pair
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, it++) {
+        const int buf = it & 1;
+        if (!mbar_wait(tempty_bar(buf), ((it >> 1) & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * FBN);
+        for (int ks = 0; ks < args.num_ks; ks++) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * P_STAGE_BYTES, s_addr = a_addr + F_TILE_BYTES + P_TILE_B_BYTES;
+          const uint32_t t_sfa = tmem_base + kSfCol0, t_sfb = t_sfa + 16;
+#pragma unroll
+          for (int j = 0; j < 4; j++) { // in both CTAs: from the CTA's own shared memory into its own tensor memory
+            f4_copy_sf_pair(t_sfa + 4 * j, make_sf_desc(s_addr + 512 * j));
+#pragma unroll
+            for (int gI = 0; gI < F_SFB_GROUPS; gI++)
+              f4_copy_sf_pair(t_sfb + 4 * (F_SFB_GROUPS * j + gI), make_sf_desc(s_addr + F_SF_BYTES * (1 + gI) + 512 * j));
+          }
+          const uint64_t adesc = make_smem_desc(a_addr), bdesc = make_smem_desc(a_addr + F_TILE_BYTES);
+#pragma unroll
+          for (int j = 0; j < 4; j++)
+            f4_mma_pair(tmem_d, adesc + 2 * j, bdesc + 2 * j, idesc, t_sfa + 4 * j, t_sfb + 4 * F_SFB_GROUPS * j, (ks | j) != 0 ? 1u : 0u);
+          f4_commit_pair(f4_map_to_cta(empty_bar(stage), 0));
+          f4_commit_pair(f4_map_to_cta(empty_bar(stage), 1));
+          if (++stage == PSTAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) {
+          f4_commit_pair(f4_map_to_cta(tfull_bar(buf), 0));
+          f4_commit_pair(f4_map_to_cta(tfull_bar(buf), 1));
+        }
+      }
+      if (!ok) asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(f4_map_to_cta(smem_u32((const void *)abort_flag), 1u)), "r"(1u) : "memory");
+      f4_commit_pair(f4_map_to_cta(drain_bar, 0));
+      const long long t0 = clock64();
+      while (!mbar_try_wait(drain_bar, 0)) {
+        if (clock64() - t0 > kWaitLimitCycles) { atomicCAS(args.status, 0, ST_TIMEOUT_DRAIN); break; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quad = warp & 3;
+    const float g = (args.ga ? __ldg(args.ga) : 1.f) * (args.gb ? __ldg(args.gb) : 1.f);
+    int it = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, it++) {
+      const int buf = it & 1;
+      const int mt = tile % args.tiles_m, nt = tile / args.tiles_m;
+      if (!mbar_wait(tfull_bar(buf), (it >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int m = mt * 256 + (int)rank * BM + quad * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * FBN);
+#pragma unroll 1
+      for (int c = 0; c < FBN / 32; c++) {
+        uint32_t r[32];
+        tmem_load_32(taddr + c * 32, r);
+        const int n = nt * FBN + c * 32;
+        if (m < args.M && n < args.N) f4_store_chunk(args, r, m, n, g);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) f4_arrive_cluster(f4_map_to_cta(tempty_bar(buf), 0)); // the leader owns the accumulator hand-over
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  f4_cluster_sync(); // neither CTA may leave while the pair's MMAs or barriers can still touch it
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
 int check_f4_operand(const char *op, const char *name, const ql_tensor *d, const ql_tensor *s, const ql_tensor *g) {
   if (!d || !s) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: %s is null", op, name);
   if (d->dtype != QL_F4E2M1 || s->dtype != QL_F8E4M3) return set_error(QL_ERR_INVALID_ARGUMENT, "%s: %s: data must be f4E2M1FN and scales f8E4M3FN", op, name);
@@ -318,7 +552,45 @@ int check_f4_operand(const char *op, const char *name, const ql_tensor *d, const
   return QL_OK;
 }
 
+// QL_NVFP4_KERNEL = pair: use the CTA-pair kernel wherever it can run (read once, again by ql_reload_tuning).  Unset, or
+// anything else: the one-CTA kernel, which is the faster of the two (see the pair kernel's comment).
+int read_f4_choice() {
+  const char *e = getenv("QL_NVFP4_KERNEL");
+  return !e ? 0 : (e[0] == 'o' ? 1 : (e[0] == 'p' ? 2 : 0));
+}
+int g_f4_choice = read_f4_choice();
+
+// CTA pairs of the pair kernel the device holds at once (0 = cannot run it)
+int f4_resident_pairs() {
+  static int cached[64] = {0};
+  static bool known[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (!known[dev]) {
+    int n = 0;
+    if (cudaFuncSetAttribute(gemm_nvfp4_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P4Smem::kDynamic) == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2 * sm_count(), 1, 1);
+      cfg.blockDim = dim3(kF4Threads, 1, 1);
+      cfg.dynamicSmemBytes = P4Smem::kDynamic;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      if (cudaOccupancyMaxActiveClusters(&n, gemm_nvfp4_pair_kernel, &cfg) != cudaSuccess) n = 0;
+    }
+    cudaGetLastError();
+    cached[dev] = n;
+    known[dev] = true;
+  }
+  return cached[dev];
+}
+
 } // namespace
+
+void f4_reload_tuning() { g_f4_choice = read_f4_choice(); }
+
 } // namespace ql
 
 using namespace ql;
@@ -368,8 +640,24 @@ extern "C" int ql_gemm_nvfp4(const ql_tensor *a, const ql_tensor *a_scales, cons
   count_launches(2);
   rc = QL_OK;
   CUtensorMap ma, mb;
-  // packed e2m1: a row is K / 2 bytes; the maps see bytes, like the e4m3 maps
-  if ((rc = make_map(&ma, KIND_F8, a->data, M, K / 2, BM)) == QL_OK && (rc = make_map(&mb, KIND_F8, b->data, N, K / 2, FBN)) == QL_OK) {
+  const int tiles_m256 = (int)((M + 255) / 256);
+  const int pairs = g_f4_choice == 2 ? f4_resident_pairs() : 0;
+  if (pairs > 0) {
+    // CTA pairs on 256 x 224 tiles; the scales travel as TMA tiles too (rows of 256 bytes of the re-ordered scratch)
+    CUtensorMap msa, msb;
+    args.tiles_m = tiles_m256;
+    if ((rc = make_map(&ma, KIND_F8, a->data, M, K / 2, BM)) == QL_OK && (rc = make_map(&mb, KIND_F8, b->data, N, K / 2, P_B_ROWS)) == QL_OK &&
+        (rc = make_map_bytes(&msa, args.sfa, (int64_t)(sfa_bytes / 256), 256, 256, F_SF_BYTES / 256)) == QL_OK &&
+        (rc = make_map_bytes(&msb, args.sfb, (int64_t)(sfb_bytes / 256), 256, 256, F_SFB_GROUPS * F_SF_BYTES / 256)) == QL_OK) {
+      const int tiles = args.tiles_m * args.tiles_n;
+      const int clusters = tiles < pairs ? tiles : pairs;
+      gemm_nvfp4_pair_kernel<<<2 * clusters, kF4Threads, P4Smem::kDynamic, st>>>(ma, mb, msa, msb, args);
+      count_launches(1);
+      cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) rc = cuda_error(e, "gemm_nvfp4_pair_kernel");
+    }
+  } else if ((rc = make_map(&ma, KIND_F8, a->data, M, K / 2, BM)) == QL_OK && (rc = make_map(&mb, KIND_F8, b->data, N, K / 2, FBN)) == QL_OK) {
+    // packed e2m1: a row is K / 2 bytes; the maps see bytes, like the e4m3 maps
     static bool configured[64] = {false};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);

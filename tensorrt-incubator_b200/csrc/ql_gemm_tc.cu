@@ -26,6 +26,7 @@
 namespace ql {
 void wo_reload_tuning(); // ql_wo_linear.cu
 void w8_reload_tuning(); // ql_gemm_w8a16.cu
+void f4_reload_tuning(); // ql_gemm_nvfp4.cu
 // ql_gemm_simt.cu
 int launch_gemm_simt(int dtype, const void *A, const void *B, const float *sa, int sa_n, const float *sb, int sb_n, const void *bias,
                      int bias_dtype, void *Y, int y_dtype, int batch, int M, int N, int K, int64_t a_m, int64_t a_k, int64_t b_k,
@@ -1384,6 +1385,7 @@ int ql_reload_tuning(void) {
   tuning() = read_tuning();
   wo_reload_tuning();
   w8_reload_tuning();
+  f4_reload_tuning();
   return QL_OK;
 }
 

@@ -113,6 +113,38 @@ def test_block_scaled_gemm_matches_dequantize_then_matmul(M, N, K, out):
     assert float((y.float() - ref).abs().max() / ref.abs().max()) < 1e-2
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 224, 256), (200, 136, 320), (512, 384, 1024), (1000, 1100, 2080), (129, 100, 64), (2048, 4096, 512)])
+@pytest.mark.parametrize("out", [torch.float32, torch.bfloat16])
+def test_block_scaled_gemm_on_cta_pairs(M, N, K, out, monkeypatch):
+    """The CTA-pair kernel (256 x 224 tiles, tcgen05.mma.cta_group::2, each CTA with its own rows of A and half of B and
+    the scales of both in its tensor memory), forced for shapes that would otherwise take the one-CTA kernel: against
+    the oracle as above (row tails inside the second CTA's half, column tails in either half of the B tile, k tails),
+    and bit for bit against the one-CTA kernel, which adds the same products in the same order."""
+    a, b = randn((M, K), torch.float32, 960 + M, std=2.0), randn((N, K), torch.float32, 961 + N, std=0.5)
+    ga, gb = 0.5, 2.0
+    qa, sa = ql.dynamic_quantize(a, ga)
+    qb, sb = ql.dynamic_quantize(b, gb)
+    results = {}
+    for choice in ("pair", "one"):
+        monkeypatch.setenv("QL_NVFP4_KERNEL", choice)
+        ql.lib().ql_reload_tuning()
+        try:
+            y = torch.full((M, N), float("nan"), dtype=out, device="cuda")
+            ql.gemm_nvfp4(qa, sa, qb, sb, ga, gb, out_dtype=ql.dtypes.from_torch(out), out=y)
+            torch.cuda.synchronize()
+            results[choice] = y
+        finally:
+            monkeypatch.delenv("QL_NVFP4_KERNEL")
+            ql.lib().ql_reload_tuning()
+    assert ql.lib().ql_gemm_status(None) == 0
+    want = orc.gemm_nvfp4(qa.packed.cpu().numpy().reshape(M, K // 2), to_np(sa), ga, qb.packed.cpu().numpy().reshape(N, K // 2), to_np(sb), gb)
+    got = results["pair"].double().cpu().numpy()
+    scale = np.sqrt(np.mean(want * want))
+    tol = 2e-5 if out == torch.float32 else 2.0 ** -8
+    assert np.all(np.abs(got - want) <= tol * np.maximum(np.abs(want), scale)), float(np.abs(got - want).max() / scale)
+    assert torch.equal(results["pair"], results["one"])
+
+
 def test_block_scaled_gemm_argument_rules():
     qa, sa = ql.dynamic_quantize(torch.ones((4, 48), device="cuda"))
     qb, sb = ql.dynamic_quantize(torch.ones((8, 48), device="cuda"))
