@@ -1233,24 +1233,35 @@ def main():
     s_in, s_run, s_out = torch.cuda.Stream(device), stream, torch.cuda.Stream(device)
     run_done, in_ready, out_done = {}, {}, {}
 
-    def e2e_step(step):
+    stage_events = []   # per timed unit: (upload start, upload end, kernels start, kernels end, read-back start, read-back end)
+
+    def e2e_step(step, timed=False):
+        def mark(st):
+            e = torch.cuda.Event(enable_timing=True)
+            e.record(st)
+            return e
         for in_key, out_key, f_in, f_run, f_out in wl.e2e_units(step):
             with torch.cuda.stream(s_in):
                 if in_key in run_done:
                     s_in.wait_event(run_done[in_key])      # the previous user of this input buffer has read it
+                t0 = mark(s_in) if timed else None
                 f_in()
-                in_ready[in_key] = s_in.record_event()
+                in_ready[in_key] = t1 = mark(s_in)
             with torch.cuda.stream(s_run):
                 s_run.wait_event(in_ready[in_key])
                 if out_key in out_done:
                     s_run.wait_event(out_done[out_key])    # the previous result in this output buffer has been read back
+                t2 = mark(s_run) if timed else None
                 f_run()
-                ev = s_run.record_event()
+                ev = mark(s_run)
                 run_done[in_key] = ev
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev)
+                t4 = mark(s_out) if timed else None
                 f_out()
-                out_done[out_key] = s_out.record_event()
+                out_done[out_key] = t5 = mark(s_out)
+            if timed:
+                stage_events.append((t0, t1, t2, ev, t4, t5))
 
     def e2e_join():
         stream.wait_stream(s_in)
@@ -1265,13 +1276,24 @@ def main():
     s_in.wait_stream(stream)
     s_out.wait_stream(stream)
     for i in range(K):
-        e2e_step(3 + i)
+        e2e_step(3 + i, timed=True)
     e2e_join()
     e_end.record(stream)
     barrier()
     e2e_ms = e_start.elapsed_time(e_end)
+    # where an end-to-end step spends its time on this rank: mean device time of each stage, and the mean distance between
+    # the starts of consecutive steps' kernels (the steady-state period)
+    n_ev = max(1, len(stage_events))
+    e2e_stages = {"upload_ms": sum(a.elapsed_time(b) for a, b, _, _, _, _ in stage_events) / n_ev,
+                  "kernels_ms": sum(c.elapsed_time(d) for _, _, c, d, _, _ in stage_events) / n_ev,
+                  "read_back_ms": sum(e.elapsed_time(f) for _, _, _, _, e, f in stage_events) / n_ev,
+                  "kernels_wait_for_upload_ms": sum(max(0.0, p[3].elapsed_time(q[2])) for p, q in zip(stage_events, stage_events[1:])) / max(1, n_ev - 1)}
 
     if dist is not None:
+        st_keys = sorted(e2e_stages)
+        st = torch.tensor([e2e_stages[k_] for k_ in st_keys], device=device, dtype=torch.float64)
+        dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        e2e_stages = {k_: float(v) for k_, v in zip(st_keys, st)}   # the slowest rank's figure for each stage
         t = torch.tensor([total_ms, e2e_ms] + part_ms, device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms, e2e_ms, part_ms = float(t[0]), float(t[1]), [float(v) for v in t[2:]]
@@ -1338,7 +1360,8 @@ def main():
                            timing="CUDA graph replay" if step_graphs else "direct launches"),
             "clocks": clock_info, "gpu_launches": int(launches),
             "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / K,
-                    "overlap": "uploads, kernels and read-backs on three streams, chained per buffer by events", "host_numa": numa},
+                    "overlap": "uploads, kernels and read-backs on three streams, chained per buffer by events", "host_numa": numa,
+                    "stages_max_over_ranks": e2e_stages},
             "roofline": roofline, "parts": per_part}
     if parity is not None:
         line["parity_check"] = parity
