@@ -87,6 +87,10 @@ def main():
     dev = torch.device("cuda", torch.cuda.current_device())
     dist.init_process_group("nccl", device_id=dev)
     check_nccl_entry_points(rank, world, dev)
+    # Partial results are added rank by rank in bf16 (in the epilogue, in the switch, or by NCCL), each addition rounding
+    # to 2^-9 of the running sum: the worst element may be off by (world - 1) such roundings on top of the benchmark's
+    # 1e-2, the bound `bench.py` uses for its own check (0.015 on two ranks, 0.03 on eight; never below 0.02 here).
+    tol = max(2e-2, 1e-2 + 0.0025 * world)
     if not peer.available():
         if rank == 0:
             print("PEER UNAVAILABLE")
@@ -119,7 +123,7 @@ def main():
             acc.barrier()
             torch.cuda.synchronize()
             e = rel_err(acc.local, full)
-            assert e < 2e-2, f"rank {rank}: ADD_ALL off by {e} for {(M, N, K)}"
+            assert e < tol, f"rank {rank}: ADD_ALL off by {e} for {(M, N, K)}"
         # reduce-scatter into the owners' rows, then the owners broadcast: the same sum again
         if M % (128 * world) == 0:
             rs = peer.PeerTensor((M, N), torch.bfloat16)
@@ -131,7 +135,7 @@ def main():
             rs.barrier()
             torch.cuda.synchronize()
             e = rel_err(rs.local, full)
-            assert e < 2e-2, f"rank {rank}: ADD_OWNER + broadcast off by {e} for {(M, N, K)}"
+            assert e < tol, f"rank {rank}: ADD_OWNER + broadcast off by {e} for {(M, N, K)}"
             assert same_everywhere(rs.local), "replicas differ after ADD_OWNER + broadcast"
         # local partial results summed by the switch: one rounding, so at least as close as the bf16 adds above
         sw_buf = peer.PeerTensor((M, N), torch.bfloat16)
@@ -143,7 +147,7 @@ def main():
             sw_buf.barrier()
             torch.cuda.synchronize()
             e = rel_err(sw_buf.local, full)
-            assert e < 2e-2, f"rank {rank}: in-switch reduce off by {e} for {(M, N, K)}"
+            assert e < tol, f"rank {rank}: in-switch reduce off by {e} for {(M, N, K)}"
             assert same_everywhere(sw_buf.local), "replicas differ after the in-switch reduce"
         # with two ranks a + b = b + a, so adding into every replica leaves them identical; with more ranks
         # the order of arrival differs per replica, which is why the MLP then uses owners
@@ -172,7 +176,7 @@ def main():
             got = mlp(x)
             torch.cuda.synchronize()
             e = rel_err(got, want)
-            assert e < 2e-2, f"rank {rank}: fused MLP ({name}) call {i} off by {e}"
+            assert e < tol, f"rank {rank}: fused MLP ({name}) call {i} off by {e}"
             assert same_everywhere(got), f"fused MLP ({name}) call {i}: ranks disagree"
     # Lifetime of the result: it is this rank's replica of one of a few internal buffers used in turn, promised intact
     # during the next call (so it can be read back while that call runs) and gone after the call after that.
@@ -183,7 +187,7 @@ def main():
         y2 = mlp(x2)
         torch.cuda.synchronize()
         assert y2.data_ptr() != y1.data_ptr() and torch.equal(y1, keep), f"MLP ({name}): the previous result was disturbed by the next call"
-        assert rel_err(y2, plain(x2)) < 2e-2
+        assert rel_err(y2, plain(x2)) < tol
     assert ql.lib().ql_gemm_status(None) == 0
     dist.barrier()
     if rank == 0:

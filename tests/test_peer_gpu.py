@@ -21,8 +21,8 @@ def test_fused_collectives_all_gpus_of_the_box():
            "--master-port", "29571", os.path.join(ROOT, "tests", "peer_worker.py")]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     out = r.stdout + r.stderr
-    print(out[-2000:])   # kept in the test log: which ranks ran and what they reported
-    assert r.returncode == 0, out[-3000:]
+    print(out[-12000:])   # kept in the test log: which ranks ran, what they reported and, on failure, the first traceback
+    assert r.returncode == 0, out[-12000:]
     assert "NCCL ABI OK" in out, out[-3000:]
     if "PEER UNAVAILABLE" in out:
         pytest.skip("no NVSwitch replication on this box")
