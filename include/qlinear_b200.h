@@ -292,6 +292,8 @@ QL_API int ql_rtexe_find_segment(const ql_rtexe *exe, const char *name); /* inde
  * __nccl_all_gather, __nccl_all_to_all, __nccl_permute).  Same conventions: communicators are non-blocking, and
  * every call ends by polling ncclCommGetAsyncError until the communicator has left ncclInProgress or `timeout_ms`
  * (5000 when <= 0, the reference's value; NCCLModule.cpp:88-106) has passed, returning QL_ERR_DEVICE_TIMEOUT then.
+ * (The first all_to_all / permute of a communicator connects every pair of ranks; on eight GPUs that alone took longer
+ * than five seconds, so a communicator meant for those should be created with a larger limit.)
  * NCCL itself is bound at run time (libnccl.so.2); without it these return QL_ERR_UNSUPPORTED and the rest of the
  * library is unaffected.  Buffers are device pointers; `stream` is a cudaStream_t.  The fused GEMM + collective
  * entry points above do not go through NCCL. */

@@ -39,7 +39,9 @@ def check_nccl_entry_points(rank, world, dev):
     from qlinear import nccl
     box = [nccl.unique_id() if rank == 0 else None]
     dist.broadcast_object_list(box, src=0)
-    comm = nccl.Communicator(rank, world, dev.index, box[0])
+    # a generous limit: the first point-to-point exchange of a communicator (all_to_all, permute) connects every pair of
+    # ranks, which took longer than the default five seconds on eight GPUs
+    comm = nccl.Communicator(rank, world, dev.index, box[0], timeout_ms=120000)
     assert (comm.rank, comm.num_ranks) == (rank, world)
     n = 4096
     mine = (torch.arange(n, device=dev) % 7 + rank).float()
