@@ -336,31 +336,6 @@ struct P4Smem {
   static constexpr int kDynamic = kTotal + 1024;
 };
 
-__device__ __forceinline__ uint32_t f4_cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ uint32_t f4_map_to_cta(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void f4_cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void f4_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void f4_tma_pair(uint32_t dst, const CUtensorMap *map, uint32_t leader_bar, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(x), "r"(y)
-               : "memory");
-}
-__device__ __forceinline__ void f4_commit_pair(uint32_t cluster_bar) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
-}
 __device__ __forceinline__ void f4_copy_sf_pair(uint32_t taddr, uint64_t desc) {
   asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
 }
@@ -392,7 +367,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kAbort);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t rank = f4_cluster_ctarank();
+  const uint32_t rank = cluster_ctarank();
   const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
   const int num_tiles = args.tiles_m * args.tiles_n;
 
@@ -415,7 +390,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   }
   tc_fence_before();
   __syncthreads();
-  f4_cluster_sync(); // the partner's barriers exist before anything is signalled across the pair
+  cluster_sync_all(); // the partner's barriers exist before anything is signalled across the pair
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
@@ -435,18 +410,18 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         for (int ks = 0; ks < args.num_ks; ks++) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, args.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           const uint32_t a_dst = smem_base + stage * P_STAGE_BYTES, b_dst = a_dst + F_TILE_BYTES, s_dst = b_dst + P_TILE_B_BYTES;
-          const uint32_t leader_full = f4_map_to_cta(full_bar(stage), 0);
+          const uint32_t leader_full = map_to_cta(full_bar(stage), 0);
           if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * P_STAGE_BYTES); // both CTAs' bytes land on the leader's barrier
-          f4_tma_pair(a_dst, &map_a, leader_full, ks * BK_BYTES, m0);
-          f4_tma_pair(b_dst, &map_b, leader_full, ks * BK_BYTES, n0);
-          f4_tma_pair(s_dst, &map_sfa, leader_full, 0, sfa_row0 + ks * (F_SF_BYTES / 256));
-          f4_tma_pair(s_dst + F_SF_BYTES, &map_sfb, leader_full, 0, sfb_row0 + ks * (F_SFB_GROUPS * F_SF_BYTES / 256));
+          tma_load_2d_pair(a_dst, &map_a, leader_full, ks * BK_BYTES, m0);
+          tma_load_2d_pair(b_dst, &map_b, leader_full, ks * BK_BYTES, n0);
+          tma_load_2d_pair(s_dst, &map_sfa, leader_full, 0, sfa_row0 + ks * (F_SF_BYTES / 256));
+          tma_load_2d_pair(s_dst + F_SF_BYTES, &map_sfb, leader_full, 0, sfb_row0 + ks * (F_SFB_GROUPS * F_SF_BYTES / 256));
           issued++;
           if (++stage == PSTAGES) { stage = 0; phase ^= 1; }
         }
       }
       if (!ok) {
-        asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(f4_map_to_cta(smem_u32((const void *)abort_flag), rank ^ 1u)), "r"(1u) : "memory");
+        signal_partner_abort(smem_u32((const void *)abort_flag), rank);
         if (rank == 0) { // both CTAs' loads complete on the leader's barriers: let the ones in flight land
           const long long pending = issued < PSTAGES ? issued : PSTAGES;
           for (long long i = 0; i < pending; i++) {
@@ -489,17 +464,17 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 #pragma unroll
           for (int j = 0; j < 4; j++)
             f4_mma_pair(tmem_d, adesc + 2 * j, bdesc + 2 * j, idesc, t_sfa + 4 * j, t_sfb + 4 * F_SFB_GROUPS * j, (ks | j) != 0 ? 1u : 0u);
-          f4_commit_pair(f4_map_to_cta(empty_bar(stage), 0));
-          f4_commit_pair(f4_map_to_cta(empty_bar(stage), 1));
+          tc_commit_pair(map_to_cta(empty_bar(stage), 0));
+          tc_commit_pair(map_to_cta(empty_bar(stage), 1));
           if (++stage == PSTAGES) { stage = 0; phase ^= 1; }
         }
         if (ok) {
-          f4_commit_pair(f4_map_to_cta(tfull_bar(buf), 0));
-          f4_commit_pair(f4_map_to_cta(tfull_bar(buf), 1));
+          tc_commit_pair(map_to_cta(tfull_bar(buf), 0));
+          tc_commit_pair(map_to_cta(tfull_bar(buf), 1));
         }
       }
-      if (!ok) asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(f4_map_to_cta(smem_u32((const void *)abort_flag), 1u)), "r"(1u) : "memory");
-      f4_commit_pair(f4_map_to_cta(drain_bar, 0));
+      if (!ok) signal_partner_abort(smem_u32((const void *)abort_flag), rank);
+      tc_commit_pair(map_to_cta(drain_bar, 0));
       const long long t0 = clock64();
       while (!mbar_try_wait(drain_bar, 0)) {
         if (clock64() - t0 > kWaitLimitCycles) { atomicCAS(args.status, 0, ST_TIMEOUT_DRAIN); break; }
@@ -527,13 +502,13 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) f4_arrive_cluster(f4_map_to_cta(tempty_bar(buf), 0)); // the leader owns the accumulator hand-over
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0)); // the leader owns the accumulator hand-over
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  f4_cluster_sync(); // neither CTA may leave while the pair's MMAs or barriers can still touch it
+  cluster_sync_all(); // neither CTA may leave while the pair's MMAs or barriers can still touch it
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");

@@ -114,20 +114,9 @@ __device__ __forceinline__ int rotated_kb(int kb, int num_kb, int who) {
   return v >= num_kb ? v - num_kb : v;
 }
 
-__device__ __forceinline__ uint32_t w8_cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void w8_cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 // 16 bytes into the shared memory of CTA `rank` of the cluster, at the address `local` has in this CTA
 __device__ __forceinline__ void w8_store_remote(uint32_t local, uint32_t rank, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
-  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(r), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(map_to_cta(local, rank)), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
 struct Ring {
@@ -171,7 +160,7 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   const int num_tiles = args.tiles_m * args.tiles_n;
   // K split: the cluster's CTAs share one tile and take consecutive ranges of the k-blocks; otherwise every CTA
   // walks the tiles with stride gridDim.x over the whole of K
-  const int krank = (KS > 1) ? (int)w8_cluster_rank() : 0;
+  const int krank = (KS > 1) ? (int)cluster_ctarank() : 0;
   const int tile_begin = (KS > 1) ? (int)blockIdx.x / KS : (int)blockIdx.x;
   const int tile_step = (KS > 1) ? num_tiles : (int)gridDim.x;
   const int nkb = args.num_kb / KS, kb_first = krank * nkb;
@@ -373,7 +362,7 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     __syncthreads();
     // every CTA of the cluster has finished its k range (its MMAs are complete: the issuer waited for them), so the
     // pipeline buffers are idle everywhere and may take the partial sums
-    w8_cluster_sync();
+    cluster_sync_all();
     if (worker) {
       // slot `krank` of every owner (this CTA included) receives this CTA's partial sums for the owner's columns
       int item = 0;
@@ -390,7 +379,7 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
       }
     }
-    w8_cluster_sync(); // release / acquire: the partial sums written into this CTA are visible
+    cluster_sync_all(); // release / acquire: the partial sums written into this CTA are visible
     if (worker) {
       // one item = eight adjacent columns of one row: added in rank order (whichever CTA does the adding), scaled,
       // rounded and stored as 16 bytes; consecutive threads take consecutive items, so a row's bytes leave together
